@@ -1,0 +1,176 @@
+/*
+ * lumi_b200 — C ABI of the B200 (sm_100a) implementation of lumi's token loop:
+ * prompt prefill plus the per-token Mamba-3 / attention decode step, with sampling on the device.
+ *
+ * This header is the whole drop-in boundary.  The reference's inference crate has no plugin
+ * interface; the seam it offers is the Rust API `NmModel::{load, init_states, forward_step}`
+ * called by `generate` (inference/src/main.rs:86,118,124,169), realised on its GPU path by the
+ * `*_metal` bridge functions (inference/src/metal_ssm.rs:135,251,341,431,589,628).  The style is
+ * that of the reference's own CUDA FFI (training/src/native_ops.rs:4-213): `extern "C"` free
+ * functions over plain pointers and 32/64-bit integers — with two deliberate differences: every
+ * call returns a status (the reference returns void and aborts, training/csrc/cublas_ops.cu:23-35)
+ * and all state lives in opaque handles with their own CUDA stream (no process globals).
+ *
+ * Rules that hold for every function:
+ *   - returns LUMI_OK (0) or a negative LUMI_E_* code; never aborts, never throws;
+ *   - after a failure, lumi_last_error() (calling thread) holds a message;
+ *   - host buffers passed in are borrowed for the duration of the call only;
+ *   - the library owns all device memory; nothing is allocated after lumi_session_create();
+ *   - one handle is driven by one host thread at a time; handles on different devices are
+ *     independent (one host thread or process per GPU; the path needs no collective);
+ *   - there is no CPU fallback: without a CUDA device every call that needs one fails.
+ */
+#ifndef LUMI_B200_H
+#define LUMI_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LUMI_OK              0
+#define LUMI_E_INVALID      -1   /* bad argument (null handle, batch out of range, ...)          */
+#define LUMI_E_CONFIG       -2   /* config.json missing a key / inconsistent dimensions          */
+#define LUMI_E_TENSOR       -3   /* unknown / missing / duplicate tensor, wrong shape or dtype   */
+#define LUMI_E_IO           -4   /* file cannot be read, malformed safetensors                   */
+#define LUMI_E_NOMEM        -5   /* device or host allocation failed                             */
+#define LUMI_E_CUDA         -6   /* CUDA runtime error (message carries cudaGetErrorString)      */
+#define LUMI_E_TIMEOUT      -7   /* a bounded device-side wait gave up (kernel returned cleanly) */
+#define LUMI_E_TOKEN        -8   /* token id >= vocab_size                                       */
+#define LUMI_E_KV_FULL      -9   /* attention cache capacity (max_tokens_kv) exceeded            */
+#define LUMI_E_UNSUPPORTED  -10  /* shape outside what the kernels were built for                */
+
+#define LUMI_DTYPE_F32  0
+#define LUMI_DTYPE_BF16 1
+
+typedef struct lumi_model   lumi_model;
+typedef struct lumi_session lumi_session;
+
+/* Sampling, replacing inference/src/main.rs:142-148,197-209.
+ * temperature <= 0: greedy argmax (lowest index wins ties).  Otherwise softmax(logits / temperature)
+ * and the reference's walk over the cumulative distribution in vocabulary order (first index whose
+ * cumulative sum >= r).  top_k > 0 keeps the k largest logits (ties towards the lower index) and
+ * renormalises before the walk (extension; 0 = reference behaviour).  r comes from Philox4x32-10:
+ * key = seed, counter = (step, sequence, 0, 0), first word, top 24 bits * 2^-24. */
+typedef struct lumi_sampling {
+    float    temperature;
+    int32_t  top_k;
+    uint64_t seed;
+    uint32_t eos_id;
+    int32_t  ignore_eos;      /* benchmark only: keep generating past eos */
+} lumi_sampling;
+
+typedef struct lumi_stats {
+    int64_t prompt_tokens;    /* batch * prompt length                          */
+    int64_t decode_tokens;    /* tokens produced by decode steps                */
+    float   ms_prefill;       /* CUDA-event time on the session stream          */
+    float   ms_decode;
+    int64_t bytes_per_step;   /* algorithmic bytes of one decode step at this batch:
+                                 weights once + per sequence (state read+write, KV)   */
+    int64_t kernel_launches;  /* kernels of this library launched in the timed phases  */
+} lumi_stats;
+
+/* Message for the last failure on the calling thread ("" if none). */
+const char* lumi_last_error(void);
+
+/* ---- model lifecycle: replaces load_model + NmModel::load (inference/src/main.rs:72-89,
+ *      inference/src/model.rs:643-728, 185-231, 469-489) -------------------------------------- */
+
+/* Parses config.json text (same keys and defaults as ModelConfig, inference/src/model.rs:20-48;
+ * unknown keys ignored; byte_level forces vocab_size 259; optional extensions attn_mlp_dim,
+ * attn_rope_base) and binds the model to a device. */
+int32_t lumi_model_create(const char* config_json, int32_t device_id, lumi_model** out);
+
+/* One call per safetensors entry, name including the `item.` prefix.  dtype F32 or BF16; rank-2
+ * tensors keep their stored width on the device, rank-1 tensors become fp32.  `ssm.h_init` may be
+ * rank 2 [n_heads, d_state] or rank 1 [n_heads * d_state]. */
+int32_t lumi_model_load_tensor(lumi_model* m, const char* name, int32_t dtype, const int64_t* shape,
+                               int32_t rank, const void* host_data, uint64_t nbytes);
+
+/* Convenience: reads a .safetensors file and calls lumi_model_load_tensor for each entry. */
+int32_t lumi_model_load_safetensors(lumi_model* m, const char* path);
+
+/* Checks that every tensor the config requires is present (b_bias / c_bias default to ones and
+ * h_init to zeros, as inference/src/model.rs:209-214) and prepares kernel-side tables. */
+int32_t lumi_model_finalize(lumi_model* m);
+
+void    lumi_model_free(lumi_model* m);
+
+/* Fills: d_model, n_layers, d_state, n_heads, head_dim, n_groups, vocab_size, n_mamba, n_attention,
+ * in_proj_out, weights dtype (LUMI_DTYPE_*), weight bytes read per step — 12 int64 values. */
+int32_t lumi_model_info(const lumi_model* m, int64_t* out12);
+
+/* ---- sessions: replaces NmModel::init_states + LayerState (inference/src/model.rs:112-159,
+ *      731-763) for `max_batch` independent sequences ----------------------------------------- */
+
+/* Allocates SSM state (fp32, rank-1 factors for prev_bx), the attention cache for max_tokens_kv
+ * tokens per sequence (bf16, ignored for models without attention layers) and all scratch, then
+ * resets every slot. */
+int32_t lumi_session_create(lumi_model* m, int32_t max_batch, int32_t max_tokens_kv, lumi_session** out);
+
+/* h <- h_init broadcast over head_dim, prev_bx <- 0, cum_angle <- 0, cache emptied.
+ * slots == NULL resets all. */
+int32_t lumi_session_reset(lumi_session* s, const int32_t* slots, int32_t n_slots);
+
+void    lumi_session_free(lumi_session* s);
+
+/* Options (name, value):  "gemm" = 0 auto | 1 SIMT only | 2 tcgen05 only;
+ *                         "split_activations" = 1 (default) feeds tensor-core GEMMs with bf16 hi+lo
+ *                         halves of each fp32 activation, 0 rounds activations to bf16 once;
+ *                         "graph" = 1 (default) replays the decode step as a CUDA graph. */
+int32_t lumi_session_set_option(lumi_session* s, const char* name, int64_t value);
+
+/* ---- token loop: replaces NmModel::forward_step (inference/src/model.rs:766-801) and the
+ *      generate loop (inference/src/main.rs:118-170) ------------------------------------------ */
+
+/* Feeds tokens[batch][T] (row-major) through the model position by position, exactly as the
+ * reference prefills (main.rs:121-125).  last_logits (may be NULL): [batch][vocab] fp32 of the final
+ * position.  Sequences occupy slots 0..batch-1. */
+int32_t lumi_prefill(lumi_session* s, const uint32_t* tokens, int32_t batch, int32_t T, float* last_logits);
+
+/* One forward_step for each of `batch` sequences: consumes in_tokens[batch], writes the sampled /
+ * argmax next token to out_tokens[batch] (may be NULL) and, if logits_out != NULL, the logits
+ * [batch][vocab].  `step` indexes the Philox counter. */
+int32_t lumi_decode_step(lumi_session* s, const uint32_t* in_tokens, int32_t batch, const lumi_sampling* sp,
+                         int32_t step, uint32_t* out_tokens, float* logits_out);
+
+/* The whole generate loop on the device with one host synchronisation: prefill prompts[batch][T],
+ * then n_new tokens per sequence.  out_tokens[batch][n_new]; out_lens[batch] = tokens before eos
+ * (n_new when ignore_eos).  logits_dump (may be NULL): [n_new][batch][vocab], the logits each
+ * generated token was chosen from.  stats may be NULL. */
+int32_t lumi_generate(lumi_session* s, const uint32_t* prompts, int32_t batch, int32_t T, int32_t n_new,
+                      const lumi_sampling* sp, uint32_t* out_tokens, int32_t* out_lens,
+                      float* logits_dump, lumi_stats* stats);
+
+/* Device-resident decode loop for measurement: runs n_steps decode steps, each consuming the
+ * previous step's greedy tokens, no host traffic.  ms_out: CUDA-event time on the session stream. */
+int32_t lumi_decode_loop_device(lumi_session* s, int32_t batch, int32_t n_steps, float* ms_out,
+                                int64_t* launches_out);
+
+/* Copies one sequence's Mamba state of one layer to host (any pointer may be NULL):
+ * h [H][P][N], x_prev [H][P], b_prev [H][N] (prev_bx = x_prev (x) b_prev), cum_angle [H][N/2]. */
+int32_t lumi_session_read_state(lumi_session* s, int32_t slot, int32_t layer, float* h, float* x_prev,
+                                float* b_prev, float* cum_angle);
+
+/* Runs block `layer` alone on a caller-supplied residual stream x[batch][d_model] (host, in/out),
+ * using and updating the session state — for per-layer parity tests. */
+int32_t lumi_debug_run_block(lumi_session* s, int32_t layer, float* x, int32_t batch);
+
+/* ---- single kernels over caller-owned DEVICE pointers (tests, profiling) -------------------- */
+
+/* D[M][N] (fp32, row-major, leading dimension ldd) = A[M][K] * W[N][K]^T (+ D if accumulate != 0),
+ * A given as bf16 hi (and optional lo, may be 0) halves, W bf16, K % 64 == 0.  tcgen05 + TMA.
+ * stream: cudaStream_t as integer (0 = default stream). */
+int32_t lumi_k_gemm_bf16_tcgen05(uint64_t a_hi, uint64_t a_lo, uint64_t w, uint64_t d, int32_t M, int32_t N,
+                                 int32_t K, int32_t ldd, int32_t accumulate, uint64_t stream);
+
+/* Same contraction on CUDA cores with fp32 activations: D[M][N] = A[M][K] * W[N][K]^T (+ residual R).
+ * w_dtype LUMI_DTYPE_*.  norm_gamma != 0 applies RMSNorm(gamma) to each row of A first. */
+int32_t lumi_k_gemv(uint64_t a_f32, uint64_t w, int32_t w_dtype, uint64_t d, uint64_t residual,
+                    uint64_t norm_gamma, int32_t M, int32_t N, int32_t K, uint64_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUMI_B200_H */

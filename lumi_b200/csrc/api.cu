@@ -1,0 +1,852 @@
+// C ABI of liblumi_b200.so: config / weight loading, sessions, the decode step and the generate
+// loop.  Replaces load_model + NmModel::{load, init_states, forward_step} and the token loop of
+// the reference (inference/src/main.rs:72-89, 118-170; inference/src/model.rs:643-801).
+#include "internal.h"
+#include "json_min.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <algorithm>
+
+using namespace lumi;
+
+// ---- errors -----------------------------------------------------------------------------------------
+namespace lumi {
+static thread_local char g_err[1024] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+int32_t fail(int32_t code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+bool Config::is_attention_layer(int i) const {          // model.rs:66-71
+    if (!attention_layers.empty())
+        return std::find(attention_layers.begin(), attention_layers.end(), i) != attention_layers.end();
+    return attention_interval > 0 && (i + 1) % attention_interval == 0;
+}
+int Config::n_attn_layers() const {
+    int n = 0;
+    for (int i = 0; i < n_layers; ++i) n += is_attention_layer(i) ? 1 : 0;
+    return n;
+}
+
+static bool get_int(const JsonValue& root, const char* key, bool required, int& out, std::string& err) {
+    const JsonValue* v = root.find(key);
+    if (!v) {
+        if (required) { err = std::string("config.json: missing key '") + key + "'"; return false; }
+        return true;
+    }
+    if (v->kind != JsonValue::Number || v->num < 0 || v->num != (double)(long long)v->num) {
+        err = std::string("config.json: key '") + key + "' must be a non-negative integer";
+        return false;
+    }
+    out = (int)v->num;
+    return true;
+}
+static bool get_int_list(const JsonValue& root, const char* key, std::vector<int>& out, std::string& err) {
+    const JsonValue* v = root.find(key);
+    if (!v) return true;
+    if (v->kind != JsonValue::Array) { err = std::string("config.json: key '") + key + "' must be an array"; return false; }
+    for (auto& e : v->arr) {
+        if (e.kind != JsonValue::Number || e.num < 0) { err = std::string("config.json: '") + key + "' holds a non-integer"; return false; }
+        out.push_back((int)e.num);
+    }
+    return true;
+}
+
+int32_t parse_config(const char* json, Config& c) {
+    if (!json) return fail(LUMI_E_INVALID, "config text is null");
+    JsonValue root;
+    std::string err;
+    JsonParser p(json, strlen(json));
+    if (!p.parse(root, err) || root.kind != JsonValue::Object) return fail(LUMI_E_CONFIG, "config.json: %s", err.empty() ? "not a JSON object" : err.c_str());
+    bool ok = get_int(root, "d_model", true, c.d_model, err) && get_int(root, "n_layers", true, c.n_layers, err) &&
+              get_int(root, "d_state", true, c.d_state, err) && get_int(root, "expand", true, c.expand, err) &&
+              get_int(root, "n_heads", true, c.n_heads, err) && get_int(root, "n_groups", true, c.n_groups, err) &&
+              get_int(root, "vocab_size", true, c.vocab, err) && get_int(root, "max_seq_len", true, c.max_seq_len, err) &&
+              get_int(root, "attention_interval", false, c.attention_interval, err) &&
+              get_int(root, "attn_n_heads", false, c.attn_n_heads, err) && get_int(root, "attn_kv_heads", false, c.attn_kv_heads, err) &&
+              get_int(root, "attn_mlp_expand", false, c.attn_mlp_expand, err) && get_int(root, "attn_mlp_dim", false, c.attn_mlp_dim, err) &&
+              get_int_list(root, "attn_window_sizes", c.attn_window_sizes, err) &&
+              get_int_list(root, "attention_layers", c.attention_layers, err);
+    if (!ok) return fail(LUMI_E_CONFIG, "%s", err.c_str());
+    if (const JsonValue* v = root.find("byte_level")) {
+        if (v->kind != JsonValue::Bool) return fail(LUMI_E_CONFIG, "config.json: key 'byte_level' must be a boolean");
+        c.byte_level = v->b;
+    }
+    if (const JsonValue* v = root.find("attn_rope_base")) {
+        if (v->kind != JsonValue::Number || v->num < 0) return fail(LUMI_E_CONFIG, "config.json: key 'attn_rope_base' must be a number >= 0");
+        c.attn_rope_base = (float)v->num;
+    }
+    if (c.byte_level) c.vocab = 259;                                    // main.rs:75-77
+    // the reference's divisibility invariants (training/tests/training_init_tests.rs:70-112) plus vector widths
+    if (c.d_model <= 0 || c.n_layers <= 0 || c.d_state <= 0 || c.expand <= 0 || c.n_heads <= 0 || c.n_groups <= 0 || c.vocab <= 0)
+        return fail(LUMI_E_CONFIG, "config.json: dimensions must be positive");
+    if (c.d_inner() % c.n_heads) return fail(LUMI_E_CONFIG, "config.json: expand*d_model (%d) not divisible by n_heads (%d)", c.d_inner(), c.n_heads);
+    if (c.n_heads % c.n_groups) return fail(LUMI_E_CONFIG, "config.json: n_heads (%d) not divisible by n_groups (%d)", c.n_heads, c.n_groups);
+    if (c.d_state % 2) return fail(LUMI_E_CONFIG, "config.json: d_state (%d) must be even", c.d_state);
+    if (c.d_model % 8) return fail(LUMI_E_CONFIG, "config.json: d_model (%d) must be a multiple of 8", c.d_model);
+    if (c.n_attn_layers() > 0) {
+        if (c.attn_n_heads <= 0 || c.attn_kv_heads <= 0 || c.d_model % c.attn_n_heads || c.attn_n_heads % c.attn_kv_heads)
+            return fail(LUMI_E_CONFIG, "config.json: attention heads (%d query / %d kv) do not divide d_model", c.attn_n_heads, c.attn_kv_heads);
+        if (c.mlp_dim() % 8) return fail(LUMI_E_CONFIG, "config.json: attention MLP width (%d) must be a multiple of 8", c.mlp_dim());
+        for (int l : c.attention_layers) if (l >= c.n_layers) return fail(LUMI_E_CONFIG, "config.json: attention_layers entry %d >= n_layers", l);
+    }
+    return LUMI_OK;
+}
+}  // namespace lumi
+
+extern "C" const char* lumi_last_error(void) { return lumi::g_err; }
+
+// ---- model ------------------------------------------------------------------------------------------
+static float bf16_to_f32(uint16_t b) {
+    uint32_t u = (uint32_t)b << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+extern "C" int32_t lumi_model_create(const char* config_json, int32_t device_id, lumi_model** out) {
+    if (!out) return fail(LUMI_E_INVALID, "out pointer is null");
+    *out = nullptr;
+    Config c;
+    LUMI_TRY(parse_config(config_json, c));
+    int ndev = 0;
+    LUMI_CUDA(cudaGetDeviceCount(&ndev));
+    if (device_id < 0 || device_id >= ndev) return fail(LUMI_E_INVALID, "device %d not available (%d CUDA devices)", device_id, ndev);
+    if (!ssm_shape_supported(c.head_dim(), c.d_state) && c.n_attn_layers() < c.n_layers)
+        return fail(LUMI_E_UNSUPPORTED, "head_dim %d / d_state %d: kernels exist for head_dim in {16,32,64} and d_state in {16,32,64,128}", c.head_dim(), c.d_state);
+    lumi_model* m = new lumi_model();
+    m->cfg = c;
+    m->device = device_id;
+    *out = m;
+    return LUMI_OK;
+}
+
+// Expected shape of a tensor by its name (without the "item." prefix); rank 0 = not a tensor of this model.
+static int expected_shape(const lumi_model* m, const std::string& name, int64_t shp[2]) {
+    const Config& c = m->cfg;
+    if (name == "embedding.weight") { shp[0] = c.vocab; shp[1] = c.d_model; return 2; }
+    if (name == "final_norm.gamma") { shp[0] = c.d_model; return 1; }
+    if (name.rfind("blocks.", 0) != 0) return 0;
+    size_t dot = name.find('.', 7);
+    if (dot == std::string::npos) return 0;
+    int layer = -1;
+    try { layer = std::stoi(name.substr(7, dot - 7)); } catch (...) { return 0; }
+    if (layer < 0 || layer >= c.n_layers) return 0;
+    const std::string k = name.substr(dot + 1);
+    const bool attn = c.is_attention_layer(layer);
+    if (!attn) {
+        if (k == "norm.gamma") { shp[0] = c.d_model; return 1; }
+        if (k == "in_proj.weight") { shp[0] = c.in_proj_out(); shp[1] = c.d_model; return 2; }
+        if (k == "out_proj.weight") { shp[0] = c.d_model; shp[1] = c.d_inner(); return 2; }
+        if (k == "b_norm.gamma" || k == "c_norm.gamma" || k == "b_bias" || k == "c_bias") { shp[0] = c.bc(); return 1; }
+        if (k == "ssm.d" || k == "ssm.dt_bias") { shp[0] = c.n_heads; return 1; }
+        if (k == "ssm.h_init") { shp[0] = c.n_heads; shp[1] = c.d_state; return 2; }
+        return 0;
+    }
+    if (k == "attn_norm.gamma" || k == "mlp_norm.gamma") { shp[0] = c.d_model; return 1; }
+    if (k == "q_proj.weight" || k == "attn_out_proj.weight") { shp[0] = c.d_model; shp[1] = c.d_model; return 2; }
+    if (k == "k_proj.weight" || k == "v_proj.weight") { shp[0] = c.kv_dim(); shp[1] = c.d_model; return 2; }
+    if (k == "mlp_gate.weight" || k == "mlp_up.weight") { shp[0] = c.mlp_dim(); shp[1] = c.d_model; return 2; }
+    if (k == "mlp_down.weight") { shp[0] = c.d_model; shp[1] = c.mlp_dim(); return 2; }
+    return 0;
+}
+
+extern "C" int32_t lumi_model_load_tensor(lumi_model* m, const char* name, int32_t dtype, const int64_t* shape, int32_t rank,
+                                          const void* host_data, uint64_t nbytes) {
+    if (!m || !name || !host_data || (!shape && rank > 0)) return fail(LUMI_E_INVALID, "null argument to lumi_model_load_tensor");
+    if (m->finalized) return fail(LUMI_E_INVALID, "model already finalized");
+    if (dtype != LUMI_DTYPE_F32 && dtype != LUMI_DTYPE_BF16) return fail(LUMI_E_TENSOR, "tensor '%s': dtype code %d not supported (F32, BF16)", name, dtype);
+    std::string n(name);
+    if (n.rfind("item.", 0) != 0) return LUMI_OK;         // the reference only reads names under "item." (main.rs:86)
+    n = n.substr(5);
+    int64_t exp[2] = {0, 0};
+    const int erank = expected_shape(m, n, exp);
+    if (erank == 0) return LUMI_OK;                       // tensors the model never asks for are ignored, as VarBuilder does
+    if (m->tensors.count(n)) return fail(LUMI_E_TENSOR, "tensor '%s' loaded twice", name);
+    int64_t count = 1;
+    for (int i = 0; i < rank; ++i) count *= shape[i];
+    const bool is_hinit = n.size() > 10 && n.compare(n.size() - 10, 10, "ssm.h_init") == 0;
+    bool shape_ok = (rank == erank);
+    for (int i = 0; shape_ok && i < rank; ++i) shape_ok = (shape[i] == exp[i]);
+    if (is_hinit && rank == 1 && shape[0] == exp[0] * exp[1]) shape_ok = true;   // the trainer writes it flat (native_checkpoint.rs:55)
+    if (!shape_ok) {
+        char got[128] = "", want[128] = "";
+        for (int i = 0; i < rank && i < 4; ++i) snprintf(got + strlen(got), sizeof(got) - strlen(got), "%s%lld", i ? "," : "", (long long)shape[i]);
+        for (int i = 0; i < erank; ++i) snprintf(want + strlen(want), sizeof(want) - strlen(want), "%s%lld", i ? "," : "", (long long)exp[i]);
+        return fail(LUMI_E_TENSOR, "tensor '%s': shape [%s], expected [%s]", name, got, want);
+    }
+    const size_t esz = dtype == LUMI_DTYPE_BF16 ? 2 : 4;
+    if ((uint64_t)count * esz != nbytes) return fail(LUMI_E_TENSOR, "tensor '%s': %llu bytes given, shape needs %llu", name, (unsigned long long)nbytes, (unsigned long long)(count * esz));
+    LUMI_CUDA(cudaSetDevice(m->device));
+    DevTensor t;
+    const bool keep_width = (erank == 2) && !is_hinit;
+    if (keep_width) {
+        if (m->wdtype >= 0 && m->wdtype != dtype) return fail(LUMI_E_TENSOR, "tensor '%s': rank-2 tensors mix F32 and BF16", name);
+        m->wdtype = dtype;
+        t.dtype = dtype;
+        t.rows = exp[0]; t.cols = exp[1];
+        t.bytes = nbytes;
+        LUMI_CUDA(cudaMalloc(&t.p, t.bytes));
+        LUMI_CUDA(cudaMemcpy(t.p, host_data, t.bytes, cudaMemcpyHostToDevice));
+    } else {
+        std::vector<float> tmp;
+        const float* src = (const float*)host_data;
+        if (dtype == LUMI_DTYPE_BF16) {
+            tmp.resize(count);
+            const uint16_t* b = (const uint16_t*)host_data;
+            for (int64_t i = 0; i < count; ++i) tmp[i] = bf16_to_f32(b[i]);
+            src = tmp.data();
+        }
+        t.dtype = LUMI_DTYPE_F32;
+        t.rows = 1; t.cols = count;
+        t.bytes = (size_t)count * 4;
+        LUMI_CUDA(cudaMalloc(&t.p, t.bytes));
+        LUMI_CUDA(cudaMemcpy(t.p, src, t.bytes, cudaMemcpyHostToDevice));
+    }
+    m->tensors[n] = t;
+    return LUMI_OK;
+}
+
+static int32_t need(lumi_model* m, const std::string& n, DevTensor& out) {
+    auto it = m->tensors.find(n);
+    if (it == m->tensors.end()) return fail(LUMI_E_TENSOR, "tensor 'item.%s' is missing", n.c_str());
+    out = it->second;
+    return LUMI_OK;
+}
+static int32_t need_f(lumi_model* m, const std::string& n, const float*& out) {
+    DevTensor t;
+    LUMI_TRY(need(m, n, t));
+    out = (const float*)t.p;
+    return LUMI_OK;
+}
+static int32_t ones_default(lumi_model* m, const std::string& n, int count, const float*& out) {   // model.rs:209-212
+    auto it = m->tensors.find(n);
+    if (it != m->tensors.end()) { out = (const float*)it->second.p; return LUMI_OK; }
+    std::vector<float> ones(count, 1.0f);
+    void* p = nullptr;
+    LUMI_CUDA(cudaMalloc(&p, (size_t)count * 4));
+    LUMI_CUDA(cudaMemcpy(p, ones.data(), (size_t)count * 4, cudaMemcpyHostToDevice));
+    m->owned.push_back(p);
+    out = (const float*)p;
+    return LUMI_OK;
+}
+// rows of several [r_i][cols] matrices stacked into one allocation; the parts are released
+static int32_t concat_rows(lumi_model* m, const std::vector<std::string>& names, DevTensor& out) {
+    std::vector<DevTensor> parts(names.size());
+    size_t total = 0;
+    int64_t rows = 0;
+    for (size_t i = 0; i < names.size(); ++i) { LUMI_TRY(need(m, names[i], parts[i])); total += parts[i].bytes; rows += parts[i].rows; }
+    void* p = nullptr;
+    LUMI_CUDA(cudaMalloc(&p, total));
+    size_t off = 0;
+    for (size_t i = 0; i < names.size(); ++i) {
+        LUMI_CUDA(cudaMemcpy((char*)p + off, parts[i].p, parts[i].bytes, cudaMemcpyDeviceToDevice));
+        off += parts[i].bytes;
+        LUMI_CUDA(cudaFree(parts[i].p));
+        m->tensors[names[i]].p = nullptr;
+    }
+    m->owned.push_back(p);
+    out = parts[0];
+    out.p = p; out.rows = rows; out.bytes = total;
+    return LUMI_OK;
+}
+
+extern "C" int32_t lumi_model_finalize(lumi_model* m) {
+    if (!m) return fail(LUMI_E_INVALID, "model is null");
+    if (m->finalized) return LUMI_OK;
+    LUMI_CUDA(cudaSetDevice(m->device));
+    const Config& c = m->cfg;
+    LUMI_TRY(need(m, "embedding.weight", m->embedding));
+    LUMI_TRY(need_f(m, "final_norm.gamma", m->final_norm_g));
+    m->weight_bytes = 0;
+    for (auto& kv : m->tensors) m->weight_bytes += (int64_t)kv.second.bytes;
+    m->layers.assign(c.n_layers, Layer());
+    int im = 0, ia = 0;
+    for (int i = 0; i < c.n_layers; ++i) {
+        Layer& L = m->layers[i];
+        const std::string p = "blocks." + std::to_string(i) + ".";
+        L.is_attn = c.is_attention_layer(i);
+        if (!L.is_attn) {
+            L.kind_idx = im++;
+            LUMI_TRY(need_f(m, p + "norm.gamma", L.m.norm_g));
+            LUMI_TRY(need(m, p + "in_proj.weight", L.m.in_proj));
+            LUMI_TRY(need(m, p + "out_proj.weight", L.m.out_proj));
+            LUMI_TRY(need_f(m, p + "b_norm.gamma", L.m.b_gamma));
+            LUMI_TRY(need_f(m, p + "c_norm.gamma", L.m.c_gamma));
+            LUMI_TRY(ones_default(m, p + "b_bias", c.bc(), L.m.b_bias));
+            LUMI_TRY(ones_default(m, p + "c_bias", c.bc(), L.m.c_bias));
+            LUMI_TRY(need_f(m, p + "ssm.d", L.m.d_skip));
+            LUMI_TRY(need_f(m, p + "ssm.dt_bias", L.m.dt_bias));
+            auto it = m->tensors.find(p + "ssm.h_init");                 // optional: zeros (model.rs:214, 744-748)
+            L.m.h_init = it == m->tensors.end() ? nullptr : (const float*)it->second.p;
+        } else {
+            L.kind_idx = ia;
+            L.window = c.attn_window_size(ia);
+            ++ia;
+            LUMI_TRY(need_f(m, p + "attn_norm.gamma", L.a.attn_norm_g));
+            LUMI_TRY(need_f(m, p + "mlp_norm.gamma", L.a.mlp_norm_g));
+            LUMI_TRY(concat_rows(m, {p + "q_proj.weight", p + "k_proj.weight", p + "v_proj.weight"}, L.a.qkv));
+            LUMI_TRY(need(m, p + "attn_out_proj.weight", L.a.o));
+            LUMI_TRY(concat_rows(m, {p + "mlp_gate.weight", p + "mlp_up.weight"}, L.a.gate_up));
+            LUMI_TRY(need(m, p + "mlp_down.weight", L.a.down));
+        }
+    }
+    m->n_mamba = im;
+    m->n_attn = ia;
+    if (m->wdtype < 0) m->wdtype = LUMI_DTYPE_F32;
+    m->finalized = true;
+    return LUMI_OK;
+}
+
+extern "C" void lumi_model_free(lumi_model* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    for (auto& kv : m->tensors) if (kv.second.p) cudaFree(kv.second.p);
+    for (void* p : m->owned) cudaFree(p);
+    delete m;
+}
+
+extern "C" int32_t lumi_model_info(const lumi_model* m, int64_t* o) {
+    if (!m || !o) return fail(LUMI_E_INVALID, "null argument to lumi_model_info");
+    const Config& c = m->cfg;
+    o[0] = c.d_model; o[1] = c.n_layers; o[2] = c.d_state; o[3] = c.n_heads; o[4] = c.head_dim(); o[5] = c.n_groups;
+    o[6] = c.vocab; o[7] = m->n_mamba; o[8] = m->n_attn; o[9] = c.in_proj_out(); o[10] = m->wdtype; o[11] = m->weight_bytes;
+    return LUMI_OK;
+}
+
+// ---- sessions ---------------------------------------------------------------------------------------
+static size_t state_h_per_seq(const Config& c) { return (size_t)c.n_heads * c.head_dim() * c.d_state; }
+
+extern "C" void lumi_session_free(lumi_session* s) {
+    if (!s) return;
+    cudaSetDevice(s->m->device);
+    if (s->stream) cudaStreamSynchronize(s->stream);
+    for (auto& g : s->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+    void* dev[] = {s->h, s->xprev, s->bprev, s->cum, s->kv_pool, s->page_table, s->kv_pos, s->x, s->proj, s->y32, s->logits,
+                   s->act_hi, s->act_lo, s->tok_cur, s->finished, s->out_len, s->ctl, s->gen_out, s->prompt_dev, s->gen_dump};
+    for (void* p : dev) if (p) cudaFree(p);
+    if (s->ctl_host) cudaFreeHost(s->ctl_host);
+    if (s->pin_tokens) cudaFreeHost(s->pin_tokens);
+    if (s->ev0) cudaEventDestroy(s->ev0);
+    if (s->ev1) cudaEventDestroy(s->ev1);
+    if (s->ev2) cudaEventDestroy(s->ev2);
+    if (s->stream) cudaStreamDestroy(s->stream);
+    delete s;
+}
+
+static int32_t session_alloc(lumi_session* s) {
+    const Config& c = s->m->cfg;
+    const size_t B = s->max_batch;
+    const int nm = s->m->n_mamba, na = s->m->n_attn;
+    LUMI_CUDA(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+    LUMI_CUDA(cudaEventCreate(&s->ev0));
+    LUMI_CUDA(cudaEventCreate(&s->ev1));
+    LUMI_CUDA(cudaEventCreate(&s->ev2));
+    if (nm > 0) {
+        LUMI_CUDA(cudaMalloc(&s->h, sizeof(float) * nm * B * state_h_per_seq(c)));
+        LUMI_CUDA(cudaMalloc(&s->xprev, sizeof(float) * nm * B * c.d_inner()));
+        LUMI_CUDA(cudaMalloc(&s->bprev, sizeof(float) * nm * B * c.n_heads * c.d_state));
+        LUMI_CUDA(cudaMalloc(&s->cum, sizeof(float) * nm * B * c.n_heads * (c.d_state / 2)));
+    }
+    if (na > 0) {
+        if (s->max_tokens_kv <= 0) return fail(LUMI_E_INVALID, "max_tokens_kv must be > 0 for a model with attention layers");
+        s->pages_per_seq = (s->max_tokens_kv + kPageTokens - 1) / kPageTokens;
+        const size_t esz = s->m->wdtype == LUMI_DTYPE_BF16 ? 2 : 4;
+        s->kv_layer_bytes = B * s->pages_per_seq * 2 * kPageTokens * (size_t)c.kv_dim() * esz;
+        LUMI_CUDA(cudaMalloc(&s->kv_pool, s->kv_layer_bytes * na));
+        LUMI_CUDA(cudaMalloc(&s->page_table, sizeof(int32_t) * B * s->pages_per_seq));
+        std::vector<int32_t> pt(B * s->pages_per_seq);
+        for (size_t i = 0; i < pt.size(); ++i) pt[i] = (int32_t)i;       // slot b owns pages [b*pps, (b+1)*pps)
+        LUMI_CUDA(cudaMemcpy(s->page_table, pt.data(), pt.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
+    }
+    LUMI_CUDA(cudaMalloc(&s->kv_pos, sizeof(int32_t) * B));
+    const size_t kmax = std::max<size_t>({(size_t)c.d_model, (size_t)c.d_inner(), na > 0 ? (size_t)c.mlp_dim() : 0});
+    const size_t pmax = std::max<size_t>({nm > 0 ? (size_t)c.in_proj_out() : 0, na > 0 ? (size_t)(c.d_model + 2 * c.kv_dim()) : 0,
+                                          na > 0 ? (size_t)(2 * c.mlp_dim()) : 0});
+    LUMI_CUDA(cudaMalloc(&s->x, sizeof(float) * B * c.d_model));
+    LUMI_CUDA(cudaMalloc(&s->proj, sizeof(float) * B * pmax));
+    LUMI_CUDA(cudaMalloc(&s->y32, sizeof(float) * B * kmax));
+    LUMI_CUDA(cudaMalloc(&s->logits, sizeof(float) * B * c.vocab));
+    if (s->m->wdtype == LUMI_DTYPE_BF16) {
+        // rows padded to a whole 128-row tile so TMA boxes never start outside the allocation
+        const size_t rows = (B + 127) / 128 * 128;
+        LUMI_CUDA(cudaMalloc(&s->act_hi, sizeof(__nv_bfloat16) * rows * kmax));
+        LUMI_CUDA(cudaMalloc(&s->act_lo, sizeof(__nv_bfloat16) * rows * kmax));
+        LUMI_CUDA(cudaMemset(s->act_hi, 0, sizeof(__nv_bfloat16) * rows * kmax));
+        LUMI_CUDA(cudaMemset(s->act_lo, 0, sizeof(__nv_bfloat16) * rows * kmax));
+    }
+    LUMI_CUDA(cudaMalloc(&s->tok_cur, sizeof(uint32_t) * B));
+    LUMI_CUDA(cudaMalloc(&s->finished, sizeof(int32_t) * B));
+    LUMI_CUDA(cudaMalloc(&s->out_len, sizeof(int32_t) * B));
+    LUMI_CUDA(cudaMalloc(&s->ctl, sizeof(StepCtl)));
+    LUMI_CUDA(cudaMallocHost(&s->ctl_host, sizeof(StepCtl)));
+    LUMI_CUDA(cudaMallocHost(&s->pin_tokens, sizeof(uint32_t) * B));
+    memset(s->ctl_host, 0, sizeof(StepCtl));
+    LUMI_CUDA(cudaMemset(s->tok_cur, 0, sizeof(uint32_t) * B));
+    return LUMI_OK;
+}
+
+extern "C" int32_t lumi_session_create(lumi_model* m, int32_t max_batch, int32_t max_tokens_kv, lumi_session** out) {
+    if (!m || !out) return fail(LUMI_E_INVALID, "null argument to lumi_session_create");
+    *out = nullptr;
+    if (!m->finalized) return fail(LUMI_E_INVALID, "lumi_model_finalize must succeed before a session is created");
+    if (max_batch <= 0) return fail(LUMI_E_INVALID, "max_batch must be > 0");
+    LUMI_CUDA(cudaSetDevice(m->device));
+    lumi_session* s = new lumi_session();
+    s->m = m;
+    s->max_batch = max_batch;
+    s->max_tokens_kv = max_tokens_kv;
+    int32_t st = session_alloc(s);
+    if (st == LUMI_OK) st = lumi_session_reset(s, nullptr, 0);
+    if (st != LUMI_OK) {
+        char keep[sizeof(lumi::g_err)];
+        memcpy(keep, lumi::g_err, sizeof(keep));
+        cudaGetLastError();
+        lumi_session_free(s);
+        memcpy(lumi::g_err, keep, sizeof(keep));
+        return st;
+    }
+    *out = s;
+    return LUMI_OK;
+}
+
+extern "C" int32_t lumi_session_reset(lumi_session* s, const int32_t* slots, int32_t n_slots) {
+    if (!s) return fail(LUMI_E_INVALID, "session is null");
+    const Config& c = s->m->cfg;
+    LUMI_CUDA(cudaSetDevice(s->m->device));
+    const size_t B = s->max_batch;
+    int32_t* dslots = nullptr;
+    int n = (int)B;
+    if (slots) {
+        if (n_slots <= 0) return LUMI_OK;
+        for (int i = 0; i < n_slots; ++i)
+            if (slots[i] < 0 || slots[i] >= s->max_batch) return fail(LUMI_E_INVALID, "slot %d out of range [0,%d)", slots[i], s->max_batch);
+        LUMI_CUDA(cudaMalloc(&dslots, sizeof(int32_t) * n_slots));
+        LUMI_CUDA(cudaMemcpyAsync(dslots, slots, sizeof(int32_t) * n_slots, cudaMemcpyHostToDevice, s->stream));
+        n = n_slots;
+    }
+    for (auto& L : s->m->layers) {
+        if (L.is_attn) continue;
+        const size_t l = L.kind_idx;
+        LUMI_CUDA(launch_state_reset(s->h + l * B * state_h_per_seq(c), s->xprev + l * B * c.d_inner(),
+                                     s->bprev + l * B * c.n_heads * c.d_state, s->cum + l * B * c.n_heads * (c.d_state / 2),
+                                     L.m.h_init, dslots, n, c.n_heads, c.head_dim(), c.d_state, s->stream));
+    }
+    if (!slots) {
+        LUMI_CUDA(cudaMemsetAsync(s->kv_pos, 0, sizeof(int32_t) * B, s->stream));
+    } else {
+        std::vector<int32_t> z(1, 0);
+        for (int i = 0; i < n_slots; ++i) LUMI_CUDA(cudaMemsetAsync(s->kv_pos + slots[i], 0, sizeof(int32_t), s->stream));
+    }
+    LUMI_CUDA(cudaStreamSynchronize(s->stream));
+    if (dslots) LUMI_CUDA(cudaFree(dslots));
+    return LUMI_OK;
+}
+
+extern "C" int32_t lumi_session_set_option(lumi_session* s, const char* name, int64_t value) {
+    if (!s || !name) return fail(LUMI_E_INVALID, "null argument to lumi_session_set_option");
+    const std::string n(name);
+    if (n == "gemm") { if (value < 0 || value > 2) return fail(LUMI_E_INVALID, "option gemm: 0, 1 or 2"); s->opt_gemm = (int)value; }
+    else if (n == "split_activations") s->opt_split = value ? 1 : 0;
+    else if (n == "graph") s->opt_graph = value ? 1 : 0;
+    else return fail(LUMI_E_INVALID, "unknown option '%s'", name);
+    for (auto& g : s->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);   // captured choices are stale
+    s->graphs.clear();
+    return LUMI_OK;
+}
+
+// ---- one step ---------------------------------------------------------------------------------------
+namespace {
+
+struct StepPlan {
+    lumi_session* s;
+    int B;
+    bool tc;         // tensor-core GEMMs (bf16 weights, batch > 8) or the weight-streaming GEMV
+    int64_t n = 0;   // launches enqueued
+};
+
+bool use_tc(const lumi_session* s, int B) {
+    const Config& c = s->m->cfg;
+    if (s->m->wdtype != LUMI_DTYPE_BF16 || s->opt_gemm == 1) return false;
+    if ((c.d_model % 64) || (c.d_inner() % 64) || (s->m->n_attn > 0 && (c.mlp_dim() % 64))) return false;
+    return s->opt_gemm == 2 || B > 8;
+}
+
+int32_t linear(StepPlan& p, const DevTensor& W, const float* in32, int K, float* out, int ldd, const float* residual,
+               const float* gamma, int act, int N) {
+    lumi_session* s = p.s;
+    const Config& c = s->m->cfg;
+    if (!p.tc) {
+        GemvArgs g{in32, K, W.p, W.dtype, out, ldd, residual, gamma, p.B, N, K, c.eps, act};
+        LUMI_CUDA(launch_gemv(g, s->stream));
+        p.n += 1;
+        return LUMI_OK;
+    }
+    // tensor-core path: the caller has already put the bf16 halves of the input into act_hi / act_lo
+    GemmArgs g{s->act_hi, s->opt_split ? s->act_lo : nullptr, (const __nv_bfloat16*)W.p, out, ldd, p.B, N, K,
+               residual != nullptr ? 1 : 0, &s->ctl->status};
+    LUMI_TRY(launch_gemm_tcgen05(g, s->stream));
+    p.n += 1;
+    return LUMI_OK;
+}
+
+int32_t mamba_block(StepPlan& p, const Layer& L) {
+    lumi_session* s = p.s;
+    const Config& c = s->m->cfg;
+    const size_t B = s->max_batch, l = L.kind_idx;
+    const int D = c.d_model, DI = c.d_inner(), R = c.in_proj_out();
+    if (p.tc) {
+        LUMI_CUDA(launch_norm_split(s->x, L.m.norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, D, c.eps, s->stream));
+        p.n += 1;
+    }
+    LUMI_TRY(linear(p, L.m.in_proj, s->x, D, s->proj, R, nullptr, L.m.norm_g, 0, R));
+    SsmArgs a{};
+    a.proj = s->proj; a.ldp = R;
+    a.bg = L.m.b_gamma; a.cg = L.m.c_gamma; a.bb = L.m.b_bias; a.cb = L.m.c_bias; a.dskip = L.m.d_skip; a.dtb = L.m.dt_bias;
+    a.h = s->h + l * B * state_h_per_seq(c);
+    a.xprev = s->xprev + l * B * DI;
+    a.bprev = s->bprev + l * B * c.n_heads * c.d_state;
+    a.cum = s->cum + l * B * c.n_heads * (c.d_state / 2);
+    a.y32 = p.tc ? nullptr : s->y32;
+    a.yhi = p.tc ? s->act_hi : nullptr;
+    a.ylo = (p.tc && s->opt_split) ? s->act_lo : nullptr;
+    a.B = p.B; a.H = c.n_heads; a.P = c.head_dim(); a.N = c.d_state; a.G = c.n_groups; a.eps = c.eps;
+    LUMI_CUDA(launch_ssm_step(a, s->stream));
+    p.n += 1;
+    LUMI_TRY(linear(p, L.m.out_proj, s->y32, DI, s->x, D, s->x, nullptr, 0, D));
+    return LUMI_OK;
+}
+
+int32_t attention_block(StepPlan& p, const Layer& L) {
+    lumi_session* s = p.s;
+    const Config& c = s->m->cfg;
+    const int D = c.d_model, KV = c.kv_dim(), Q = D + 2 * KV, MLP = c.mlp_dim();
+    if (p.tc) {
+        LUMI_CUDA(launch_norm_split(s->x, L.a.attn_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, D, c.eps, s->stream));
+        p.n += 1;
+    }
+    LUMI_TRY(linear(p, L.a.qkv, s->x, D, s->proj, Q, nullptr, L.a.attn_norm_g, 0, Q));
+    AttnArgs a{};
+    a.qkv = s->proj; a.ldq = Q;
+    a.pool = (char*)s->kv_pool + (size_t)L.kind_idx * s->kv_layer_bytes;
+    a.kv_is_f32 = s->m->wdtype == LUMI_DTYPE_BF16 ? 0 : 1;
+    a.page_table = s->page_table; a.pages_per_seq = s->pages_per_seq;
+    a.pos = s->kv_pos;
+    a.ctx32 = p.tc ? nullptr : s->y32;
+    a.chi = p.tc ? s->act_hi : nullptr;
+    a.clo = (p.tc && s->opt_split) ? s->act_lo : nullptr;
+    a.B = p.B; a.n_heads = c.attn_n_heads; a.kv_heads = c.attn_kv_heads; a.head_dim = c.attn_head_dim();
+    a.window = L.window; a.max_tokens = s->pages_per_seq * kPageTokens;
+    if (a.max_tokens > s->max_tokens_kv) a.max_tokens = s->max_tokens_kv;
+    a.rope_base = c.attn_rope_base;
+    a.ctl = s->ctl;
+    cudaError_t e = launch_attention_decode(a, s->stream);
+    if (e == cudaErrorInvalidValue) return fail(LUMI_E_UNSUPPORTED, "attention head_dim %d with %d query heads per kv head is not built", a.head_dim, a.n_heads / a.kv_heads);
+    LUMI_CUDA(e);
+    p.n += 1;
+    LUMI_TRY(linear(p, L.a.o, s->y32, D, s->x, D, s->x, nullptr, 0, D));
+    // sigmoid-gated MLP (model.rs:546-555)
+    if (p.tc) {
+        LUMI_CUDA(launch_norm_split(s->x, L.a.mlp_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, D, c.eps, s->stream));
+        LUMI_TRY(linear(p, L.a.gate_up, nullptr, D, s->proj, 2 * MLP, nullptr, nullptr, 0, 2 * MLP));
+        LUMI_CUDA(launch_gate_mul(s->proj, 2 * MLP, nullptr, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, MLP, s->stream));
+        p.n += 2;
+    } else {
+        LUMI_TRY(linear(p, L.a.gate_up, s->x, D, s->y32, MLP, nullptr, L.a.mlp_norm_g, 1, MLP));
+    }
+    LUMI_TRY(linear(p, L.a.down, s->y32, MLP, s->x, D, s->x, nullptr, 0, D));
+    return LUMI_OK;
+}
+
+// embedding -> blocks -> (final norm -> logits -> sample) -> advance
+int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches) {
+    const Config& c = s->m->cfg;
+    StepPlan p{s, B, use_tc(s, B)};
+    LUMI_CUDA(launch_embed(s->m->embedding.p, s->m->embedding.dtype, s->tok_cur, s->x, B, c.d_model, c.vocab, s->ctl, s->stream));
+    p.n += 1;
+    for (const Layer& L : s->m->layers) {
+        if (L.is_attn) LUMI_TRY(attention_block(p, L));
+        else LUMI_TRY(mamba_block(p, L));
+    }
+    if (with_head) {
+        if (p.tc) {
+            LUMI_CUDA(launch_norm_split(s->x, s->m->final_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, B, c.d_model, c.eps, s->stream));
+            p.n += 1;
+        }
+        LUMI_TRY(linear(p, s->m->embedding, s->x, c.d_model, s->logits, c.vocab, nullptr, s->m->final_norm_g, 0, c.vocab));
+        LUMI_CUDA(launch_sample(s->logits, B, c.vocab, s->ctl, s->tok_cur, s->finished, s->out_len, s->stream));
+        p.n += 1;
+    }
+    LUMI_CUDA(launch_advance_step(s->ctl, s->m->n_attn > 0 ? s->kv_pos : nullptr, B, with_head ? 1 : 0, s->stream));
+    p.n += 1;
+    *launches = p.n;
+    return LUMI_OK;
+}
+
+// Runs one step, through a captured graph when enabled.
+int32_t run_step(lumi_session* s, int B, bool with_head) {
+    if (!s->opt_graph) {
+        int64_t n = 0;
+        LUMI_TRY(enqueue_step(s, B, with_head, &n));
+        s->launches += n;
+        return LUMI_OK;
+    }
+    const int64_t key = (int64_t)B * 2 + (with_head ? 1 : 0);
+    auto it = s->graphs.find(key);
+    if (it == s->graphs.end()) {
+        GraphEntry ge;
+        cudaGraph_t graph = nullptr;
+        LUMI_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+        int32_t st = enqueue_step(s, B, with_head, &ge.launches);
+        cudaError_t e = cudaStreamEndCapture(s->stream, &graph);
+        if (st != LUMI_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+        LUMI_CUDA(e);
+        e = cudaGraphInstantiate(&ge.exec, graph, 0);
+        cudaGraphDestroy(graph);
+        LUMI_CUDA(e);
+        it = s->graphs.emplace(key, ge).first;
+    }
+    LUMI_CUDA(cudaGraphLaunch(it->second.exec, s->stream));
+    s->launches += it->second.launches;
+    return LUMI_OK;
+}
+
+int32_t check_status(lumi_session* s) {
+    const int st = s->ctl_host->status;
+    if (st & STATUS_TIMEOUT) return fail(LUMI_E_TIMEOUT, "a bounded device-side wait expired inside the tensor-core GEMM");
+    if (st & STATUS_BAD_TOKEN) return fail(LUMI_E_TOKEN, "a token id was >= vocab_size (%d)", s->m->cfg.vocab);
+    if (st & STATUS_KV_FULL) return fail(LUMI_E_KV_FULL, "attention cache capacity (%d tokens per sequence) exceeded", s->max_tokens_kv);
+    return LUMI_OK;
+}
+
+int32_t check_batch(lumi_session* s, int batch) {
+    if (!s) return fail(LUMI_E_INVALID, "session is null");
+    if (batch <= 0 || batch > s->max_batch) return fail(LUMI_E_INVALID, "batch %d outside [1, %d]", batch, s->max_batch);
+    return LUMI_OK;
+}
+
+void fill_ctl(lumi_session* s, int batch, const lumi_sampling* sp) {
+    StepCtl& c = *s->ctl_host;
+    memset(&c, 0, sizeof(c));
+    c.batch = batch;
+    if (sp) {
+        c.temperature = sp->temperature;
+        c.top_k = sp->top_k;
+        c.seed_lo = (uint32_t)(sp->seed & 0xffffffffu);
+        c.seed_hi = (uint32_t)(sp->seed >> 32);
+        c.eos_id = sp->eos_id;
+        c.ignore_eos = sp->ignore_eos;
+    }
+}
+
+int32_t push_ctl(lumi_session* s) {
+    LUMI_CUDA(cudaMemcpyAsync(s->ctl, s->ctl_host, sizeof(StepCtl), cudaMemcpyHostToDevice, s->stream));
+    return LUMI_OK;
+}
+int32_t pull_ctl(lumi_session* s) {
+    LUMI_CUDA(cudaMemcpyAsync(s->ctl_host, s->ctl, sizeof(StepCtl), cudaMemcpyDeviceToHost, s->stream));
+    return LUMI_OK;
+}
+
+template <typename T>
+int32_t grow(T*& p, size_t& cap, size_t need_elems) {
+    if (need_elems <= cap) return LUMI_OK;
+    if (p) LUMI_CUDA(cudaFree(p));
+    p = nullptr; cap = 0;
+    LUMI_CUDA(cudaMalloc(&p, need_elems * sizeof(T)));
+    cap = need_elems;
+    return LUMI_OK;
+}
+
+// prompt[batch][T] (host) -> prompt_dev[T][batch]
+int32_t upload_prompt(lumi_session* s, const uint32_t* tokens, int batch, int T) {
+    LUMI_TRY(grow(s->prompt_dev, s->prompt_cap, (size_t)batch * T));
+    std::vector<uint32_t> tr((size_t)batch * T);
+    for (int b = 0; b < batch; ++b)
+        for (int t = 0; t < T; ++t) tr[(size_t)t * batch + b] = tokens[(size_t)b * T + t];
+    LUMI_CUDA(cudaMemcpyAsync(s->prompt_dev, tr.data(), tr.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, s->stream));
+    LUMI_CUDA(cudaStreamSynchronize(s->stream));     // tr goes out of scope
+    return LUMI_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t lumi_prefill(lumi_session* s, const uint32_t* tokens, int32_t batch, int32_t T, float* last_logits) {
+    LUMI_TRY(check_batch(s, batch));
+    if (!tokens || T <= 0) return fail(LUMI_E_INVALID, "prefill needs tokens and T > 0");
+    LUMI_CUDA(cudaSetDevice(s->m->device));
+    LUMI_TRY(upload_prompt(s, tokens, batch, T));
+    fill_ctl(s, batch, nullptr);
+    s->ctl_host->prompt = s->prompt_dev;
+    s->ctl_host->prompt_len = T;
+    LUMI_TRY(push_ctl(s));
+    for (int t = 0; t < T; ++t) LUMI_TRY(run_step(s, batch, last_logits != nullptr && t == T - 1));
+    if (last_logits)
+        LUMI_CUDA(cudaMemcpyAsync(last_logits, s->logits, sizeof(float) * batch * s->m->cfg.vocab, cudaMemcpyDeviceToHost, s->stream));
+    LUMI_TRY(pull_ctl(s));
+    LUMI_CUDA(cudaStreamSynchronize(s->stream));
+    return check_status(s);
+}
+
+extern "C" int32_t lumi_decode_step(lumi_session* s, const uint32_t* in_tokens, int32_t batch, const lumi_sampling* sp,
+                                    int32_t step, uint32_t* out_tokens, float* logits_out) {
+    LUMI_TRY(check_batch(s, batch));
+    if (!in_tokens) return fail(LUMI_E_INVALID, "in_tokens is null");
+    LUMI_CUDA(cudaSetDevice(s->m->device));
+    fill_ctl(s, batch, sp);
+    s->ctl_host->step = step;
+    LUMI_TRY(push_ctl(s));
+    memcpy(s->pin_tokens, in_tokens, sizeof(uint32_t) * batch);
+    LUMI_CUDA(cudaMemcpyAsync(s->tok_cur, s->pin_tokens, sizeof(uint32_t) * batch, cudaMemcpyHostToDevice, s->stream));
+    LUMI_TRY(run_step(s, batch, true));
+    LUMI_CUDA(cudaMemcpyAsync(s->pin_tokens, s->tok_cur, sizeof(uint32_t) * batch, cudaMemcpyDeviceToHost, s->stream));
+    if (logits_out)
+        LUMI_CUDA(cudaMemcpyAsync(logits_out, s->logits, sizeof(float) * batch * s->m->cfg.vocab, cudaMemcpyDeviceToHost, s->stream));
+    LUMI_TRY(pull_ctl(s));
+    LUMI_CUDA(cudaStreamSynchronize(s->stream));
+    if (out_tokens) memcpy(out_tokens, s->pin_tokens, sizeof(uint32_t) * batch);
+    return check_status(s);
+}
+
+extern "C" int32_t lumi_generate(lumi_session* s, const uint32_t* prompts, int32_t batch, int32_t T, int32_t n_new,
+                                 const lumi_sampling* sp, uint32_t* out_tokens, int32_t* out_lens, float* logits_dump,
+                                 lumi_stats* stats) {
+    LUMI_TRY(check_batch(s, batch));
+    if (!prompts || T <= 0 || n_new < 0 || !sp) return fail(LUMI_E_INVALID, "generate needs prompts, T > 0, n_new >= 0 and sampling parameters");
+    LUMI_CUDA(cudaSetDevice(s->m->device));
+    const int V = s->m->cfg.vocab;
+    LUMI_TRY(upload_prompt(s, prompts, batch, T));
+    LUMI_TRY(grow(s->gen_out, s->gen_out_cap, (size_t)std::max(1, n_new) * batch));
+    if (logits_dump) LUMI_TRY(grow(s->gen_dump, s->gen_dump_cap, (size_t)std::max(1, n_new) * batch * V));
+    fill_ctl(s, batch, sp);
+    StepCtl& c = *s->ctl_host;
+    c.prompt = s->prompt_dev;
+    c.prompt_len = T;
+    c.record = 1;
+    c.want_dump = logits_dump ? 1 : 0;
+    c.out_tokens = s->gen_out;
+    c.dump = s->gen_dump;
+    LUMI_TRY(push_ctl(s));
+    LUMI_CUDA(cudaMemsetAsync(s->finished, 0, sizeof(int32_t) * batch, s->stream));
+    LUMI_CUDA(cudaMemsetAsync(s->out_len, 0, sizeof(int32_t) * batch, s->stream));
+    const int64_t l0 = s->launches;
+    LUMI_CUDA(cudaEventRecord(s->ev0, s->stream));
+    // main.rs:121-125: the prompt goes through forward_step token by token; the last position's
+    // logits give generated token 0
+    for (int t = 0; t < T; ++t) LUMI_TRY(run_step(s, batch, n_new > 0 && t == T - 1));
+    LUMI_CUDA(cudaEventRecord(s->ev1, s->stream));
+    for (int i = 1; i < n_new; ++i) LUMI_TRY(run_step(s, batch, true));      // main.rs:136-170
+    LUMI_CUDA(cudaEventRecord(s->ev2, s->stream));
+    std::vector<uint32_t> tmp((size_t)n_new * batch);
+    if (n_new > 0) LUMI_CUDA(cudaMemcpyAsync(tmp.data(), s->gen_out, tmp.size() * sizeof(uint32_t), cudaMemcpyDeviceToHost, s->stream));
+    if (logits_dump && n_new > 0)
+        LUMI_CUDA(cudaMemcpyAsync(logits_dump, s->gen_dump, sizeof(float) * (size_t)n_new * batch * V, cudaMemcpyDeviceToHost, s->stream));
+    if (out_lens) LUMI_CUDA(cudaMemcpyAsync(out_lens, s->out_len, sizeof(int32_t) * batch, cudaMemcpyDeviceToHost, s->stream));
+    LUMI_TRY(pull_ctl(s));
+    LUMI_CUDA(cudaStreamSynchronize(s->stream));
+    if (out_tokens)
+        for (int i = 0; i < n_new; ++i)
+            for (int b = 0; b < batch; ++b) out_tokens[(size_t)b * n_new + i] = tmp[(size_t)i * batch + b];
+    if (stats) {
+        memset(stats, 0, sizeof(*stats));
+        stats->prompt_tokens = (int64_t)batch * T;
+        stats->decode_tokens = (int64_t)batch * std::max(0, n_new - 1);
+        LUMI_CUDA(cudaEventElapsedTime(&stats->ms_prefill, s->ev0, s->ev1));
+        LUMI_CUDA(cudaEventElapsedTime(&stats->ms_decode, s->ev1, s->ev2));
+        stats->kernel_launches = s->launches - l0;
+        const Config& cf = s->m->cfg;
+        const int64_t per_seq = (int64_t)s->m->n_mamba * 2 * 4 *
+                                ((int64_t)state_h_per_seq(cf) + cf.d_inner() + cf.n_heads * cf.d_state + cf.n_heads * (cf.d_state / 2));
+        stats->bytes_per_step = s->m->weight_bytes + (int64_t)batch * per_seq;
+    }
+    return check_status(s);
+}
+
+extern "C" int32_t lumi_decode_loop_device(lumi_session* s, int32_t batch, int32_t n_steps, float* ms_out, int64_t* launches_out) {
+    LUMI_TRY(check_batch(s, batch));
+    if (n_steps <= 0) return fail(LUMI_E_INVALID, "n_steps must be > 0");
+    LUMI_CUDA(cudaSetDevice(s->m->device));
+    lumi_sampling sp{};
+    sp.ignore_eos = 1;
+    fill_ctl(s, batch, &sp);
+    LUMI_TRY(push_ctl(s));
+    const int64_t l0 = s->launches;
+    LUMI_CUDA(cudaEventRecord(s->ev0, s->stream));
+    for (int i = 0; i < n_steps; ++i) LUMI_TRY(run_step(s, batch, true));
+    LUMI_CUDA(cudaEventRecord(s->ev1, s->stream));
+    LUMI_TRY(pull_ctl(s));
+    LUMI_CUDA(cudaStreamSynchronize(s->stream));
+    float ms = 0.f;
+    LUMI_CUDA(cudaEventElapsedTime(&ms, s->ev0, s->ev1));
+    if (ms_out) *ms_out = ms;
+    if (launches_out) *launches_out = s->launches - l0;
+    return check_status(s);
+}
+
+extern "C" int32_t lumi_session_read_state(lumi_session* s, int32_t slot, int32_t layer, float* h, float* x_prev, float* b_prev,
+                                           float* cum_angle) {
+    if (!s) return fail(LUMI_E_INVALID, "session is null");
+    const Config& c = s->m->cfg;
+    if (slot < 0 || slot >= s->max_batch) return fail(LUMI_E_INVALID, "slot %d out of range", slot);
+    if (layer < 0 || layer >= c.n_layers || s->m->layers[layer].is_attn) return fail(LUMI_E_INVALID, "layer %d is not a Mamba layer", layer);
+    LUMI_CUDA(cudaSetDevice(s->m->device));
+    const size_t B = s->max_batch, l = s->m->layers[layer].kind_idx;
+    const size_t nh = state_h_per_seq(c), nx = c.d_inner(), nb = (size_t)c.n_heads * c.d_state, nc = (size_t)c.n_heads * (c.d_state / 2);
+    LUMI_CUDA(cudaStreamSynchronize(s->stream));
+    if (h) LUMI_CUDA(cudaMemcpy(h, s->h + (l * B + slot) * nh, nh * 4, cudaMemcpyDeviceToHost));
+    if (x_prev) LUMI_CUDA(cudaMemcpy(x_prev, s->xprev + (l * B + slot) * nx, nx * 4, cudaMemcpyDeviceToHost));
+    if (b_prev) LUMI_CUDA(cudaMemcpy(b_prev, s->bprev + (l * B + slot) * nb, nb * 4, cudaMemcpyDeviceToHost));
+    if (cum_angle) LUMI_CUDA(cudaMemcpy(cum_angle, s->cum + (l * B + slot) * nc, nc * 4, cudaMemcpyDeviceToHost));
+    return LUMI_OK;
+}
+
+extern "C" int32_t lumi_debug_run_block(lumi_session* s, int32_t layer, float* x, int32_t batch) {
+    LUMI_TRY(check_batch(s, batch));
+    const Config& c = s->m->cfg;
+    if (!x || layer < 0 || layer >= c.n_layers) return fail(LUMI_E_INVALID, "bad layer or null x");
+    LUMI_CUDA(cudaSetDevice(s->m->device));
+    fill_ctl(s, batch, nullptr);
+    LUMI_TRY(push_ctl(s));
+    LUMI_CUDA(cudaMemcpyAsync(s->x, x, sizeof(float) * batch * c.d_model, cudaMemcpyHostToDevice, s->stream));
+    StepPlan p{s, batch, use_tc(s, batch)};
+    const Layer& L = s->m->layers[layer];
+    if (L.is_attn) {
+        LUMI_TRY(attention_block(p, L));
+        LUMI_CUDA(launch_advance_step(s->ctl, s->kv_pos, batch, 0, s->stream));
+    } else {
+        LUMI_TRY(mamba_block(p, L));
+    }
+    LUMI_CUDA(cudaMemcpyAsync(x, s->x, sizeof(float) * batch * c.d_model, cudaMemcpyDeviceToHost, s->stream));
+    LUMI_TRY(pull_ctl(s));
+    LUMI_CUDA(cudaStreamSynchronize(s->stream));
+    return check_status(s);
+}
+
+// ---- single kernels over caller-owned device pointers ---------------------------------------------------
+extern "C" int32_t lumi_k_gemm_bf16_tcgen05(uint64_t a_hi, uint64_t a_lo, uint64_t w, uint64_t d, int32_t M, int32_t N, int32_t K,
+                                            int32_t ldd, int32_t accumulate, uint64_t stream) {
+    if (!a_hi || !w || !d) return fail(LUMI_E_INVALID, "null device pointer");
+    GemmArgs g{(const __nv_bfloat16*)a_hi, (const __nv_bfloat16*)a_lo, (const __nv_bfloat16*)w, (float*)d, ldd, M, N, K, accumulate, nullptr};
+    return launch_gemm_tcgen05(g, (cudaStream_t)stream);
+}
+
+extern "C" int32_t lumi_k_gemv(uint64_t a_f32, uint64_t w, int32_t w_dtype, uint64_t d, uint64_t residual, uint64_t norm_gamma,
+                               int32_t M, int32_t N, int32_t K, uint64_t stream) {
+    if (!a_f32 || !w || !d || M <= 0 || N <= 0 || K <= 0) return fail(LUMI_E_INVALID, "bad argument to lumi_k_gemv");
+    if (K % 8) return fail(LUMI_E_UNSUPPORTED, "K must be a multiple of 8");
+    GemvArgs g{(const float*)a_f32, K, (const void*)w, w_dtype, (float*)d, N, (const float*)residual, (const float*)norm_gamma, M, N, K, 1e-5f, 0};
+    LUMI_CUDA(launch_gemv(g, (cudaStream_t)stream));
+    return LUMI_OK;
+}

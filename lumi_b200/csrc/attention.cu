@@ -1,0 +1,226 @@
+// Single-token GQA attention over a paged KV cache, replacing AttentionBlock::forward_step's
+// cache append + softmax(q K^T / sqrt(d)) V (inference/src/model.rs:508-538, KvCache::append
+// :133-152).  One CTA per (sequence, KV head) serves all query heads of that group, so K and V
+// are read once.  The sliding window of the reference (keep the last `window` tokens) is a ring:
+// token t lives in slot t % window.  Optional rotary embedding (extension, off by default).
+#include "internal.h"
+
+#include <cmath>
+
+namespace lumi {
+
+namespace {
+
+template <typename T> struct KvIo;
+template <> struct KvIo<float> {
+    __device__ static float ld(const float* p) { return *p; }
+    __device__ static void st(float* p, float v) { *p = v; }
+};
+template <> struct KvIo<__nv_bfloat16> {
+    __device__ static float ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    __device__ static void st(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+__device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+    hi = __float2bfloat16_rn(v);
+    lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+
+// Page layout: [page][K|V][kPageTokens][kv_dim]
+template <typename KT>
+__device__ __forceinline__ KT* kv_ptr(KT* pool, const int32_t* pt, int slot, int sel, int kv_dim) {
+    const int page = pt[slot / kPageTokens];
+    return pool + (((size_t)page * 2 + sel) * kPageTokens + (slot % kPageTokens)) * kv_dim;
+}
+
+template <typename KT, int HD, int HPK>
+__global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) {
+    extern __shared__ float smem[];
+    float* qs = smem;                      // [HD][HPK]   (rotated q, head-interleaved)
+    float* red = qs + HD * HPK;            // [4 warps][HPK * HD] cross-warp reduction / scratch
+    float* sc = red + 4 * HPK * HD;        // [HPK][T]
+    __shared__ float hmax[HPK], hsum[HPK];
+
+    const int b = blockIdx.y, kvh = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int D = a.n_heads * HD, KV = a.kv_heads * HD;
+    const float* q = a.qkv + (size_t)b * a.ldq + (size_t)kvh * HPK * HD;
+    const float* kn = a.qkv + (size_t)b * a.ldq + D + kvh * HD;
+    const float* vn = kn + KV;
+    const int pos = a.pos[b];
+    const int32_t* pt = a.page_table + (size_t)b * a.pages_per_seq;
+    const int cap = a.window > 0 ? min(a.window, a.max_tokens) : a.max_tokens;
+    int T, slot_new;
+    if (a.window > 0 && a.window <= a.max_tokens) { slot_new = pos % a.window; T = min(pos + 1, a.window); }
+    else { slot_new = pos; T = pos + 1; }
+    if (slot_new >= cap || T > cap) {      // cache capacity exceeded: report, write nothing
+        if (tid == 0) atomicOr(&a.ctl->status, STATUS_KV_FULL);
+        return;
+    }
+
+    // rotary embedding on interleaved pairs at the absolute position (extension), then stage q and
+    // append the new K / V row
+    for (int i = tid; i < HPK * HD / 2; i += 128) {
+        const int hq = i / (HD / 2), pr = i % (HD / 2);
+        float q0 = q[hq * HD + 2 * pr], q1 = q[hq * HD + 2 * pr + 1];
+        if (a.rope_base > 0.f) {
+            float inv = powf(a.rope_base, -(float)(2 * pr) / (float)HD);
+            float ang = __fmul_rn((float)pos, inv);
+            float sa, ca;
+            sincosf(ang, &sa, &ca);
+            float r0 = __fsub_rn(__fmul_rn(ca, q0), __fmul_rn(sa, q1));
+            float r1 = __fadd_rn(__fmul_rn(sa, q0), __fmul_rn(ca, q1));
+            q0 = r0; q1 = r1;
+        }
+        qs[(2 * pr) * HPK + hq] = q0;
+        qs[(2 * pr + 1) * HPK + hq] = q1;
+    }
+    for (int pr = tid; pr < HD / 2; pr += 128) {
+        float k0 = kn[2 * pr], k1 = kn[2 * pr + 1];
+        if (a.rope_base > 0.f) {
+            float inv = powf(a.rope_base, -(float)(2 * pr) / (float)HD);
+            float ang = __fmul_rn((float)pos, inv);
+            float sa, ca;
+            sincosf(ang, &sa, &ca);
+            float r0 = __fsub_rn(__fmul_rn(ca, k0), __fmul_rn(sa, k1));
+            float r1 = __fadd_rn(__fmul_rn(sa, k0), __fmul_rn(ca, k1));
+            k0 = r0; k1 = r1;
+        }
+        KT* kd = kv_ptr(pool, pt, slot_new, 0, KV) + kvh * HD;
+        KT* vd = kv_ptr(pool, pt, slot_new, 1, KV) + kvh * HD;
+        KvIo<KT>::st(kd + 2 * pr, k0);
+        KvIo<KT>::st(kd + 2 * pr + 1, k1);
+        KvIo<KT>::st(vd + 2 * pr, vn[2 * pr]);
+        KvIo<KT>::st(vd + 2 * pr + 1, vn[2 * pr + 1]);
+    }
+    __syncthreads();
+
+    // scores: one cached token per thread
+    const float scale = (float)(1.0 / sqrt((double)HD));            // model.rs:530
+    float lmax[HPK];
+#pragma unroll
+    for (int hq = 0; hq < HPK; ++hq) lmax[hq] = -INFINITY;
+    for (int t = tid; t < T; t += 128) {
+        const KT* kr = kv_ptr(pool, pt, t, 0, KV) + kvh * HD;
+        float acc[HPK];
+#pragma unroll
+        for (int hq = 0; hq < HPK; ++hq) acc[hq] = 0.f;
+#pragma unroll 8
+        for (int d = 0; d < HD; ++d) {
+            const float kv = KvIo<KT>::ld(kr + d);
+#pragma unroll
+            for (int hq = 0; hq < HPK; ++hq) acc[hq] = fmaf(qs[d * HPK + hq], kv, acc[hq]);
+        }
+#pragma unroll
+        for (int hq = 0; hq < HPK; ++hq) {
+            float s = __fmul_rn(acc[hq], scale);                    // model.rs:532
+            sc[hq * T + t] = s;
+            lmax[hq] = fmaxf(lmax[hq], s);
+        }
+    }
+    // block max per head
+#pragma unroll
+    for (int hq = 0; hq < HPK; ++hq) {
+        float v = lmax[hq];
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+        if (lane == 0) red[warp * HPK + hq] = v;
+    }
+    __syncthreads();
+    if (tid < HPK) hmax[tid] = fmaxf(fmaxf(red[tid], red[HPK + tid]), fmaxf(red[2 * HPK + tid], red[3 * HPK + tid]));
+    __syncthreads();
+    float lsum[HPK];
+#pragma unroll
+    for (int hq = 0; hq < HPK; ++hq) lsum[hq] = 0.f;
+    for (int t = tid; t < T; t += 128) {
+#pragma unroll
+        for (int hq = 0; hq < HPK; ++hq) {
+            float e = expf(__fsub_rn(sc[hq * T + t], hmax[hq]));    // model.rs:535
+            sc[hq * T + t] = e;
+            lsum[hq] += e;
+        }
+    }
+    __syncthreads();   // red is reused below
+#pragma unroll
+    for (int hq = 0; hq < HPK; ++hq) {
+        float v = lsum[hq];
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) red[warp * HPK + hq] = v;
+    }
+    __syncthreads();
+    if (tid < HPK) hsum[tid] = (red[tid] + red[HPK + tid]) + (red[2 * HPK + tid] + red[3 * HPK + tid]);
+    __syncthreads();
+
+    // context: warp w takes tokens t = w (mod 4); lane owns dims lane, lane + 32, ...
+    constexpr int DPL = (HD + 31) / 32;
+    float ctx[HPK][DPL];
+#pragma unroll
+    for (int hq = 0; hq < HPK; ++hq)
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) ctx[hq][j] = 0.f;
+    for (int t = warp; t < T; t += 4) {
+        const KT* vr = kv_ptr(pool, pt, t, 1, KV) + kvh * HD;
+        float vv[DPL];
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) vv[j] = (lane + 32 * j < HD) ? KvIo<KT>::ld(vr + lane + 32 * j) : 0.f;
+#pragma unroll
+        for (int hq = 0; hq < HPK; ++hq) {
+            const float p = __fdiv_rn(sc[hq * T + t], hsum[hq]);
+#pragma unroll
+            for (int j = 0; j < DPL; ++j) ctx[hq][j] = fmaf(p, vv[j], ctx[hq][j]);
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int hq = 0; hq < HPK; ++hq)
+#pragma unroll
+        for (int j = 0; j < DPL; ++j)
+            if (lane + 32 * j < HD) red[warp * HPK * HD + hq * HD + lane + 32 * j] = ctx[hq][j];
+    __syncthreads();
+    for (int i = tid; i < HPK * HD; i += 128) {
+        float v = (red[i] + red[HPK * HD + i]) + (red[2 * HPK * HD + i] + red[3 * HPK * HD + i]);
+        const size_t o = (size_t)b * D + (size_t)kvh * HPK * HD + i;
+        if (a.ctx32) a.ctx32[o] = v;
+        if (a.chi) {
+            __nv_bfloat16 hh, ll;
+            split_bf16(v, hh, ll);
+            a.chi[o] = hh;
+            if (a.clo) a.clo[o] = ll;
+        }
+    }
+}
+
+template <typename KT, int HD, int HPK>
+cudaError_t launch_t(const AttnArgs& a, cudaStream_t st) {
+    const int cap = a.window > 0 ? (a.window < a.max_tokens ? a.window : a.max_tokens) : a.max_tokens;
+    size_t smem = sizeof(float) * ((size_t)HD * HPK + 4 * HPK * HD + (size_t)HPK * cap);
+    auto kern = attn_decode_kernel<KT, HD, HPK>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    dim3 grid(a.kv_heads, a.B);
+    kern<<<grid, 128, smem, st>>>(a, reinterpret_cast<KT*>(a.pool));
+    return cudaGetLastError();
+}
+
+template <typename KT>
+cudaError_t launch_kt(const AttnArgs& a, cudaStream_t st) {
+    const int hpk = a.n_heads / a.kv_heads;
+#define LUMI_ATT(HD_, HPK_) if (a.head_dim == HD_ && hpk == HPK_) return launch_t<KT, HD_, HPK_>(a, st);
+    LUMI_ATT(64, 4) LUMI_ATT(64, 1) LUMI_ATT(64, 2) LUMI_ATT(64, 8)
+    LUMI_ATT(32, 1) LUMI_ATT(32, 2) LUMI_ATT(32, 4) LUMI_ATT(32, 8)
+    LUMI_ATT(128, 1) LUMI_ATT(128, 2) LUMI_ATT(128, 4) LUMI_ATT(128, 8)
+#undef LUMI_ATT
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+// The cache element type follows the weights: fp32 weights keep an fp32 cache (so fp32 parity is
+// not limited by cache rounding), bf16 weights a bf16 cache.  `pool` carries the type by flag.
+cudaError_t launch_attention_decode(const AttnArgs& a, cudaStream_t st) {
+    if (a.kv_is_f32) return launch_kt<float>(a, st);
+    return launch_kt<__nv_bfloat16>(a, st);
+}
+
+}  // namespace lumi

@@ -1,0 +1,308 @@
+// bf16 x bf16 -> fp32 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM),
+// operands staged by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast).
+//
+//   D[M][N] (+)= A[M][K] * W[N][K]^T        A = activations (batch rows), W = weights as stored
+//
+// replacing the Linear layers of the reference at batch >= 9 with bf16 weights
+// (inference/src/model.rs:299,373,504-506,542,550-553,800; the trainer's cuBLAS call sites
+// training/src/native_trainer.rs:220,262,545-548).  Each fp32 activation can be fed as the sum of
+// two bf16 values (hi + lo): two MMAs per weight tile into the same accumulator, which keeps ~16
+// mantissa bits of the activation while the weight tile is loaded once.
+//
+// One CTA computes one 128 x BN tile.  Warp 0: TMA producer.  Warp 1: TMEM allocation + MMA issue
+// (one elected lane).  Warps 2-5: epilogue (tcgen05.ld -> registers -> global).
+// Every wait on an mbarrier is bounded by a wall-clock limit; on expiry the kernel records
+// STATUS_TIMEOUT, drains its own copies, frees its TMEM and returns.
+#include "internal.h"
+
+#include <cuda.h>
+
+namespace lumi {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                       // 64 bf16 = 128 bytes = one swizzle atom row
+constexpr int kSmemBudget = 196608;          // bytes of pipeline stages
+constexpr uint64_t kWaitLimitNs = 500ull * 1000 * 1000;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit expired.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);        // start address, bits [0,14)
+    d |= (uint64_t)1 << 16;                             // leading byte offset (unused with swizzle), bits [16,30)
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset, bits [32,46)
+    d |= (uint64_t)1 << 46;                             // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                             // layout: SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN, bool SPLIT>
+struct Tile {
+    static constexpr int A_BYTES = BM * BK * 2;                 // 16 KiB
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE = A_BYTES * (SPLIT ? 2 : 1) + B_BYTES;
+    static constexpr int STAGES = kSmemBudget / STAGE;
+    static constexpr int SMEM = STAGES * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <int BN, bool SPLIT>
+__global__ void __launch_bounds__(192, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
+            const __grid_constant__ CUtensorMap map_w, float* __restrict__ D, int ldd, int M, int N, int K,
+            int accumulate, int32_t* status) {
+    using T = Tile<BN, SPLIT>;
+    constexpr int S = T::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(base + S * T::STAGE);
+    uint64_t* empty_bar = full_bar + S;
+    uint64_t* tmem_full = empty_bar + S;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const int num_kb = K / BK;
+
+    // a wait that expired in an earlier CTA of this launch: do not start new work
+    if (status != nullptr && (*reinterpret_cast<volatile int32_t*>(status) & STATUS_TIMEOUT)) return;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    bool timed_out = false;
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % S;
+                const uint32_t ph = (uint32_t)(kb / S) & 1u;
+                if (!mbar_wait(&empty_bar[s], ph ^ 1u)) { timed_out = true; break; }
+                uint8_t* st = base + s * T::STAGE;
+                mbar_expect_tx(&full_bar[s], (uint32_t)T::STAGE);
+                tma_load_2d(st, &map_ahi, &full_bar[s], kb * BK, m0);
+                if (SPLIT) tma_load_2d(st + T::A_BYTES, &map_alo, &full_bar[s], kb * BK, m0);
+                tma_load_2d(st + T::A_BYTES * (SPLIT ? 2 : 1), &map_w, &full_bar[s], kb * BK, n0);
+                issued = kb + 1;
+            }
+            if (timed_out) {
+                // drain: wait (bounded) for the copies this thread issued and nobody may consume
+                for (int kb = max(0, issued - S); kb < issued; ++kb)
+                    mbar_wait(&full_bar[kb % S], (uint32_t)(kb / S) & 1u);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % S;
+                const uint32_t ph = (uint32_t)(kb / S) & 1u;
+                if (!mbar_wait(&full_bar[s], ph)) { timed_out = true; break; }
+                tc_fence_after();
+                const uint32_t a_hi = smem_u32(base + s * T::STAGE);
+                const uint32_t b_addr = a_hi + T::A_BYTES * (SPLIT ? 2 : 1);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    // 16 bf16 = 32 bytes along K inside the 128-byte swizzled row
+                    umma_bf16(tmem_base, make_smem_desc(a_hi + k * 32), make_smem_desc(b_addr + k * 32), idesc,
+                              (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                if (SPLIT) {
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_bf16(tmem_base, make_smem_desc(a_hi + T::A_BYTES + k * 32), make_smem_desc(b_addr + k * 32), idesc, 1u);
+                }
+                umma_commit(&empty_bar[s]);      // arrives when these MMAs have finished reading the stage
+            }
+            umma_commit(tmem_full);              // arrives when every MMA issued so far has completed
+            if (timed_out) mbar_wait(tmem_full, 0);
+        }
+    } else {
+        const int q = warp & 3;                  // TMEM lane quarter this warp may read
+        if (!mbar_wait(tmem_full, 0)) timed_out = true;
+        tc_fence_after();
+        if (!timed_out) {
+            const int row = m0 + q * 32 + lane;
+            const bool vec_ok = (ldd & 3) == 0;
+#pragma unroll 1
+            for (int cb = 0; cb < BN / 32; ++cb) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 32), r);
+                const int col0 = n0 + cb * 32;
+                if (row < M && col0 < N) {
+                    float* dp = D + (size_t)row * ldd + col0;
+                    if (vec_ok && col0 + 32 <= N) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                            if (accumulate) {
+                                float4 o = *reinterpret_cast<const float4*>(dp + 4 * j);
+                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                            }
+                            *reinterpret_cast<float4*>(dp + 4 * j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (col0 + j < N) {
+                                float v = __uint_as_float(r[j]);
+                                if (accumulate) v += dp[j];
+                                dp[j] = v;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (timed_out && status != nullptr) atomicOr(status, STATUS_TIMEOUT);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+// [rows][K] bf16 row-major, box = 64 (K) x box_rows, 128-byte swizzle, out-of-range reads give zeros
+int32_t make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LUMI_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows %d, K %d)", (int)r, rows, K);
+    return LUMI_OK;
+}
+
+template <int BN, bool SPLIT>
+int32_t launch_t(const GemmArgs& a, cudaStream_t st) {
+    using T = Tile<BN, SPLIT>;
+    CUtensorMap mh, ml, mw;
+    LUMI_TRY(make_map(&mh, a.a_hi, a.M, a.K, BM));
+    LUMI_TRY(make_map(&ml, SPLIT ? a.a_lo : a.a_hi, a.M, a.K, BM));
+    LUMI_TRY(make_map(&mw, a.w, a.N, a.K, BN));
+    auto kern = gemm_kernel<BN, SPLIT>;
+    LUMI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
+    dim3 grid((a.N + BN - 1) / BN, (a.M + BM - 1) / BM);
+    kern<<<grid, 192, T::SMEM, st>>>(mh, ml, mw, a.d, a.ldd, a.M, a.N, a.K, a.accumulate, a.status_word);
+    LUMI_CUDA(cudaGetLastError());
+    return LUMI_OK;
+}
+
+}  // namespace
+
+int32_t gemm_tcgen05_init() {
+    if (g_encode != nullptr) return LUMI_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    LUMI_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (fn == nullptr || q != cudaDriverEntryPointSuccess)
+        return fail(LUMI_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    return LUMI_OK;
+}
+
+int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st) {
+    if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.K % BK) != 0)
+        return fail(LUMI_E_UNSUPPORTED, "tcgen05 GEMM needs K %% 64 == 0 (M %d N %d K %d)", a.M, a.N, a.K);
+    if ((reinterpret_cast<uintptr_t>(a.a_hi) | reinterpret_cast<uintptr_t>(a.w) | reinterpret_cast<uintptr_t>(a.a_lo)) & 15)
+        return fail(LUMI_E_INVALID, "tcgen05 GEMM operands must be 16-byte aligned");
+    LUMI_TRY(gemm_tcgen05_init());
+    const bool split = a.a_lo != nullptr;
+    // wide tiles when the problem has enough of them to fill the GPU
+    const long tiles256 = (long)((a.N + 255) / 256) * ((a.M + BM - 1) / BM);
+    if (tiles256 >= 148) return split ? launch_t<256, true>(a, st) : launch_t<256, false>(a, st);
+    return split ? launch_t<128, true>(a, st) : launch_t<128, false>(a, st);
+}
+
+}  // namespace lumi

@@ -1,0 +1,239 @@
+// Internal structures shared by the translation units of liblumi_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/lumi_b200.h"
+
+namespace lumi {
+
+// ---- errors -----------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int32_t fail(int32_t code, const char* fmt, ...);
+
+#define LUMI_CUDA(expr)                                                                            \
+    do {                                                                                           \
+        cudaError_t _e = (expr);                                                                   \
+        if (_e != cudaSuccess)                                                                     \
+            return ::lumi::fail(_e == cudaErrorMemoryAllocation ? LUMI_E_NOMEM : LUMI_E_CUDA,      \
+                                "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+    } while (0)
+
+#define LUMI_TRY(expr)                    \
+    do {                                  \
+        int32_t _s = (expr);              \
+        if (_s != LUMI_OK) return _s;     \
+    } while (0)
+
+// ---- configuration (ModelConfig of the reference, inference/src/model.rs:20-86) -----------------
+struct Config {
+    int d_model = 0, n_layers = 0, d_state = 0, expand = 0, n_heads = 0, n_groups = 0, vocab = 0, max_seq_len = 0;
+    int attention_interval = 0, attn_n_heads = 16, attn_kv_heads = 4, attn_mlp_expand = 4;
+    std::vector<int> attn_window_sizes, attention_layers;
+    bool byte_level = false;
+    int attn_mlp_dim = 0;        // extension: 0 = attn_mlp_expand * d_model
+    float attn_rope_base = 0.f;  // extension: 0 = no rotary embedding in attention
+    float eps = 1e-5f;           // the reference hard-codes 1e-5 (model.rs:97) and has no norm_eps key
+
+    int d_inner() const { return expand * d_model; }
+    int head_dim() const { return d_inner() / n_heads; }
+    int bc() const { return n_groups * d_state; }
+    int in_proj_out() const { return 2 * d_inner() + 2 * bc() + 3 * n_heads + n_heads * d_state / 2; }
+    int attn_head_dim() const { return d_model / attn_n_heads; }
+    int kv_dim() const { return attn_kv_heads * attn_head_dim(); }
+    int mlp_dim() const { return attn_mlp_dim > 0 ? attn_mlp_dim : attn_mlp_expand * d_model; }
+    bool is_attention_layer(int i) const;
+    int n_attn_layers() const;
+    int attn_window_size(int attn_idx) const {
+        return attn_idx < (int)attn_window_sizes.size() ? attn_window_sizes[attn_idx] : 0;
+    }
+};
+int32_t parse_config(const char* json, Config& out);
+
+// ---- device tensors -----------------------------------------------------------------------------
+struct DevTensor {
+    void* p = nullptr;
+    int dtype = LUMI_DTYPE_F32;
+    int64_t rows = 0, cols = 0;   // rank-1 tensors: rows = 1
+    size_t bytes = 0;
+};
+
+struct MambaW {
+    const float* norm_g = nullptr;
+    DevTensor in_proj, out_proj;
+    const float *b_gamma = nullptr, *c_gamma = nullptr, *b_bias = nullptr, *c_bias = nullptr;
+    const float *d_skip = nullptr, *dt_bias = nullptr, *h_init = nullptr;   // h_init may stay null (zeros)
+};
+struct AttnW {
+    const float *attn_norm_g = nullptr, *mlp_norm_g = nullptr;
+    DevTensor qkv, o, gate_up, down;     // q|k|v and gate|up rows concatenated at finalize
+};
+struct Layer {
+    bool is_attn = false;
+    int kind_idx = 0;     // index among the Mamba layers, or among the attention layers
+    int window = 0;
+    MambaW m;
+    AttnW a;
+};
+
+}  // namespace lumi
+
+struct lumi_model {
+    lumi::Config cfg;
+    int device = 0;
+    bool finalized = false;
+    int wdtype = -1;                                  // dtype of rank-2 tensors (all must agree)
+    std::map<std::string, lumi::DevTensor> tensors;   // by name without the "item." prefix
+    std::vector<void*> owned;                         // extra device allocations made at finalize
+    std::vector<lumi::Layer> layers;
+    lumi::DevTensor embedding;
+    const float* final_norm_g = nullptr;
+    int n_mamba = 0, n_attn = 0;
+    int64_t weight_bytes = 0;                         // bytes of weights one decode step reads
+};
+
+namespace lumi {
+
+// Device-resident control block read by the kernels of a step, so that a captured CUDA graph stays
+// valid from call to call: the host rewrites these fields, not kernel arguments.
+struct StepCtl {
+    int32_t step;            // index of the token being generated (Philox counter, output row)
+    int32_t status;          // 0 ok; kernels OR in LUMI_STATUS_* bits
+    int32_t record;          // 1: write sampled tokens to out_tokens[step][b] and track eos
+    int32_t want_dump;       // 1: copy logits to dump[step][b][:]
+    float temperature;
+    int32_t top_k;
+    uint32_t seed_lo, seed_hi;
+    uint32_t eos_id;
+    int32_t ignore_eos;
+    uint32_t* out_tokens;    // [n_new][batch]
+    float* dump;             // [n_new][batch][vocab]
+    int32_t batch;
+    int32_t prompt_len;      // prefill: tokens per sequence still to come from `prompt`
+    int32_t prompt_pos;      // next prompt position; >= prompt_len means "consume tok_cur"
+    int32_t pad;
+    const uint32_t* prompt;  // [prompt_len][batch]
+};
+enum { STATUS_BAD_TOKEN = 1, STATUS_KV_FULL = 2, STATUS_TIMEOUT = 4 };
+
+struct GraphEntry {
+    cudaGraphExec_t exec = nullptr;
+    int64_t launches = 0;
+};
+
+}  // namespace lumi
+
+struct lumi_session {
+    lumi_model* m = nullptr;
+    int max_batch = 0, max_tokens_kv = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;
+    // options
+    int opt_gemm = 0, opt_split = 1, opt_graph = 1;
+    // state, per Mamba layer l: base + l * max_batch * per-sequence size
+    float *h = nullptr, *xprev = nullptr, *bprev = nullptr, *cum = nullptr;
+    // attention cache: pool of pages of kPageTokens tokens, [n_attn][pages][2][kPageTokens][kv_dim] bf16
+    void* kv_pool = nullptr;           // element type follows the weights (fp32 or bf16)
+    size_t kv_layer_bytes = 0;
+    int32_t* page_table = nullptr;     // [max_batch][pages_per_seq]
+    int32_t* kv_pos = nullptr;         // [max_batch] tokens consumed so far (absolute position)
+    int pages_per_seq = 0;
+    // activations
+    float *x = nullptr, *proj = nullptr, *y32 = nullptr, *logits = nullptr;
+    __nv_bfloat16 *act_hi = nullptr, *act_lo = nullptr;
+    uint32_t *tok_cur = nullptr;       // [max_batch] tokens the next step consumes
+    int32_t *finished = nullptr, *out_len = nullptr;   // [max_batch]
+    lumi::StepCtl* ctl = nullptr;      // device
+    lumi::StepCtl* ctl_host = nullptr; // pinned mirror
+    uint32_t* pin_tokens = nullptr;    // pinned staging [max_batch]
+    // grow-only buffers for lumi_generate outputs
+    uint32_t* gen_out = nullptr; size_t gen_out_cap = 0;
+    uint32_t* prompt_dev = nullptr; size_t prompt_cap = 0;
+    float* gen_dump = nullptr; size_t gen_dump_cap = 0;
+    std::map<int64_t, lumi::GraphEntry> graphs;
+    int64_t launches = 0;              // kernels enqueued outside graphs since last reset of the counter
+    int64_t launches_per_step = 0;
+};
+
+namespace lumi {
+
+constexpr int kPageTokens = 64;
+
+// ---- kernel launchers (kernels.cu) --------------------------------------------------------------
+// All take the stream to enqueue on and return a cudaError_t from the launch.
+struct GemvArgs {
+    const float* A; int lda;         // [M][K] fp32
+    const void* W; int w_dtype;      // [N][K]
+    float* D; int ldd;               // [M][N]
+    const float* R;                  // residual, same layout as D, or null
+    const float* gamma;              // RMSNorm weight applied to rows of A first, or null
+    int M, N, K;
+    float eps;
+    int act;                         // 0 none; 1: D = sigmoid(W_gate a) * (W_up a), W = [gate rows | up rows], N = rows of each
+};
+cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);
+
+cudaError_t launch_embed(const void* emb, int dtype, const uint32_t* tok_cur, float* x, int B, int D, int vocab,
+                         StepCtl* ctl, cudaStream_t st);
+// x[B][D] fp32 -> RMSNorm(gamma) -> bf16 hi (+ lo if lo != null); gamma null = plain split
+cudaError_t launch_norm_split(const float* x, const float* gamma, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int D,
+                              float eps, cudaStream_t st);
+
+struct SsmArgs {
+    const float* proj; int ldp;      // [B][in_proj_out]
+    const float *bg, *cg, *bb, *cb, *dskip, *dtb;
+    float *h, *xprev, *bprev, *cum;  // this layer's slices
+    float* y32;                      // [B][d_inner] fp32, or null
+    __nv_bfloat16 *yhi, *ylo;        // [B][d_inner] bf16 halves, or null
+    int B, H, P, N, G;
+    float eps;
+};
+cudaError_t launch_ssm_step(const SsmArgs& a, cudaStream_t st);
+bool ssm_shape_supported(int P, int N);
+
+cudaError_t launch_state_reset(float* h, float* xprev, float* bprev, float* cum, const float* h_init, const int32_t* slots,
+                               int n_slots, int H, int P, int N, cudaStream_t st);
+
+cudaError_t launch_sample(const float* logits, int B, int V, StepCtl* ctl, uint32_t* tok_cur, int32_t* finished,
+                          int32_t* out_len, cudaStream_t st);
+cudaError_t launch_advance_step(StepCtl* ctl, int32_t* kv_pos, int B, int sampled, cudaStream_t st);
+
+// ---- attention (attention.cu) ---------------------------------------------------------------------
+struct AttnArgs {
+    const float* qkv; int ldq;       // [B][d_model + 2 kv_dim] fp32 (q | k | v) of the current token
+    void* pool;                      // this layer's page pool (fp32 or bf16 elements)
+    int kv_is_f32;
+    const int32_t* page_table; int pages_per_seq;
+    const int32_t* pos;              // [B] absolute position of the current token
+    float* ctx32;                    // [B][d_model] fp32 or null
+    __nv_bfloat16 *chi, *clo;        // bf16 halves or null
+    int B, n_heads, kv_heads, head_dim, window, max_tokens;
+    float rope_base;
+    StepCtl* ctl;
+};
+cudaError_t launch_attention_decode(const AttnArgs& a, cudaStream_t st);
+
+
+// ---- tcgen05 GEMM (gemm_tcgen05.cu) ---------------------------------------------------------------
+// D[M][N] (+)= A[M][K] W[N][K]^T ; A as bf16 hi (+ lo) halves, W bf16, fp32 accumulate and output.
+// epi: 0 store, 1 add to existing D (residual), 2 sigmoid-gate: D[m][n] = sigmoid(acc[n]) * acc[n + N] is NOT
+// done here (see gate kernel).  status_word: device int that receives STATUS_TIMEOUT if a bounded wait gives up.
+struct GemmArgs {
+    const __nv_bfloat16 *a_hi, *a_lo;   // [M][K]
+    const __nv_bfloat16* w;             // [N][K]
+    float* d; int ldd;
+    int M, N, K;
+    int accumulate;
+    int32_t* status_word;               // may be null
+};
+int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st);   // returns LUMI_* status
+int32_t gemm_tcgen05_init();                                        // resolves the driver entry point
+
+cudaError_t launch_gate_mul(const float* gu, int ld, float* out32, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int mlp,
+                            cudaStream_t st);
+
+}  // namespace lumi

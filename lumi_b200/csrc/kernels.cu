@@ -1,0 +1,620 @@
+// Bandwidth-bound kernels of the decode step: embedding gather, RMSNorm, weight-streaming GEMV,
+// the fused Mamba-3 state update, and sampling.
+//
+// Arithmetic follows the reference's CPU branch (inference/src/model.rs:296-375) operation by
+// operation; where the reference rounds after every multiply and add (Rust never contracts to FMA),
+// the round-to-nearest intrinsics below are used so the compiler cannot contract either.  Dot
+// products use FMA with a fixed summation order (per-lane strided partials, xor-shuffle tree), so
+// results are bit-stable from run to run.
+#include "internal.h"
+
+#include <cfloat>
+#include <cmath>
+
+namespace lumi {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// model.rs:12-17, :830-832 and candle's silu, in the reference's operation order
+__device__ __forceinline__ float sigmoid_ref(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
+__device__ __forceinline__ float softplus_ref(float x) { return logf(__fadd_rn(expf(x), 1.0f)); }
+__device__ __forceinline__ float silu_ref(float x) { return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))); }
+__device__ __forceinline__ float rms_scale(float sumsq, int n, float eps) {
+    float mean = __fmul_rn(sumsq, (float)(1.0 / (double)n));
+    return __frcp_rn(__fsqrt_rn(__fadd_rn(mean, eps)));
+}
+
+__device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+    hi = __float2bfloat16_rn(v);
+    lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+
+// ---- 16-byte weight loads ------------------------------------------------------------------------
+template <typename WT> struct WLoad;
+template <> struct WLoad<float> {
+    static constexpr int E = 4;
+    __device__ static __forceinline__ void load(const float* p, float (&w)[4]) {
+        float4 v = __ldg(reinterpret_cast<const float4*>(p));
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    }
+};
+template <> struct WLoad<__nv_bfloat16> {
+    static constexpr int E = 8;
+    __device__ static __forceinline__ void load(const __nv_bfloat16* p, float (&w)[8]) {
+        uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            w[2 * i] = __uint_as_float(u[i] << 16);
+            w[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+        }
+    }
+};
+
+// ---- embedding gather (model.rs:772-773) -----------------------------------------------------------
+template <typename WT>
+__global__ void embed_kernel(const WT* __restrict__ emb, const uint32_t* __restrict__ tok_cur, float* __restrict__ x,
+                             int D, int vocab, StepCtl* ctl) {
+    const int b = blockIdx.x;
+    // during prefill the token comes from the uploaded prompt, afterwards from the last sampled one
+    const int pp = ctl->prompt_pos;
+    uint32_t t = (pp < ctl->prompt_len) ? ctl->prompt[(size_t)pp * ctl->batch + b] : tok_cur[b];
+    if (t >= (uint32_t)vocab) {          // reported to the host; the row read stays in bounds
+        if (threadIdx.x == 0) atomicOr(&ctl->status, STATUS_BAD_TOKEN);
+        t = 0;
+    }
+    constexpr int E = WLoad<WT>::E;
+    const WT* row = emb + (size_t)t * D;
+    for (int c = threadIdx.x; c < D / E; c += blockDim.x) {
+        float w[E];
+        WLoad<WT>::load(row + c * E, w);
+#pragma unroll
+        for (int e = 0; e < E; ++e) x[(size_t)b * D + c * E + e] = w[e];
+    }
+}
+
+// ---- RMSNorm to bf16 halves for the tensor-core GEMMs (model.rs:100-106) ---------------------------
+__global__ void __launch_bounds__(256) norm_split_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                                         __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
+                                                         int D, float eps) {
+    __shared__ float red[8];
+    const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* xr = x + (size_t)b * D;
+    float r = 1.0f;
+    if (gamma) {
+        float s = 0.f;
+        for (int i = threadIdx.x; i < D; i += 256) s = fmaf(xr[i], xr[i], s);
+        s = warp_sum(s);
+        if (lane == 0) red[warp] = s;
+        __syncthreads();
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += red[w];
+        r = rms_scale(t, D, eps);
+    }
+    for (int i = threadIdx.x; i < D; i += 256) {
+        float v = xr[i];
+        if (gamma) v = __fmul_rn(__fmul_rn(v, r), gamma[i]);
+        __nv_bfloat16 h, l;
+        split_bf16(v, h, l);
+        hi[(size_t)b * D + i] = h;
+        if (lo) lo[(size_t)b * D + i] = l;
+    }
+}
+
+// ---- weight-streaming GEMV for small batches ---------------------------------------------------------
+// D[m][n] = sum_k A'[m][k] W[n][k] (+ R[m][n]),  A' = RMSNorm(A; gamma) when gamma != null.
+// One warp owns RPW output rows at a time and streams them with 16-byte loads (lane c reads chunk
+// c, c+32, ...); the NB activation rows of the batch tile sit in shared memory.  Per-lane partial
+// sums run in ascending k, then a 5-step xor-shuffle tree.
+template <typename WT, int NB, int RPW, int ACT>
+__global__ void __launch_bounds__(256) gemv_kernel(const float* __restrict__ A, int lda, const WT* __restrict__ W,
+                                                   float* __restrict__ D, int ldd, const float* __restrict__ R,
+                                                   const float* __restrict__ gamma, int M, int N, int K, float eps) {
+    extern __shared__ float4 gemv_smem4[];
+    float* xs = reinterpret_cast<float*>(gemv_smem4);
+    constexpr int E = WLoad<WT>::E;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * NB;
+    const int nb = min(NB, M - m0);
+    const int K4 = K >> 2;
+    for (int i = threadIdx.x; i < NB * K4; i += 256) {
+        int b = i / K4, k4 = i - b * K4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (b < nb) v = *reinterpret_cast<const float4*>(A + (size_t)(m0 + b) * lda + 4 * k4);
+        reinterpret_cast<float4*>(xs)[i] = v;
+    }
+    __syncthreads();
+    if (gamma != nullptr) {
+        for (int b = warp; b < nb; b += 8) {
+            float* xr = xs + b * K;
+            float s = 0.f;
+            for (int k = lane; k < K; k += 32) s = fmaf(xr[k], xr[k], s);
+            s = warp_sum(s);
+            float r = rms_scale(s, K, eps);
+            for (int k = lane; k < K; k += 32) xr[k] = __fmul_rn(__fmul_rn(xr[k], r), gamma[k]);
+        }
+        __syncthreads();
+    }
+    // with ACT == 1 each logical output n pairs weight rows n (gate) and n + N (up)
+    constexpr int NR = (ACT == 1) ? 2 * RPW : RPW;
+    const int row0 = (blockIdx.x * 8 + warp) * RPW;
+    if (row0 >= N) return;
+    const WT* wp[NR];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+        int row = min(row0 + r, N - 1);
+        wp[r] = W + (size_t)row * K;
+        if constexpr (ACT == 1) wp[RPW + r] = W + (size_t)(row + N) * K;
+    }
+    float acc[NR][NB];
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+#pragma unroll
+        for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
+    const int KC = K / E;
+#pragma unroll 2
+    for (int c = lane; c < KC; c += 32) {
+        float w[NR][E];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) WLoad<WT>::load(wp[r] + c * E, w[r]);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            float xv[E];
+#pragma unroll
+            for (int q = 0; q < E / 4; ++q) {
+                float4 v = *reinterpret_cast<const float4*>(xs + b * K + c * E + 4 * q);
+                xv[4 * q] = v.x; xv[4 * q + 1] = v.y; xv[4 * q + 2] = v.z; xv[4 * q + 3] = v.w;
+            }
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+#pragma unroll
+                for (int e = 0; e < E; ++e) acc[r][b] = fmaf(w[r][e], xv[e], acc[r][b]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+#pragma unroll
+        for (int b = 0; b < NB; ++b) acc[r][b] = warp_sum(acc[r][b]);
+    if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+            int row = row0 + r;
+            if (row >= N) break;
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                if (b >= nb) break;
+                float v = acc[r][b];
+                if constexpr (ACT == 1) v = __fmul_rn(sigmoid_ref(v), acc[RPW + r][b]);     // model.rs:550-552
+                size_t o = (size_t)(m0 + b) * ldd + row;
+                if (R != nullptr) v = __fadd_rn(v, R[o]);
+                D[o] = v;
+            }
+        }
+    }
+}
+
+// ---- fused Mamba-3 decode step ---------------------------------------------------------------------
+// One warp per (sequence, head).  Prologue: BCNorm statistics over all n_groups*d_state elements
+// (block-wide), per-head scalars, DD-RoPE with one rotation pair per lane, staged in shared memory.
+// Main loop: the head's [P][N] fp32 state tile as consecutive float4 (lane-contiguous, coalesced);
+// prev_bx is rebuilt from its rank-1 factors x_prev (x) B_prev, which are what is kept in HBM.
+template <int P, int N>
+struct SsmSmem {
+    float bt[N], ct[N], xa[P], xp[P], gate[P], yout[P];
+};
+
+template <int P, int N>
+__global__ void __launch_bounds__(256, 2) ssm_step_kernel(SsmArgs a) {
+    __shared__ SsmSmem<P, N> sm_all[8];
+    __shared__ float red[2][8];
+    const int b = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hpb = blockDim.x >> 5;
+    const int h = blockIdx.x * hpb + warp;
+    const int H = a.H, DI = H * P, BC = a.G * N, HN = N / 2;
+    const float* pr = a.proj + (size_t)b * a.ldp;
+    const float* Bp = pr + 2 * DI;
+    const float* Cp = Bp + BC;
+    const float* dt = Cp + BC;
+    const float* lam_raw = dt + H;
+    const float* dda = dt + 2 * H;
+    const float* theta = dt + 3 * H;
+
+    // BCNorm statistics (model.rs:311-312: the norm runs over the whole bc vector)
+    float sb = 0.f, sc = 0.f;
+    for (int i = threadIdx.x; i < BC; i += blockDim.x) {
+        float v = Bp[i];
+        sb = fmaf(v, v, sb);
+        v = Cp[i];
+        sc = fmaf(v, v, sc);
+    }
+    sb = warp_sum(sb);
+    sc = warp_sum(sc);
+    if (lane == 0) { red[0][warp] = sb; red[1][warp] = sc; }
+    __syncthreads();
+    if (h >= H) return;
+    float tb = 0.f, tc = 0.f;
+    for (int w = 0; w < hpb; ++w) { tb += red[0][w]; tc += red[1][w]; }
+    const float rb = rms_scale(tb, BC, a.eps), rc = rms_scale(tc, BC, a.eps);
+
+    SsmSmem<P, N>& sm = sm_all[warp];
+    const size_t bh = (size_t)b * H + h;
+
+    // per-head scalars (model.rs:307, 314-317, 355-359)
+    const float dtp = softplus_ref(__fadd_rn(dt[h], a.dtb[h]));
+    float av = -softplus_ref(dda[h]);
+    av = fminf(fmaxf(av, -1e6f), -1e-4f);
+    const float abar = expf(__fmul_rn(av, dtp));
+    const float lam = sigmoid_ref(lam_raw[h]);
+    const float oml = __fadd_rn(__fmul_rn(lam, -1.0f), 1.0f);
+    const float c2 = __fmul_rn(abar, oml);
+    const int g = h / (H / a.G);
+
+    // previous B~ for this lane's four state columns, read before it is overwritten below
+    constexpr int CG = N / 4;              // lanes sharing one state row
+    const int c = lane % CG, r0 = lane / CG;
+    const float4 bpq = reinterpret_cast<const float4*>(a.bprev + bh * N)[c];
+
+    // DD-RoPE (model.rs:338-350): lane k rotates pair (2k, 2k+1) of the normalised B and C
+    const float PI_F = 3.14159265358979323846f;
+    const float TWO_PI = __fmul_rn(2.0f, PI_F);
+    for (int k = lane; k < HN; k += 32) {
+        float angle = __fmul_rn(tanhf(theta[h * HN + k]), PI_F);
+        float cu = a.cum[bh * HN + k];
+        cu = fmodf(__fadd_rn(cu, __fmul_rn(dtp, angle)), TWO_PI);
+        a.cum[bh * HN + k] = cu;
+        float sa, ca;
+        sincosf(cu, &sa, &ca);
+        const int i0 = g * N + 2 * k;
+        float b0 = __fadd_rn(__fmul_rn(__fmul_rn(Bp[i0], rb), a.bg[i0]), a.bb[i0]);
+        float b1 = __fadd_rn(__fmul_rn(__fmul_rn(Bp[i0 + 1], rb), a.bg[i0 + 1]), a.bb[i0 + 1]);
+        float c0 = __fadd_rn(__fmul_rn(__fmul_rn(Cp[i0], rc), a.cg[i0]), a.cb[i0]);
+        float c1 = __fadd_rn(__fmul_rn(__fmul_rn(Cp[i0 + 1], rc), a.cg[i0 + 1]), a.cb[i0 + 1]);
+        sm.bt[2 * k] = __fsub_rn(__fmul_rn(ca, b0), __fmul_rn(sa, b1));
+        sm.bt[2 * k + 1] = __fadd_rn(__fmul_rn(sa, b0), __fmul_rn(ca, b1));
+        sm.ct[2 * k] = __fsub_rn(__fmul_rn(ca, c0), __fmul_rn(sa, c1));
+        sm.ct[2 * k + 1] = __fadd_rn(__fmul_rn(sa, c0), __fmul_rn(ca, c1));
+    }
+    for (int p = lane; p < P; p += 32) {
+        sm.xa[p] = silu_ref(pr[h * P + p]);                 // model.rs:310
+        sm.xp[p] = a.xprev[bh * P + p];
+        sm.gate[p] = silu_ref(pr[DI + h * P + p]);          // model.rs:370
+    }
+    __syncwarp();
+
+    const float4 bq = reinterpret_cast<const float4*>(sm.bt)[c];
+    const float4 cq = reinterpret_cast<const float4*>(sm.ct)[c];
+    constexpr int RS = 32 / CG;            // state rows covered by one warp-wide float4 access
+    constexpr int IT = P / RS;             // accesses per tile
+    constexpr int CH = IT < 16 ? IT : 16;  // accesses kept in registers at once
+    float4* h4 = reinterpret_cast<float4*>(a.h + bh * (size_t)(P * N));
+#pragma unroll 1
+    for (int i0 = 0; i0 < IT; i0 += CH) {
+        float4 t[CH];
+#pragma unroll
+        for (int i = 0; i < CH; ++i) t[i] = h4[(i0 + i) * 32 + lane];
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+            const int row = r0 + (i0 + i) * RS;
+            const float xv = sm.xa[row], xpv = sm.xp[row];
+            float part;
+            {   // model.rs:354-366 : h = (abar*h + (abar*(1-lam))*prev_bx) + lam*bx ; y = sum_s C~[s] h[s]
+                float nh;
+                nh = __fadd_rn(__fadd_rn(__fmul_rn(abar, t[i].x), __fmul_rn(c2, __fmul_rn(xpv, bpq.x))), __fmul_rn(lam, __fmul_rn(xv, bq.x)));
+                t[i].x = nh; part = __fmul_rn(cq.x, nh);
+                nh = __fadd_rn(__fadd_rn(__fmul_rn(abar, t[i].y), __fmul_rn(c2, __fmul_rn(xpv, bpq.y))), __fmul_rn(lam, __fmul_rn(xv, bq.y)));
+                t[i].y = nh; part = fmaf(cq.y, nh, part);
+                nh = __fadd_rn(__fadd_rn(__fmul_rn(abar, t[i].z), __fmul_rn(c2, __fmul_rn(xpv, bpq.z))), __fmul_rn(lam, __fmul_rn(xv, bq.z)));
+                t[i].z = nh; part = fmaf(cq.z, nh, part);
+                nh = __fadd_rn(__fadd_rn(__fmul_rn(abar, t[i].w), __fmul_rn(c2, __fmul_rn(xpv, bpq.w))), __fmul_rn(lam, __fmul_rn(xv, bq.w)));
+                t[i].w = nh; part = fmaf(cq.w, nh, part);
+            }
+            h4[(i0 + i) * 32 + lane] = t[i];
+#pragma unroll
+            for (int o = CG / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (c == 0) sm.yout[row] = part;
+        }
+    }
+    __syncwarp();
+    for (int p = lane; p < P; p += 32) {
+        float xv = sm.xa[p];
+        float yv = __fadd_rn(sm.yout[p], __fmul_rn(a.dskip[h], xv));     // model.rs:367-368
+        yv = __fmul_rn(yv, sm.gate[p]);                                  // model.rs:370
+        const size_t o = (size_t)b * DI + h * P + p;
+        if (a.y32) a.y32[o] = yv;
+        if (a.yhi) {
+            __nv_bfloat16 hh, ll;
+            split_bf16(yv, hh, ll);
+            a.yhi[o] = hh;
+            if (a.ylo) a.ylo[o] = ll;
+        }
+        a.xprev[bh * P + p] = xv;
+    }
+    for (int s = lane; s < N; s += 32) a.bprev[bh * N + s] = sm.bt[s];
+}
+
+// h <- h_init broadcast over head_dim (model.rs:744-748); factors and angles <- 0 (:751-752)
+__global__ void state_reset_kernel(float* h, float* xprev, float* bprev, float* cum, const float* __restrict__ h_init,
+                                   const int32_t* __restrict__ slots, int H, int P, int N) {
+    const int slot = slots ? slots[blockIdx.x] : blockIdx.x;
+    const size_t per = (size_t)H * P * N;
+    for (size_t i = threadIdx.x; i < per; i += blockDim.x) {
+        int n = i % N;
+        int hh = i / ((size_t)P * N);
+        h[(size_t)slot * per + i] = h_init ? h_init[hh * N + n] : 0.f;
+    }
+    for (int i = threadIdx.x; i < H * P; i += blockDim.x) xprev[(size_t)slot * H * P + i] = 0.f;
+    for (int i = threadIdx.x; i < H * N; i += blockDim.x) bprev[(size_t)slot * H * N + i] = 0.f;
+    for (int i = threadIdx.x; i < H * N / 2; i += blockDim.x) cum[(size_t)slot * H * (N / 2) + i] = 0.f;
+}
+
+// ---- sampling (main.rs:142-148, 197-209) -----------------------------------------------------------
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1,
+                                              uint32_t& o0) {
+#pragma unroll
+    for (int i = 0; i < 10; ++i) {
+        uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+        c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+    o0 = c0;
+}
+
+struct BestPair { float v; int i; };
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+__device__ BestPair block_argmax(float v, int i, BestPair* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (better(ov, oi, v, i)) { v = ov; i = oi; }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();                       // red may still be read from a previous round
+    if (lane == 0) { red[warp].v = v; red[warp].i = i; }
+    __syncthreads();
+    BestPair r = red[0];
+    for (int w = 1; w < nw; ++w) if (better(red[w].v, red[w].i, r.v, r.i)) r = red[w];
+    return r;
+}
+
+constexpr int kMaxTopK = 256;
+
+// One block per sequence.  Greedy: argmax with the lowest index on ties.  Otherwise temperature
+// softmax over the top-k survivors (or the whole vocabulary) and the walk over the cumulative
+// distribution in vocabulary order.
+__global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ logits, int V, StepCtl* ctl,
+                                                      uint32_t* tok_cur, int32_t* finished, int32_t* out_len) {
+    __shared__ BestPair red[32];
+    __shared__ float top_v[kMaxTopK];
+    __shared__ int top_i[kMaxTopK];
+    __shared__ float chunk_sum[1024];
+    __shared__ int result;
+    const int b = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    const float* lg = logits + (size_t)b * V;
+    const int step = ctl->step;
+    if (ctl->want_dump) {
+        float* d = ctl->dump + ((size_t)step * ctl->batch + b) * V;
+        for (int i = tid; i < V; i += nt) d[i] = lg[i];
+    }
+    const float temperature = ctl->temperature;
+    int chosen;
+    if (temperature <= 0.f) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int i = tid; i < V; i += nt) { float v = lg[i]; if (better(v, i, bv, bi)) { bv = v; bi = i; } }
+        BestPair r = block_argmax(bv, bi, red);
+        chosen = r.i;
+    } else {
+        const float inv_t = (float)(1.0 / (double)temperature);
+        uint32_t rw;
+        philox4x32_10((uint32_t)step, (uint32_t)b, 0u, 0u, ctl->seed_lo, ctl->seed_hi, rw);
+        const float r = (float)(rw >> 8) * (1.0f / 16777216.0f);
+        int k = ctl->top_k;
+        if (k > kMaxTopK) k = kMaxTopK;
+        if (k > 0 && k < V) {
+            // k rounds of block-wide argmax over the not-yet-taken entries
+            for (int round = 0; round < k; ++round) {
+                float bv = -INFINITY; int bi = 0x7fffffff;
+                for (int i = tid; i < V; i += nt) {
+                    float v = lg[i];
+                    bool taken = false;
+                    if (round > 0) {
+                        // an entry is taken iff it is at least as good as the last survivor
+                        float lv = top_v[round - 1]; int li = top_i[round - 1];
+                        taken = !better(lv, li, v, i);
+                    }
+                    if (!taken && better(v, i, bv, bi)) { bv = v; bi = i; }
+                }
+                BestPair rr = block_argmax(bv, bi, red);
+                if (tid == 0) { top_v[round] = rr.v; top_i[round] = rr.i; }
+                __syncthreads();
+            }
+            if (tid == 0) {
+                // survivors into vocabulary order (insertion sort, k <= 256)
+                for (int a1 = 1; a1 < k; ++a1) {
+                    float v = top_v[a1]; int i = top_i[a1]; int j = a1 - 1;
+                    while (j >= 0 && top_i[j] > i) { top_v[j + 1] = top_v[j]; top_i[j + 1] = top_i[j]; --j; }
+                    top_v[j + 1] = v; top_i[j + 1] = i;
+                }
+                float mx = -INFINITY;
+                for (int j = 0; j < k; ++j) { top_v[j] = __fmul_rn(top_v[j], inv_t); mx = fmaxf(mx, top_v[j]); }
+                float sum = 0.f;
+                for (int j = 0; j < k; ++j) { top_v[j] = expf(__fsub_rn(top_v[j], mx)); sum = __fadd_rn(sum, top_v[j]); }
+                float cum = 0.f; int pick = top_i[k - 1];
+                for (int j = 0; j < k; ++j) {
+                    cum = __fadd_rn(cum, __fdiv_rn(top_v[j], sum));
+                    if (cum >= r) { pick = top_i[j]; break; }
+                }
+                result = pick;
+            }
+            __syncthreads();
+            chosen = result;
+        } else {
+            // whole vocabulary: each thread owns a contiguous chunk; chunk sums are combined in
+            // chunk order, so the cumulative sums differ from a single sequential pass only by rounding
+            float bv = -INFINITY; int bi = 0x7fffffff;
+            for (int i = tid; i < V; i += nt) { float v = __fmul_rn(lg[i], inv_t); if (better(v, i, bv, bi)) { bv = v; bi = i; } }
+            const float mx = block_argmax(bv, bi, red).v;
+            const int per = (V + nt - 1) / nt;
+            const int lo = tid * per, hi = min(V, lo + per);
+            float s = 0.f;
+            for (int i = lo; i < hi; ++i) s = __fadd_rn(s, expf(__fsub_rn(__fmul_rn(lg[i], inv_t), mx)));
+            chunk_sum[tid] = s;
+            if (tid == 0) result = V - 1;
+            __syncthreads();
+            float total = 0.f, before = 0.f;
+            for (int t = 0; t < nt; ++t) { if (t == tid) before = total; total = __fadd_rn(total, chunk_sum[t]); }
+            float cum = __fdiv_rn(before, total);
+            for (int i = lo; i < hi; ++i) {
+                cum = __fadd_rn(cum, __fdiv_rn(expf(__fsub_rn(__fmul_rn(lg[i], inv_t), mx)), total));
+                if (cum >= r) { atomicMin(&result, i); break; }
+            }
+            __syncthreads();
+            chosen = result;
+        }
+    }
+    if (tid == 0) {
+        tok_cur[b] = (uint32_t)chosen;
+        if (ctl->record) {
+            ctl->out_tokens[(size_t)step * ctl->batch + b] = (uint32_t)chosen;
+            if (!finished[b]) {
+                if ((uint32_t)chosen == ctl->eos_id && !ctl->ignore_eos) finished[b] = 1;   // main.rs:150
+                else out_len[b] += 1;
+            }
+        }
+    }
+}
+
+// End of a step: next prompt position / next output row, and one more cached token per sequence.
+__global__ void advance_step_kernel(StepCtl* ctl, int32_t* kv_pos, int B, int sampled) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (kv_pos != nullptr && i < B) kv_pos[i] += 1;
+    if (i == 0) {
+        if (ctl->prompt_pos < ctl->prompt_len) ctl->prompt_pos += 1;
+        if (sampled) ctl->step += 1;
+    }
+}
+
+// D = sigmoid(gate) * up for the attention block's MLP (model.rs:550-552); gu = [gate | up] per row
+__global__ void gate_mul_kernel(const float* __restrict__ gu, int ld, float* out32, __nv_bfloat16* hi, __nv_bfloat16* lo,
+                                int mlp) {
+    const int b = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= mlp) return;
+    float v = __fmul_rn(sigmoid_ref(gu[(size_t)b * ld + i]), gu[(size_t)b * ld + mlp + i]);
+    if (out32) out32[(size_t)b * mlp + i] = v;
+    if (hi) {
+        __nv_bfloat16 hh, ll;
+        split_bf16(v, hh, ll);
+        hi[(size_t)b * mlp + i] = hh;
+        if (lo) lo[(size_t)b * mlp + i] = ll;
+    }
+}
+
+}  // namespace
+
+// ---- launchers -------------------------------------------------------------------------------------
+cudaError_t launch_embed(const void* emb, int dtype, const uint32_t* tok_cur, float* x, int B, int D, int vocab,
+                         StepCtl* ctl, cudaStream_t st) {
+    if (dtype == LUMI_DTYPE_BF16)
+        embed_kernel<__nv_bfloat16><<<B, 128, 0, st>>>((const __nv_bfloat16*)emb, tok_cur, x, D, vocab, ctl);
+    else
+        embed_kernel<float><<<B, 128, 0, st>>>((const float*)emb, tok_cur, x, D, vocab, ctl);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_norm_split(const float* x, const float* gamma, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int D,
+                              float eps, cudaStream_t st) {
+    norm_split_kernel<<<B, 256, 0, st>>>(x, gamma, hi, lo, D, eps);
+    return cudaGetLastError();
+}
+
+template <typename WT, int NB, int ACT>
+static cudaError_t gemv_dispatch(const GemvArgs& a, cudaStream_t st) {
+    constexpr int RPW = (ACT == 1 || NB > 4) ? 1 : 2;
+    auto kern = gemv_kernel<WT, NB, RPW, ACT>;
+    size_t smem = (size_t)NB * a.K * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    dim3 grid((a.N + 8 * RPW - 1) / (8 * RPW), (a.M + NB - 1) / NB);
+    kern<<<grid, 256, smem, st>>>(a.A, a.lda, (const WT*)a.W, a.D, a.ldd, a.R, a.gamma, a.M, a.N, a.K, a.eps);
+    return cudaGetLastError();
+}
+
+template <typename WT>
+static cudaError_t gemv_by_batch(const GemvArgs& a, cudaStream_t st) {
+    if (a.act == 1) {
+        if (a.M <= 1) return gemv_dispatch<WT, 1, 1>(a, st);
+        if (a.M <= 2) return gemv_dispatch<WT, 2, 1>(a, st);
+        return gemv_dispatch<WT, 4, 1>(a, st);
+    }
+    if (a.M <= 1) return gemv_dispatch<WT, 1, 0>(a, st);
+    if (a.M <= 2) return gemv_dispatch<WT, 2, 0>(a, st);
+    if (a.M <= 4) return gemv_dispatch<WT, 4, 0>(a, st);
+    return gemv_dispatch<WT, 8, 0>(a, st);
+}
+
+cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st) {
+    if (a.w_dtype == LUMI_DTYPE_BF16) return gemv_by_batch<__nv_bfloat16>(a, st);
+    return gemv_by_batch<float>(a, st);
+}
+
+bool ssm_shape_supported(int P, int N) {
+    return (P == 16 || P == 32 || P == 64) && (N == 16 || N == 32 || N == 64 || N == 128);
+}
+
+template <int P, int N>
+static cudaError_t ssm_launch(const SsmArgs& a, cudaStream_t st) {
+    int hpb = a.B <= 4 ? 2 : 8;
+    if (hpb > a.H) hpb = a.H;
+    dim3 grid((a.H + hpb - 1) / hpb, a.B);
+    ssm_step_kernel<P, N><<<grid, hpb * 32, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ssm_step(const SsmArgs& a, cudaStream_t st) {
+#define LUMI_SSM_CASE(PP, NN) if (a.P == PP && a.N == NN) return ssm_launch<PP, NN>(a, st);
+    LUMI_SSM_CASE(32, 64) LUMI_SSM_CASE(32, 16) LUMI_SSM_CASE(32, 32) LUMI_SSM_CASE(32, 128)
+    LUMI_SSM_CASE(16, 16) LUMI_SSM_CASE(16, 32) LUMI_SSM_CASE(16, 64) LUMI_SSM_CASE(16, 128)
+    LUMI_SSM_CASE(64, 16) LUMI_SSM_CASE(64, 32) LUMI_SSM_CASE(64, 64) LUMI_SSM_CASE(64, 128)
+#undef LUMI_SSM_CASE
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_state_reset(float* h, float* xprev, float* bprev, float* cum, const float* h_init, const int32_t* slots,
+                               int n_slots, int H, int P, int N, cudaStream_t st) {
+    state_reset_kernel<<<n_slots, 256, 0, st>>>(h, xprev, bprev, cum, h_init, slots, H, P, N);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_sample(const float* logits, int B, int V, StepCtl* ctl, uint32_t* tok_cur, int32_t* finished,
+                          int32_t* out_len, cudaStream_t st) {
+    sample_kernel<<<B, 1024, 0, st>>>(logits, V, ctl, tok_cur, finished, out_len);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_advance_step(StepCtl* ctl, int32_t* kv_pos, int B, int sampled, cudaStream_t st) {
+    advance_step_kernel<<<(B + 127) / 128, 128, 0, st>>>(ctl, kv_pos, B, sampled);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gate_mul(const float* gu, int ld, float* out32, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int mlp,
+                            cudaStream_t st) {
+    dim3 grid((mlp + 255) / 256, B);
+    gate_mul_kernel<<<grid, 256, 0, st>>>(gu, ld, out32, hi, lo, mlp);
+    return cudaGetLastError();
+}
+
+}  // namespace lumi
