@@ -1,0 +1,345 @@
+#!/usr/bin/env python
+"""Decode throughput of the lumi token loop on B200, against the HBM roofline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (the benchmark definition's throughput sweep): the 96-layer Mamba-3 LM in byte-level
+mode (vocab 259), bf16 weights, fp32 state; 4096 independent sequences sharded contiguously over
+the N ranks with no collective; seeded uniform-random prompts prefilled token by token as the
+reference does; then greedy decode.  One "step" is one decode step of every resident sequence.
+Per-rank state for more than `--capacity` sequences does not fit one GPU (fp32 state is
+53.5 MB per sequence), so a rank runs its shard in waves; a step of the job is then one step of
+each wave and the times add.
+
+Prints ONE JSON line on rank 0.  `value` times the steps with tokens resident on the device
+(CUDA events on the session stream); `e2e` times the same steps through lumi_decode_step with
+host token buffers copied in and out every step.  `--impl reference` times the CPU restatement of
+the reference's own CPU path on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from lumi_b200 import shard, synth  # noqa: E402
+
+METRIC = "decode_tokens_per_second"
+UNIT = "tok/s"
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json, stream copy)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is not None:
+            self.proc.terminate()          # the exact process started above
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def workload_config(args) -> synth.ModelConfig:
+    return synth.base_config(n_layers=args.layers, byte_level=True, max_seq_len=4096)
+
+
+def state_bytes_per_seq_step(cfg) -> int:
+    """Read + write of h, the rank-1 factors of prev_bx and cum_angle, per Mamba layer."""
+    per = cfg.n_heads * cfg.head_dim * cfg.d_state + cfg.d_inner + cfg.n_heads * cfg.d_state + cfg.n_heads * cfg.d_state // 2
+    return 2 * 4 * per
+
+
+# --------------------------------------------------------------------------------------------------
+def run_reference(args, rank, world):
+    """The reference arm: the CPU restatement of lumi-infer's CPU path (the Rust/Candle binary cannot
+    be built on this image) on the host cores, all OpenMP threads.  A step = one decode token for each
+    of `--ref-seqs` sequences, run one after another (the reference has no batching)."""
+    if rank != 0:
+        return
+    from oracle import cpu_oracle
+    cfg = workload_config(args)
+    tens = list(synth.iter_tensors(cfg, seed=0, weights_dtype="bf16"))
+    om = cpu_oracle.OracleModel(cfg, tens)
+    del tens
+    nseq = args.ref_seqs
+    prompts = synth.random_prompts(nseq, 4, cfg.vocab_size, seed=0)
+    states, toks = [], []
+    for b in range(nseq):
+        st = om.init_states()
+        for t in prompts[b]:
+            lg = st.forward_step(int(t))
+        states.append(st)
+        toks.append(cpu_oracle.argmax(lg))
+
+    def step():
+        for b in range(nseq):
+            toks[b] = cpu_oracle.argmax(states[b].forward_step(toks[b]))
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    value = nseq * args.steps / dt
+    cores = os.cpu_count() or 1
+    sample = f"{nseq} sequence(s) x {args.steps} decode tokens of the same 96-layer model, after a 4-token prompt"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD_NAME(args), "reference": "CPU restatement (oracle/lumi_oracle.cpp) of inference/src/model.rs CPU branch; "
+                   "the Rust/Candle reference cannot be built here (no cargo/rustc, crates not vendored)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def WORKLOAD_NAME(args):
+    return (f"throughput sweep: {args.layers}-layer Mamba-3 LM, byte-level vocab 259, bf16 weights, fp32 state; "
+            f"{args.sequences} sequences x {args.prompt_len}-token uniform-random prompts, greedy decode")
+
+
+def cpu_baseline(args, cfg):
+    """Rank 0, N = 1: the oracle timed on the host cores on a bounded sample of the same workload."""
+    from oracle import cpu_oracle
+    tens = list(synth.iter_tensors(cfg, seed=0, weights_dtype="bf16"))
+    om = cpu_oracle.OracleModel(cfg, tens)
+    del tens
+    st = om.init_states()
+    prompt = synth.random_prompts(1, 4, cfg.vocab_size, seed=0)[0]
+    for t in prompt:
+        lg = st.forward_step(int(t))
+    tok = cpu_oracle.argmax(lg)
+    n = args.cpu_tokens
+    t0 = time.perf_counter()
+    for _ in range(n):
+        tok = cpu_oracle.argmax(st.forward_step(tok))
+    dt = time.perf_counter() - t0
+    return {"value": n / dt, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+            "sample": f"1 sequence x {n} decode tokens of the same {cfg.n_layers}-layer model after a 4-token prompt "
+                      f"(the reference runs sequences one at a time: per-sequence tok/s)"}
+
+
+def batch1_line(args, peak_gbs):
+    """Secondary figure: the base 48-layer fp32 model at batch 1 (weights-bound decode)."""
+    import lumi_b200
+    cfg = synth.base_config()
+    model = lumi_b200.NmModel.from_tensors(cfg, synth.iter_tensors(cfg, seed=0))
+    sess = model.init_states(1)
+    prompt = synth.random_prompts(1, 32, cfg.vocab_size, seed=0)
+    sess.prefill(prompt, want_logits=True)
+    sess.decode_loop_device(1, 8)
+    best = None
+    for _ in range(3):
+        ms, _ = sess.decode_loop_device(1, 64)
+        best = ms if best is None else min(best, ms)
+    per_step = model.info()["weight_bytes"] + model.info()["n_mamba"] * state_bytes_per_seq_step(cfg)
+    toks = 64 / (best * 1e-3)
+    ach = per_step * toks / 1e9
+    sess.close(); model.close()
+    return {"workload": "base 48-layer Mamba-3 LM, fp32 weights, batch 1, 32-token prompt, greedy decode (64 timed steps, best of 3)",
+            "value": toks, "unit": UNIT, "bytes_per_step": per_step, "achieved_gbs": ach, "peak_gbs": peak_gbs, "frac": ach / peak_gbs}
+
+
+def run_ours(args, rank, local_rank, world):
+    import torch
+    import torch.distributed as dist
+    import lumi_b200
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = torch.device("cuda", local_rank)
+    cfg = workload_config(args)
+    peak_gbs, peak_src = measured_peak_gbs()
+
+    lo, hi = shard.shard_range(args.sequences, rank, world)
+    my_waves = shard.waves(hi - lo, args.capacity)
+    cap = max(b - a for a, b in my_waves)
+    model = lumi_b200.NmModel.from_tensors(cfg, synth.iter_tensors(cfg, seed=0, weights_dtype="bf16"), device=local_rank)
+    info = model.info()
+    sess = model.init_states(cap)
+    sess.set_option("split_activations", args.split)
+    prompts = synth.random_prompts(hi - lo, args.prompt_len, cfg.vocab_size, seed=1000 + lo) if hi > lo else None
+
+    S = state_bytes_per_seq_step(cfg)
+    t_dev_ms, t_e2e_ms, launches = 0.0, 0.0, 0
+    fam_ms, fam_n, ssm_batch = {}, {}, 0
+    sampler = ClockSampler(local_rank)
+    h2d = d2h = 0
+    for wi, (a, b) in enumerate(my_waves):
+        nb = b - a
+        sess.reset()
+        sess.prefill(prompts[a:b], want_logits=True)                 # untimed: prompt, then first token
+        sess.decode_loop_device(nb, max(args.warmup, 3))              # warm-up steps (>= 3)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        if wi == 0:
+            sampler.start()
+        ms, n = sess.decode_loop_device(nb, args.steps)               # timed: EXACTLY K steps, CUDA events
+        torch.cuda.synchronize()
+        t_dev_ms += ms
+        launches += n
+        # end to end through the C ABI with host buffers: tokens in and out every step
+        toks = np.full(nb, 5, dtype=np.uint32)
+        _, toks = sess.forward_step(toks, want_logits=False)
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            _, toks = sess.forward_step(toks, want_logits=False, step=i)
+        t_e2e_ms += (time.perf_counter() - t0) * 1e3
+        h2d += nb * 4 + 80
+        d2h += nb * 4 + 80
+        # live per-kernel times (an event in front of every launch), second of two profiled steps
+        sess.profile_step(nb)
+        prof = sess.profile_step(nb)
+        if nb >= ssm_batch:
+            ssm_batch = nb
+            fam_ms = {k: v[0] for k, v in prof.items()}
+            fam_n = {k: v[1] for k, v in prof.items()}
+    clocks = sampler.stop()
+
+    units = float((hi - lo) * args.steps)
+    if world > 1:
+        dist.barrier()
+        tmax, total_units = shard.reduce_max_sum(dist, t_dev_ms, units, device=dev)
+        emax, _ = shard.reduce_max_sum(dist, t_e2e_ms, 0.0, device=dev)
+        lsum = shard.reduce_max_sum(dist, 0.0, float(launches), device=dev)[1]
+    else:
+        tmax, total_units, emax, lsum = t_dev_ms, units, t_e2e_ms, float(launches)
+
+    if rank == 0:
+        value = total_units / (tmax * 1e-3)
+        e2e = total_units / (emax * 1e-3)
+        # whole-step roofline on this rank: algorithmic bytes of its waves' steps over its device time
+        step_bytes = sum(info["weight_bytes"] + (b - a) * info["n_mamba"] * S for a, b in my_waves)
+        step_gbs = step_bytes * args.steps / (t_dev_ms * 1e-3) / 1e9
+        # dominant kernel: the fused Mamba state step; algorithmic bytes per launch = batch * S
+        ssm_launch_ms = fam_ms.get("ssm_step", 0.0) / max(1, fam_n.get("ssm_step", 1))
+        ssm_bytes = ssm_batch * S
+        ssm_gbs = ssm_bytes / (ssm_launch_ms * 1e-3) / 1e9 if ssm_launch_ms > 0 else 0.0
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "ssm_step_traffic.json")
+        if os.path.exists(tpath):
+            try:
+                with open(tpath) as f:
+                    traffic = float(json.load(f)["dram_bytes_per_sequence_layer"]) * ssm_batch
+            except Exception:
+                traffic = None
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": tmax / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD_NAME(args), "sequences_per_gpu": hi - lo, "waves_per_gpu": len(my_waves),
+                       "resident_sequences": cap, "weights": "bf16", "state": "fp32",
+                       "activations_into_gemm": "bf16 hi+lo split" if args.split else "bf16",
+                       "l2": "inputs larger than L2: each step streams %.1f GB of state" % (cap * info["n_mamba"] * S / 1e9),
+                       "prefill": "token by token through the decode step (untimed)"},
+            "gpu_launches": int(lsum),
+            "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "roofline": {"bound": "hbm", "kernel": "ssm_step_kernel<32,64>", "achieved": ssm_gbs, "peak": peak_gbs, "unit": "GB/s",
+                         "frac": ssm_gbs / peak_gbs, "traffic": traffic, "peak_source": peak_src,
+                         "algorithmic_bytes_per_launch": ssm_bytes, "launch_ms": ssm_launch_ms,
+                         "whole_step": {"bytes_per_step": step_bytes, "achieved": step_gbs, "frac": step_gbs / peak_gbs,
+                                        "frac_of_8TBs_nominal": step_gbs / 8000.0}},
+            "kernel_ms_per_step": fam_ms, "kernel_launches_per_step": fam_n,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(args, cfg)
+        sess.close(); model.close()
+        if not args.no_batch1:
+            try:
+                line["batch1"] = batch1_line(args, peak_gbs)
+            except Exception as e:        # the secondary figure must not take the headline down
+                line["batch1"] = {"error": str(e)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sequences", type=int, default=4096)
+    ap.add_argument("--capacity", type=int, default=2048, help="resident sequences per GPU (fp32 state: 53.5 MB each at 96 layers)")
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=96)
+    ap.add_argument("--split", type=int, default=1)
+    ap.add_argument("--ref-seqs", type=int, default=1)
+    ap.add_argument("--cpu-tokens", type=int, default=24)
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-batch1", action="store_true")
+    args = ap.parse_args()
+    rank, local_rank, world = shard.env_rank_world()
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE {world}")
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

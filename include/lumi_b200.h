@@ -148,6 +148,12 @@ int32_t lumi_generate(lumi_session* s, const uint32_t* prompts, int32_t batch, i
 int32_t lumi_decode_loop_device(lumi_session* s, int32_t batch, int32_t n_steps, float* ms_out,
                                 int64_t* launches_out);
 
+/* One decode step launched kernel by kernel with a CUDA event in front of every launch, for live
+ * per-kernel timing.  Fills 8 entries each: milliseconds and launch counts by family —
+ * 0 embedding, 1 RMSNorm to bf16, 2 in_proj, 3 Mamba state step, 4 out_proj, 5 attention block,
+ * 6 final norm + lm_head, 7 sampling + bookkeeping.  Advances the sequences by one (greedy) token. */
+int32_t lumi_profile_step(lumi_session* s, int32_t batch, float* ms_by_family, int64_t* launches_by_family);
+
 /* Copies one sequence's Mamba state of one layer to host (any pointer may be NULL):
  * h [H][P][N], x_prev [H][P], b_prev [H][N] (prev_bx = x_prev (x) b_prev), cum_angle [H][N/2]. */
 int32_t lumi_session_read_state(lumi_session* s, int32_t slot, int32_t layer, float* h, float* x_prev,

@@ -24,7 +24,7 @@ EXPORTS = [
     "lumi_last_error", "lumi_model_create", "lumi_model_load_tensor", "lumi_model_load_safetensors",
     "lumi_model_finalize", "lumi_model_free", "lumi_model_info", "lumi_session_create", "lumi_session_reset",
     "lumi_session_free", "lumi_session_set_option", "lumi_prefill", "lumi_decode_step", "lumi_generate",
-    "lumi_decode_loop_device", "lumi_session_read_state", "lumi_debug_run_block", "lumi_k_gemm_bf16_tcgen05",
+    "lumi_decode_loop_device", "lumi_profile_step", "lumi_session_read_state", "lumi_debug_run_block", "lumi_k_gemm_bf16_tcgen05",
     "lumi_k_gemv",
 ]
 
@@ -71,6 +71,7 @@ def lib():
         L.lumi_decode_step.argtypes = [vp, vp, i32, C.POINTER(Sampling), i32, vp, vp]
         L.lumi_generate.argtypes = [vp, vp, i32, i32, i32, C.POINTER(Sampling), vp, vp, vp, C.POINTER(Stats)]
         L.lumi_decode_loop_device.argtypes = [vp, i32, i32, C.POINTER(C.c_float), C.POINTER(i64)]
+        L.lumi_profile_step.argtypes = [vp, i32, C.POINTER(C.c_float), C.POINTER(i64)]
         L.lumi_session_read_state.argtypes = [vp, i32, i32, vp, vp, vp, vp]
         L.lumi_debug_run_block.argtypes = [vp, i32, vp, i32]
         L.lumi_k_gemm_bf16_tcgen05.argtypes = [u64, u64, u64, u64, i32, i32, i32, i32, i32, u64]
@@ -223,6 +224,15 @@ class Session:
         n = C.c_int64()
         check(lib().lumi_decode_loop_device(self._h, batch, n_steps, C.byref(ms), C.byref(n)))
         return float(ms.value), int(n.value)
+
+    FAMILIES = ["embedding", "norm_split", "in_proj", "ssm_step", "out_proj", "attention_block", "lm_head", "sample"]
+
+    def profile_step(self, batch: int) -> dict:
+        """One decode step with a CUDA event before every launch: {family: (ms, launches)}."""
+        ms = (C.c_float * 8)()
+        n = (C.c_int64 * 8)()
+        check(lib().lumi_profile_step(self._h, batch, ms, n))
+        return {f: (float(ms[i]), int(n[i])) for i, f in enumerate(self.FAMILIES)}
 
     def read_state(self, slot: int, layer: int):
         c = self.model.config

@@ -470,12 +470,28 @@ extern "C" int32_t lumi_session_set_option(lumi_session* s, const char* name, in
 // ---- one step ---------------------------------------------------------------------------------------
 namespace {
 
+enum Family { FAM_EMBED = 0, FAM_NORM, FAM_IN_PROJ, FAM_SSM, FAM_OUT_PROJ, FAM_ATTN, FAM_HEAD, FAM_SAMPLE, FAM_COUNT };
+
 struct StepPlan {
     lumi_session* s;
     int B;
     bool tc;         // tensor-core GEMMs (bf16 weights, batch > 8) or the weight-streaming GEMV
     int64_t n = 0;   // launches enqueued
+    int fam = FAM_EMBED;                                          // family of the launches that follow
+    std::vector<std::pair<int, cudaEvent_t>>* prof = nullptr;     // profiling: an event before every launch
 };
+
+// Counts a launch and, when profiling, drops an event in front of it.
+void mark(StepPlan& p) {
+    p.n += 1;
+    if (p.prof) {
+        cudaEvent_t e = nullptr;
+        if (cudaEventCreate(&e) == cudaSuccess) {
+            cudaEventRecord(e, p.s->stream);
+            p.prof->push_back({p.fam, e});
+        }
+    }
+}
 
 bool use_tc(const lumi_session* s, int B) {
     const Config& c = s->m->cfg;
@@ -490,15 +506,15 @@ int32_t linear(StepPlan& p, const DevTensor& W, const float* in32, int K, float*
     const Config& c = s->m->cfg;
     if (!p.tc) {
         GemvArgs g{in32, K, W.p, W.dtype, out, ldd, residual, gamma, p.B, N, K, c.eps, act};
+        mark(p);
         LUMI_CUDA(launch_gemv(g, s->stream));
-        p.n += 1;
         return LUMI_OK;
     }
     // tensor-core path: the caller has already put the bf16 halves of the input into act_hi / act_lo
     GemmArgs g{s->act_hi, s->opt_split ? s->act_lo : nullptr, (const __nv_bfloat16*)W.p, out, ldd, p.B, N, K,
                residual != nullptr ? 1 : 0, &s->ctl->status};
+    mark(p);
     LUMI_TRY(launch_gemm_tcgen05(g, s->stream));
-    p.n += 1;
     return LUMI_OK;
 }
 
@@ -508,9 +524,11 @@ int32_t mamba_block(StepPlan& p, const Layer& L) {
     const size_t B = s->max_batch, l = L.kind_idx;
     const int D = c.d_model, DI = c.d_inner(), R = c.in_proj_out();
     if (p.tc) {
+        p.fam = FAM_NORM;
+        mark(p);
         LUMI_CUDA(launch_norm_split(s->x, L.m.norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, D, c.eps, s->stream));
-        p.n += 1;
     }
+    p.fam = FAM_IN_PROJ;
     LUMI_TRY(linear(p, L.m.in_proj, s->x, D, s->proj, R, nullptr, L.m.norm_g, 0, R));
     SsmArgs a{};
     a.proj = s->proj; a.ldp = R;
@@ -523,8 +541,10 @@ int32_t mamba_block(StepPlan& p, const Layer& L) {
     a.yhi = p.tc ? s->act_hi : nullptr;
     a.ylo = (p.tc && s->opt_split) ? s->act_lo : nullptr;
     a.B = p.B; a.H = c.n_heads; a.P = c.head_dim(); a.N = c.d_state; a.G = c.n_groups; a.eps = c.eps;
+    p.fam = FAM_SSM;
+    mark(p);
     LUMI_CUDA(launch_ssm_step(a, s->stream));
-    p.n += 1;
+    p.fam = FAM_OUT_PROJ;
     LUMI_TRY(linear(p, L.m.out_proj, s->y32, DI, s->x, D, s->x, nullptr, 0, D));
     return LUMI_OK;
 }
@@ -533,9 +553,10 @@ int32_t attention_block(StepPlan& p, const Layer& L) {
     lumi_session* s = p.s;
     const Config& c = s->m->cfg;
     const int D = c.d_model, KV = c.kv_dim(), Q = D + 2 * KV, MLP = c.mlp_dim();
+    p.fam = FAM_ATTN;
     if (p.tc) {
+        mark(p);
         LUMI_CUDA(launch_norm_split(s->x, L.a.attn_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, D, c.eps, s->stream));
-        p.n += 1;
     }
     LUMI_TRY(linear(p, L.a.qkv, s->x, D, s->proj, Q, nullptr, L.a.attn_norm_g, 0, Q));
     AttnArgs a{};
@@ -552,17 +573,18 @@ int32_t attention_block(StepPlan& p, const Layer& L) {
     if (a.max_tokens > s->max_tokens_kv) a.max_tokens = s->max_tokens_kv;
     a.rope_base = c.attn_rope_base;
     a.ctl = s->ctl;
+    mark(p);
     cudaError_t e = launch_attention_decode(a, s->stream);
     if (e == cudaErrorInvalidValue) return fail(LUMI_E_UNSUPPORTED, "attention head_dim %d with %d query heads per kv head is not built", a.head_dim, a.n_heads / a.kv_heads);
     LUMI_CUDA(e);
-    p.n += 1;
     LUMI_TRY(linear(p, L.a.o, s->y32, D, s->x, D, s->x, nullptr, 0, D));
     // sigmoid-gated MLP (model.rs:546-555)
     if (p.tc) {
+        mark(p);
         LUMI_CUDA(launch_norm_split(s->x, L.a.mlp_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, D, c.eps, s->stream));
         LUMI_TRY(linear(p, L.a.gate_up, nullptr, D, s->proj, 2 * MLP, nullptr, nullptr, 0, 2 * MLP));
+        mark(p);
         LUMI_CUDA(launch_gate_mul(s->proj, 2 * MLP, nullptr, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, MLP, s->stream));
-        p.n += 2;
     } else {
         LUMI_TRY(linear(p, L.a.gate_up, s->x, D, s->y32, MLP, nullptr, L.a.mlp_norm_g, 1, MLP));
     }
@@ -571,26 +593,36 @@ int32_t attention_block(StepPlan& p, const Layer& L) {
 }
 
 // embedding -> blocks -> (final norm -> logits -> sample) -> advance
-int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches) {
+int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches,
+                     std::vector<std::pair<int, cudaEvent_t>>* prof = nullptr) {
     const Config& c = s->m->cfg;
     StepPlan p{s, B, use_tc(s, B)};
+    p.prof = prof;
+    mark(p);
     LUMI_CUDA(launch_embed(s->m->embedding.p, s->m->embedding.dtype, s->tok_cur, s->x, B, c.d_model, c.vocab, s->ctl, s->stream));
-    p.n += 1;
     for (const Layer& L : s->m->layers) {
         if (L.is_attn) LUMI_TRY(attention_block(p, L));
         else LUMI_TRY(mamba_block(p, L));
     }
     if (with_head) {
+        p.fam = FAM_HEAD;
         if (p.tc) {
+            mark(p);
             LUMI_CUDA(launch_norm_split(s->x, s->m->final_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, B, c.d_model, c.eps, s->stream));
-            p.n += 1;
         }
         LUMI_TRY(linear(p, s->m->embedding, s->x, c.d_model, s->logits, c.vocab, nullptr, s->m->final_norm_g, 0, c.vocab));
+        p.fam = FAM_SAMPLE;
+        mark(p);
         LUMI_CUDA(launch_sample(s->logits, B, c.vocab, s->ctl, s->tok_cur, s->finished, s->out_len, s->stream));
-        p.n += 1;
     }
+    p.fam = FAM_SAMPLE;
+    mark(p);
     LUMI_CUDA(launch_advance_step(s->ctl, s->m->n_attn > 0 ? s->kv_pos : nullptr, B, with_head ? 1 : 0, s->stream));
-    p.n += 1;
+    if (prof) {   // closing event
+        p.fam = FAM_COUNT;
+        mark(p);
+        p.n -= 1;
+    }
     *launches = p.n;
     return LUMI_OK;
 }
@@ -792,6 +824,35 @@ extern "C" int32_t lumi_decode_loop_device(lumi_session* s, int32_t batch, int32
     LUMI_CUDA(cudaEventElapsedTime(&ms, s->ev0, s->ev1));
     if (ms_out) *ms_out = ms;
     if (launches_out) *launches_out = s->launches - l0;
+    return check_status(s);
+}
+
+extern "C" int32_t lumi_profile_step(lumi_session* s, int32_t batch, float* ms_by_family, int64_t* launches_by_family) {
+    LUMI_TRY(check_batch(s, batch));
+    if (!ms_by_family || !launches_by_family) return fail(LUMI_E_INVALID, "null output to lumi_profile_step");
+    LUMI_CUDA(cudaSetDevice(s->m->device));
+    lumi_sampling sp{};
+    sp.ignore_eos = 1;
+    fill_ctl(s, batch, &sp);
+    LUMI_TRY(push_ctl(s));
+    std::vector<std::pair<int, cudaEvent_t>> ev;
+    int64_t n = 0;
+    int32_t st = enqueue_step(s, batch, true, &n, &ev);
+    cudaError_t e = cudaStreamSynchronize(s->stream);
+    for (int f = 0; f < 8; ++f) { ms_by_family[f] = 0.f; launches_by_family[f] = 0; }
+    if (st == LUMI_OK && e == cudaSuccess) {
+        for (size_t i = 0; i + 1 < ev.size(); ++i) {
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, ev[i].second, ev[i + 1].second);
+            if (ev[i].first < 8) { ms_by_family[ev[i].first] += ms; launches_by_family[ev[i].first] += 1; }
+        }
+    }
+    for (auto& pe : ev) cudaEventDestroy(pe.second);
+    if (st != LUMI_OK) return st;
+    LUMI_CUDA(e);
+    s->launches += n;
+    LUMI_TRY(pull_ctl(s));
+    LUMI_CUDA(cudaStreamSynchronize(s->stream));
     return check_status(s);
 }
 

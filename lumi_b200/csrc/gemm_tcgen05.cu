@@ -201,6 +201,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__
     } else {
         const int q = warp & 3;                  // TMEM lane quarter this warp may read
         if (!mbar_wait(tmem_full, 0)) timed_out = true;
+        timed_out = __any_sync(0xffffffffu, timed_out);     // tcgen05.ld below is warp-collective
         tc_fence_after();
         if (!timed_out) {
             const int row = m0 + q * 32 + lane;
