@@ -178,7 +178,7 @@ def cpu_baseline(args, cfg):
 def batch1_line(args, peak_gbs):
     """Secondary figure: the base 48-layer fp32 model at batch 1 (weights-bound decode)."""
     import lumi_b200
-    cfg = synth.base_config()
+    cfg = synth.base_config(n_layers=args.b1_layers)
     model = lumi_b200.NmModel.from_tensors(cfg, synth.iter_tensors(cfg, seed=0))
     sess = model.init_states(1)
     prompt = synth.random_prompts(1, 32, cfg.vocab_size, seed=0)
@@ -192,7 +192,7 @@ def batch1_line(args, peak_gbs):
     toks = 64 / (best * 1e-3)
     ach = per_step * toks / 1e9
     sess.close(); model.close()
-    return {"workload": "base 48-layer Mamba-3 LM, fp32 weights, batch 1, 32-token prompt, greedy decode (64 timed steps, best of 3)",
+    return {"workload": f"base {cfg.n_layers}-layer Mamba-3 LM, fp32 weights, batch 1, 32-token prompt, greedy decode (64 timed steps, best of 3)",
             "value": toks, "unit": UNIT, "bytes_per_step": per_step, "achieved_gbs": ach, "peak_gbs": peak_gbs, "frac": ach / peak_gbs}
 
 
@@ -331,11 +331,15 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=24)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-batch1", action="store_true")
+    ap.add_argument("--only-batch1", action="store_true", help="run just the batch-1 figure (profiling)")
+    ap.add_argument("--b1-layers", type=int, default=48)
     args = ap.parse_args()
     rank, local_rank, world = shard.env_rank_world()
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE {world}")
-    if args.impl == "reference":
+    if args.only_batch1:
+        print(json.dumps({"batch1": batch1_line(args, measured_peak_gbs()[0])}), flush=True)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     else:
         run_ours(args, rank, local_rank, world)

@@ -118,7 +118,9 @@ void    lumi_session_free(lumi_session* s);
 /* Options (name, value):  "gemm" = 0 auto | 1 SIMT only | 2 tcgen05 only;
  *                         "split_activations" = 1 (default) feeds tensor-core GEMMs with bf16 hi+lo
  *                         halves of each fp32 activation, 0 rounds activations to bf16 once;
- *                         "graph" = 1 (default) replays the decode step as a CUDA graph. */
+ *                         "graph" = 1 (default) replays the decode step as a CUDA graph;
+ *                         "pdl" = 1 (default) launches the weight-streaming kernels with programmatic
+ *                         dependent launch so each one prefetches its weights while its predecessor runs. */
 int32_t lumi_session_set_option(lumi_session* s, const char* name, int64_t value);
 
 /* ---- token loop: replaces NmModel::forward_step (inference/src/model.rs:766-801) and the
@@ -175,6 +177,13 @@ int32_t lumi_k_gemm_bf16_tcgen05(uint64_t a_hi, uint64_t a_lo, uint64_t w, uint6
  * w_dtype LUMI_DTYPE_*.  norm_gamma != 0 applies RMSNorm(gamma) to each row of A first. */
 int32_t lumi_k_gemv(uint64_t a_f32, uint64_t w, int32_t w_dtype, uint64_t d, uint64_t residual,
                     uint64_t norm_gamma, int32_t M, int32_t N, int32_t K, uint64_t stream);
+
+/* The fused Mamba-3 state step alone (inference/src/model.rs:301-370 after in_proj, before
+ * out_proj): proj[B][ldp] holds in_proj's output rows; h[B][H][P][N], x_prev[B][H][P],
+ * b_prev[B][H][N], cum_angle[B][H][N/2] are updated in place; y[B][H*P] receives the gated output. */
+int32_t lumi_k_ssm_step(uint64_t proj, int32_t ldp, uint64_t b_gamma, uint64_t c_gamma, uint64_t b_bias, uint64_t c_bias,
+                        uint64_t d_skip, uint64_t dt_bias, uint64_t h, uint64_t x_prev, uint64_t b_prev, uint64_t cum_angle,
+                        uint64_t y, int32_t B, int32_t H, int32_t P, int32_t N, int32_t G, uint64_t stream);
 
 #ifdef __cplusplus
 }

