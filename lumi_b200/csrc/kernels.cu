@@ -124,30 +124,63 @@ __global__ void __launch_bounds__(256) norm_split_kernel(const float* __restrict
 
 // ---- weight-streaming GEMV for small batches ---------------------------------------------------------
 // D[m][n] = sum_k A'[m][k] W[n][k] (+ R[m][n]),  A' = RMSNorm(A; gamma) when gamma != null.
-// One warp owns RPW output rows at a time and streams them with 16-byte loads (lane c reads chunk
-// c, c+32, ...); the NB activation rows of the batch tile sit in shared memory.  Per-lane partial
-// sums run in ascending k, then a 5-step xor-shuffle tree.
+//
+// A warp owns RPW output rows and one K segment of them (KSEG = 32 lanes x U chunks of 16 bytes).
+// It loads its whole share of the weights into registers FIRST — before the dependent-launch wait
+// and before the activation prologue — so the HBM stream of this kernel overlaps its predecessor
+// and its own prologue.  Rows longer than one segment are split over KS warps of the same CTA and
+// combined through shared memory in segment order (fixed summation order: per-lane partials in
+// ascending k, 5-step xor tree, then segments 0..KS-1).
+constexpr int kGemvU = 8;
+
+template <typename WT> struct WRaw;      // 16 raw bytes -> floats
+template <> struct WRaw<float> {
+    __device__ static __forceinline__ void cvt(const uint4& v, float (&w)[4]) {
+        w[0] = __uint_as_float(v.x); w[1] = __uint_as_float(v.y); w[2] = __uint_as_float(v.z); w[3] = __uint_as_float(v.w);
+    }
+};
+template <> struct WRaw<__nv_bfloat16> {
+    __device__ static __forceinline__ void cvt(const uint4& v, float (&w)[8]) {
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { w[2 * i] = __uint_as_float(u[i] << 16); w[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
+    }
+};
+
 template <typename WT, int NB, int RPW, int ACT>
 __global__ void __launch_bounds__(256) gemv_kernel(const float* __restrict__ A, int lda, const WT* __restrict__ W,
                                                    float* __restrict__ D, int ldd, const float* __restrict__ R,
-                                                   const float* __restrict__ gamma, int M, int N, int K, float eps) {
+                                                   const float* __restrict__ gamma, int M, int N, int K, float eps, int KS) {
     extern __shared__ float4 gemv_smem4[];
     float* xs = reinterpret_cast<float*>(gemv_smem4);
     constexpr int E = WLoad<WT>::E;
+    constexpr int U = kGemvU;
+    constexpr int NR = (ACT == 1) ? 2 * RPW : RPW;     // ACT == 1 pairs weight rows n (gate) and n + N (up)
+    __shared__ float part[8][NR][NB];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * NB;
     const int nb = min(NB, M - m0);
-    const int K4 = K >> 2;
+    const int K4 = K >> 2, KC = K / E;
+    const int gpc = 8 / KS;                             // row groups per CTA
+    const int g = warp / KS, seg = warp - g * KS;
+    const int row0 = (blockIdx.x * gpc + g) * RPW;
+    const int c0 = seg * 32 * U + lane;                 // this lane's first 16-byte chunk
+
     pdl_launch_dependents();
-    if (blockIdx.y == 0) {
-        // the weights do not depend on the previous kernel: start them towards L2 before waiting for it
-        const int r = blockIdx.x * 8 * RPW + threadIdx.x;
-        if (threadIdx.x < 8 * RPW && r < N) {
-            l2_prefetch(W + (size_t)r * K, (uint32_t)(K * sizeof(WT)));
-            if (ACT == 1) l2_prefetch(W + (size_t)(r + N) * K, (uint32_t)(K * sizeof(WT)));
+    // the weights do not depend on the previous kernel: all loads go out before waiting for it
+    uint4 wreg[NR][U];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        const int row = min(row0 + (r % RPW), N - 1) + ((ACT == 1 && r >= RPW) ? N : 0);
+        const WT* wp = W + (size_t)row * K;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = c0 + 32 * u;
+            wreg[r][u] = (c < KC && row0 < N) ? __ldg(reinterpret_cast<const uint4*>(wp + (size_t)c * E)) : make_uint4(0u, 0u, 0u, 0u);
         }
     }
     pdl_wait();
+
     for (int i = threadIdx.x; i < NB * K4; i += 256) {
         int b = i / K4, k4 = i - b * K4;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -166,47 +199,56 @@ __global__ void __launch_bounds__(256) gemv_kernel(const float* __restrict__ A, 
         }
         __syncthreads();
     }
-    // with ACT == 1 each logical output n pairs weight rows n (gate) and n + N (up)
-    constexpr int NR = (ACT == 1) ? 2 * RPW : RPW;
-    const int row0 = (blockIdx.x * 8 + warp) * RPW;
-    if (row0 >= N) return;
-    const WT* wp[NR];
-#pragma unroll
-    for (int r = 0; r < RPW; ++r) {
-        int row = min(row0 + r, N - 1);
-        wp[r] = W + (size_t)row * K;
-        if constexpr (ACT == 1) wp[RPW + r] = W + (size_t)(row + N) * K;
-    }
     float acc[NR][NB];
 #pragma unroll
     for (int r = 0; r < NR; ++r)
 #pragma unroll
         for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
-    const int KC = K / E;
-#pragma unroll 2
-    for (int c = lane; c < KC; c += 32) {
-        float w[NR][E];
 #pragma unroll
-        for (int r = 0; r < NR; ++r) WLoad<WT>::load(wp[r] + c * E, w[r]);
+    for (int u = 0; u < U; ++u) {
+        const int c = c0 + 32 * u;
+        if (c < KC) {
+            float w[NR][E];
 #pragma unroll
-        for (int b = 0; b < NB; ++b) {
-            float xv[E];
+            for (int r = 0; r < NR; ++r) WRaw<WT>::cvt(wreg[r][u], w[r]);
 #pragma unroll
-            for (int q = 0; q < E / 4; ++q) {
-                float4 v = *reinterpret_cast<const float4*>(xs + b * K + c * E + 4 * q);
-                xv[4 * q] = v.x; xv[4 * q + 1] = v.y; xv[4 * q + 2] = v.z; xv[4 * q + 3] = v.w;
+            for (int b = 0; b < NB; ++b) {
+                float xv[E];
+#pragma unroll
+                for (int q = 0; q < E / 4; ++q) {
+                    float4 v = *reinterpret_cast<const float4*>(xs + b * K + c * E + 4 * q);
+                    xv[4 * q] = v.x; xv[4 * q + 1] = v.y; xv[4 * q + 2] = v.z; xv[4 * q + 3] = v.w;
+                }
+#pragma unroll
+                for (int r = 0; r < NR; ++r)
+#pragma unroll
+                    for (int e = 0; e < E; ++e) acc[r][b] = fmaf(w[r][e], xv[e], acc[r][b]);
             }
-#pragma unroll
-            for (int r = 0; r < NR; ++r)
-#pragma unroll
-                for (int e = 0; e < E; ++e) acc[r][b] = fmaf(w[r][e], xv[e], acc[r][b]);
         }
     }
 #pragma unroll
     for (int r = 0; r < NR; ++r)
 #pragma unroll
         for (int b = 0; b < NB; ++b) acc[r][b] = warp_sum(acc[r][b]);
-    if (lane == 0) {
+    if (KS > 1) {
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+#pragma unroll
+                for (int b = 0; b < NB; ++b) part[warp][r][b] = acc[r][b];
+        }
+        __syncthreads();
+        if (seg != 0) return;
+#pragma unroll
+        for (int r = 0; r < NR; ++r)
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                float t = part[warp][r][b];
+                for (int sg = 1; sg < KS; ++sg) t += part[warp + sg][r][b];
+                acc[r][b] = t;
+            }
+    }
+    if (lane == 0 && row0 < N) {
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
             int row = row0 + r;
@@ -234,18 +276,49 @@ struct SsmSmem {
     float bt[N], ct[N], xa[P], xp[P], gate[P], yout[P];
 };
 
-template <int P, int N>
+// WPH warps share one head: each owns P / WPH consecutive state rows.  WPH = 1 at large batch (a
+// warp streams a whole 8 KiB tile); WPH = 4 at small batch, where the tile compute of one warp
+// would otherwise sit on the critical path of the token.
+template <int P, int N, int WPH>
 __global__ void __launch_bounds__(256, 2) ssm_step_kernel(SsmArgs a) {
     __shared__ SsmSmem<P, N> sm_all[8];
     __shared__ float red[2][8];
+    constexpr int CG = N / 4;              // lanes sharing one state row
+    constexpr int RS = 32 / CG;            // state rows covered by one warp-wide float4 access
+    constexpr int IT = P / RS;             // accesses per tile
+    constexpr int ITW = IT / WPH;          // accesses per warp
+    constexpr int CH = ITW < 16 ? ITW : 16;
+    constexpr int ROWS = P / WPH;          // rows per warp
+    static_assert(IT % WPH == 0 && ITW >= 1, "rows must split evenly over the warps of a head");
     const int b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int hpb = blockDim.x >> 5;
-    const int h = blockIdx.x * hpb + warp;
+    const int nwarp = blockDim.x >> 5;
+    const int hpb = nwarp / WPH;
+    const int hl = warp / WPH, sub = warp - hl * WPH;
+    const int h = blockIdx.x * hpb + hl;
     const int H = a.H, DI = H * P, BC = a.G * N, HN = N / 2;
+    const bool active = h < H;
+    const size_t bh = (size_t)b * H + (active ? h : H - 1);
+    const int c = lane % CG, r0 = lane / CG;
+
     pdl_launch_dependents();
-    if (h < H && lane == 0) l2_prefetch(a.h + ((size_t)b * H + h) * (size_t)(P * N), (uint32_t)(P * N * sizeof(float)));
+    // State is only ever written by this same kernel one token earlier, and every step starts with a
+    // kernel that is not launched early, so the whole previous step has finished before this line:
+    // the state can be requested ahead of the dependency wait and its HBM latency runs under the
+    // predecessor's tail and the prologue below.
+    float4* h4 = reinterpret_cast<float4*>(a.h + bh * (size_t)(P * N)) + (size_t)sub * ITW * 32;
+    float4 t[CH];
+    float4 bpq = make_float4(0.f, 0.f, 0.f, 0.f);
+    float cu_old[(HN + 31) / 32];
+    if (active) {
+#pragma unroll
+        for (int i = 0; i < CH; ++i) t[i] = h4[i * 32 + lane];
+        bpq = reinterpret_cast<const float4*>(a.bprev + bh * N)[c];
+#pragma unroll
+        for (int j = 0; j < (HN + 31) / 32; ++j) cu_old[j] = (lane + 32 * j < HN) ? a.cum[bh * HN + lane + 32 * j] : 0.f;
+    }
     pdl_wait();
+
     const float* pr = a.proj + (size_t)b * a.ldp;
     const float* Bp = pr + 2 * DI;
     const float* Cp = Bp + BC;
@@ -265,14 +338,13 @@ __global__ void __launch_bounds__(256, 2) ssm_step_kernel(SsmArgs a) {
     sb = warp_sum(sb);
     sc = warp_sum(sc);
     if (lane == 0) { red[0][warp] = sb; red[1][warp] = sc; }
-    __syncthreads();
-    if (h >= H) return;
+    __syncthreads();       // also orders every warp's reads of bprev / cum above before the writes below
+    if (!active) return;
     float tb = 0.f, tc = 0.f;
-    for (int w = 0; w < hpb; ++w) { tb += red[0][w]; tc += red[1][w]; }
+    for (int w = 0; w < nwarp; ++w) { tb += red[0][w]; tc += red[1][w]; }
     const float rb = rms_scale(tb, BC, a.eps), rc = rms_scale(tc, BC, a.eps);
 
     SsmSmem<P, N>& sm = sm_all[warp];
-    const size_t bh = (size_t)b * H + h;
 
     // per-head scalars (model.rs:307, 314-317, 355-359)
     const float dtp = softplus_ref(__fadd_rn(dt[h], a.dtb[h]));
@@ -284,52 +356,49 @@ __global__ void __launch_bounds__(256, 2) ssm_step_kernel(SsmArgs a) {
     const float c2 = __fmul_rn(abar, oml);
     const int g = h / (H / a.G);
 
-    // previous B~ for this lane's four state columns, read before it is overwritten below
-    constexpr int CG = N / 4;              // lanes sharing one state row
-    const int c = lane % CG, r0 = lane / CG;
-    const float4 bpq = reinterpret_cast<const float4*>(a.bprev + bh * N)[c];
-
     // DD-RoPE (model.rs:338-350): lane k rotates pair (2k, 2k+1) of the normalised B and C
     const float PI_F = 3.14159265358979323846f;
     const float TWO_PI = __fmul_rn(2.0f, PI_F);
-    for (int k = lane; k < HN; k += 32) {
-        float angle = __fmul_rn(tanhf(theta[h * HN + k]), PI_F);
-        float cu = a.cum[bh * HN + k];
-        cu = fmodf(__fadd_rn(cu, __fmul_rn(dtp, angle)), TWO_PI);
-        a.cum[bh * HN + k] = cu;
-        float sa, ca;
-        sincosf(cu, &sa, &ca);
-        const int i0 = g * N + 2 * k;
-        float b0 = __fadd_rn(__fmul_rn(__fmul_rn(Bp[i0], rb), a.bg[i0]), a.bb[i0]);
-        float b1 = __fadd_rn(__fmul_rn(__fmul_rn(Bp[i0 + 1], rb), a.bg[i0 + 1]), a.bb[i0 + 1]);
-        float c0 = __fadd_rn(__fmul_rn(__fmul_rn(Cp[i0], rc), a.cg[i0]), a.cb[i0]);
-        float c1 = __fadd_rn(__fmul_rn(__fmul_rn(Cp[i0 + 1], rc), a.cg[i0 + 1]), a.cb[i0 + 1]);
-        sm.bt[2 * k] = __fsub_rn(__fmul_rn(ca, b0), __fmul_rn(sa, b1));
-        sm.bt[2 * k + 1] = __fadd_rn(__fmul_rn(sa, b0), __fmul_rn(ca, b1));
-        sm.ct[2 * k] = __fsub_rn(__fmul_rn(ca, c0), __fmul_rn(sa, c1));
-        sm.ct[2 * k + 1] = __fadd_rn(__fmul_rn(sa, c0), __fmul_rn(ca, c1));
+#pragma unroll
+    for (int j = 0; j < (HN + 31) / 32; ++j) {
+        const int k = lane + 32 * j;
+        if (k < HN) {
+            float angle = __fmul_rn(tanhf(theta[h * HN + k]), PI_F);
+            float cu = fmodf(__fadd_rn(cu_old[j], __fmul_rn(dtp, angle)), TWO_PI);
+            if (sub == 0) a.cum[bh * HN + k] = cu;
+            float sa, ca;
+            sincosf(cu, &sa, &ca);
+            const int i0 = g * N + 2 * k;
+            float b0 = __fadd_rn(__fmul_rn(__fmul_rn(Bp[i0], rb), a.bg[i0]), a.bb[i0]);
+            float b1 = __fadd_rn(__fmul_rn(__fmul_rn(Bp[i0 + 1], rb), a.bg[i0 + 1]), a.bb[i0 + 1]);
+            float c0 = __fadd_rn(__fmul_rn(__fmul_rn(Cp[i0], rc), a.cg[i0]), a.cb[i0]);
+            float c1 = __fadd_rn(__fmul_rn(__fmul_rn(Cp[i0 + 1], rc), a.cg[i0 + 1]), a.cb[i0 + 1]);
+            sm.bt[2 * k] = __fsub_rn(__fmul_rn(ca, b0), __fmul_rn(sa, b1));
+            sm.bt[2 * k + 1] = __fadd_rn(__fmul_rn(sa, b0), __fmul_rn(ca, b1));
+            sm.ct[2 * k] = __fsub_rn(__fmul_rn(ca, c0), __fmul_rn(sa, c1));
+            sm.ct[2 * k + 1] = __fadd_rn(__fmul_rn(sa, c0), __fmul_rn(ca, c1));
+        }
     }
-    for (int p = lane; p < P; p += 32) {
-        sm.xa[p] = silu_ref(pr[h * P + p]);                 // model.rs:310
-        sm.xp[p] = a.xprev[bh * P + p];
-        sm.gate[p] = silu_ref(pr[DI + h * P + p]);          // model.rs:370
+    const int prow0 = sub * ROWS;          // first state row of this warp
+    for (int p = lane; p < ROWS; p += 32) {
+        const int row = prow0 + p;
+        sm.xa[row] = silu_ref(pr[h * P + row]);             // model.rs:310
+        sm.xp[row] = a.xprev[bh * P + row];
+        sm.gate[row] = silu_ref(pr[DI + h * P + row]);      // model.rs:370
     }
     __syncwarp();
 
     const float4 bq = reinterpret_cast<const float4*>(sm.bt)[c];
     const float4 cq = reinterpret_cast<const float4*>(sm.ct)[c];
-    constexpr int RS = 32 / CG;            // state rows covered by one warp-wide float4 access
-    constexpr int IT = P / RS;             // accesses per tile
-    constexpr int CH = IT < 16 ? IT : 16;  // accesses kept in registers at once
-    float4* h4 = reinterpret_cast<float4*>(a.h + bh * (size_t)(P * N));
 #pragma unroll 1
-    for (int i0 = 0; i0 < IT; i0 += CH) {
-        float4 t[CH];
+    for (int i0 = 0; i0 < ITW; i0 += CH) {
+        if (i0 > 0) {
 #pragma unroll
-        for (int i = 0; i < CH; ++i) t[i] = h4[(i0 + i) * 32 + lane];
+            for (int i = 0; i < CH; ++i) t[i] = h4[(i0 + i) * 32 + lane];
+        }
 #pragma unroll
         for (int i = 0; i < CH; ++i) {
-            const int row = r0 + (i0 + i) * RS;
+            const int row = r0 + (sub * ITW + i0 + i) * RS;
             const float xv = sm.xa[row], xpv = sm.xp[row];
             float part;
             {   // model.rs:354-366 : h = (abar*h + (abar*(1-lam))*prev_bx) + lam*bx ; y = sum_s C~[s] h[s]
@@ -350,11 +419,12 @@ __global__ void __launch_bounds__(256, 2) ssm_step_kernel(SsmArgs a) {
         }
     }
     __syncwarp();
-    for (int p = lane; p < P; p += 32) {
-        float xv = sm.xa[p];
-        float yv = __fadd_rn(sm.yout[p], __fmul_rn(a.dskip[h], xv));     // model.rs:367-368
-        yv = __fmul_rn(yv, sm.gate[p]);                                  // model.rs:370
-        const size_t o = (size_t)b * DI + h * P + p;
+    for (int p = lane; p < ROWS; p += 32) {
+        const int row = prow0 + p;
+        float xv = sm.xa[row];
+        float yv = __fadd_rn(sm.yout[row], __fmul_rn(a.dskip[h], xv));   // model.rs:367-368
+        yv = __fmul_rn(yv, sm.gate[row]);                                // model.rs:370
+        const size_t o = (size_t)b * DI + h * P + row;
         if (a.y32) a.y32[o] = yv;
         if (a.yhi) {
             __nv_bfloat16 hh, ll;
@@ -362,9 +432,10 @@ __global__ void __launch_bounds__(256, 2) ssm_step_kernel(SsmArgs a) {
             a.yhi[o] = hh;
             if (a.ylo) a.ylo[o] = ll;
         }
-        a.xprev[bh * P + p] = xv;
+        a.xprev[bh * P + row] = xv;
     }
-    for (int s = lane; s < N; s += 32) a.bprev[bh * N + s] = sm.bt[s];
+    if (sub == 0)
+        for (int s2 = lane; s2 < N; s2 += 32) a.bprev[bh * N + s2] = sm.bt[s2];
 }
 
 // h <- h_init broadcast over head_dim (model.rs:744-748); factors and angles <- 0 (:751-752)
@@ -578,9 +649,18 @@ static cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_
 
 cudaError_t launch_embed(const void* emb, int dtype, const uint32_t* tok_cur, float* x, int B, int D, int vocab,
                          StepCtl* ctl, cudaStream_t st) {
+    // The first kernel of a step is never launched early: it starts only when the previous step has
+    // completely finished, which is what lets later kernels of this step read state ahead of their
+    // own dependency wait.
+    const bool keep = g_pdl;
+    g_pdl = false;
+    cudaError_t e;
     if (dtype == LUMI_DTYPE_BF16)
-        return launch_k(embed_kernel<__nv_bfloat16>, dim3(B), dim3(128), 0, st, (const __nv_bfloat16*)emb, tok_cur, x, D, vocab, ctl);
-    return launch_k(embed_kernel<float>, dim3(B), dim3(128), 0, st, (const float*)emb, tok_cur, x, D, vocab, ctl);
+        e = launch_k(embed_kernel<__nv_bfloat16>, dim3(B), dim3(128), 0, st, (const __nv_bfloat16*)emb, tok_cur, x, D, vocab, ctl);
+    else
+        e = launch_k(embed_kernel<float>, dim3(B), dim3(128), 0, st, (const float*)emb, tok_cur, x, D, vocab, ctl);
+    g_pdl = keep;
+    return e;
 }
 
 cudaError_t launch_norm_split(const float* x, const float* gamma, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int D,
@@ -588,17 +668,29 @@ cudaError_t launch_norm_split(const float* x, const float* gamma, __nv_bfloat16*
     return launch_k(norm_split_kernel, dim3(B), dim3(256), 0, st, x, gamma, hi, lo, D, eps);
 }
 
-template <typename WT, int NB, int ACT>
-static cudaError_t gemv_dispatch(const GemvArgs& a, cudaStream_t st) {
-    constexpr int RPW = (ACT == 1 || NB > 4) ? 1 : 2;
+template <typename WT, int NB, int RPW, int ACT>
+static cudaError_t gemv_launch(const GemvArgs& a, int KS, cudaStream_t st) {
     auto kern = gemv_kernel<WT, NB, RPW, ACT>;
     size_t smem = (size_t)NB * a.K * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    dim3 grid((a.N + 8 * RPW - 1) / (8 * RPW), (a.M + NB - 1) / NB);
-    return launch_k(kern, grid, dim3(256), smem, st, a.A, a.lda, (const WT*)a.W, a.D, a.ldd, a.R, a.gamma, a.M, a.N, a.K, a.eps);
+    const int rows_per_cta = (8 / KS) * RPW;
+    dim3 grid((a.N + rows_per_cta - 1) / rows_per_cta, (a.M + NB - 1) / NB);
+    return launch_k(kern, grid, dim3(256), smem, st, a.A, a.lda, (const WT*)a.W, a.D, a.ldd, a.R, a.gamma, a.M, a.N, a.K, a.eps, KS);
+}
+
+template <typename WT, int NB, int ACT>
+static cudaError_t gemv_dispatch(const GemvArgs& a, cudaStream_t st) {
+    constexpr int E = WLoad<WT>::E;
+    const int kseg = 32 * kGemvU * E;
+    int KS = 1;
+    while (KS < 8 && KS * kseg < a.K) KS *= 2;
+    if (KS * kseg < a.K) return cudaErrorInvalidValue;          // K beyond 8 segments per row
+    // two rows per warp only when that still leaves at least two CTAs per SM
+    if (ACT == 0 && NB <= 4 && (long)a.N / ((8 / KS) * 2) >= 296) return gemv_launch<WT, NB, 2, ACT>(a, KS, st);
+    return gemv_launch<WT, NB, 1, ACT>(a, KS, st);
 }
 
 template <typename WT>
@@ -625,10 +717,17 @@ bool ssm_shape_supported(int P, int N) {
 
 template <int P, int N>
 static cudaError_t ssm_launch(const SsmArgs& a, cudaStream_t st) {
-    int hpb = a.B <= 4 ? 2 : 8;
-    if (hpb > a.H) hpb = a.H;
+    constexpr int IT = P / (128 / N);
+    if constexpr (IT % 4 == 0) {
+        if (a.B <= 8) {        // small batch: four warps per head, two heads per CTA
+            int hpb = a.H < 2 ? a.H : 2;
+            dim3 grid((a.H + hpb - 1) / hpb, a.B);
+            return launch_k(ssm_step_kernel<P, N, 4>, grid, dim3(hpb * 4 * 32), 0, st, a);
+        }
+    }
+    int hpb = a.H < 8 ? a.H : 8;
     dim3 grid((a.H + hpb - 1) / hpb, a.B);
-    return launch_k(ssm_step_kernel<P, N>, grid, dim3(hpb * 32), 0, st, a);
+    return launch_k(ssm_step_kernel<P, N, 1>, grid, dim3(hpb * 32), 0, st, a);
 }
 
 cudaError_t launch_ssm_step(const SsmArgs& a, cudaStream_t st) {
