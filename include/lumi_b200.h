@@ -120,7 +120,10 @@ void    lumi_session_free(lumi_session* s);
  *                         halves of each fp32 activation, 0 rounds activations to bf16 once;
  *                         "graph" = 1 (default) replays the decode step as a CUDA graph;
  *                         "pdl" = 1 (default) launches the weight-streaming kernels with programmatic
- *                         dependent launch so each one prefetches its weights while its predecessor runs. */
+ *                         dependent launch so each one prefetches its weights while its predecessor runs;
+ *                         "megakernel" = 1 runs batch-1 calls on Mamba-only models (head_dim 32, d_state 64) as
+ *                         one persistent cooperative kernel per call (default 0: measured on par with the
+ *                         graph-replayed kernel chain, which needs no device-side waits). */
 int32_t lumi_session_set_option(lumi_session* s, const char* name, int64_t value);
 
 /* ---- token loop: replaces NmModel::forward_step (inference/src/model.rs:766-801) and the

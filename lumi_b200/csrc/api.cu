@@ -336,7 +336,8 @@ extern "C" void lumi_session_free(lumi_session* s) {
     if (s->stream) cudaStreamSynchronize(s->stream);
     for (auto& g : s->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
     void* dev[] = {s->h, s->xprev, s->bprev, s->cum, s->kv_pool, s->page_table, s->kv_pos, s->x, s->proj, s->y32, s->logits,
-                   s->act_hi, s->act_lo, s->tok_cur, s->finished, s->out_len, s->ctl, s->gen_out, s->prompt_dev, s->gen_dump};
+                   s->act_hi, s->act_lo, s->tok_cur, s->finished, s->out_len, s->ctl, s->gen_out, s->prompt_dev, s->gen_dump,
+                   s->b1_layers, s->b1_grid_ctl, s->b1_amax_val, s->b1_amax_idx, s->b1_timing, s->b1_tagged};
     for (void* p : dev) if (p) cudaFree(p);
     if (s->ctl_host) cudaFreeHost(s->ctl_host);
     if (s->pin_tokens) cudaFreeHost(s->pin_tokens);
@@ -396,6 +397,26 @@ static int32_t session_alloc(lumi_session* s) {
     LUMI_CUDA(cudaMallocHost(&s->pin_tokens, sizeof(uint32_t) * B));
     memset(s->ctl_host, 0, sizeof(StepCtl));
     LUMI_CUDA(cudaMemset(s->tok_cur, 0, sizeof(uint32_t) * B));
+    // batch-1 persistent kernel: per-layer pointer table, barrier words, argmax partials
+    s->b1_ok = decode_b1_supported(c, na, s->m->device);
+    if (s->b1_ok) {
+        std::vector<B1Layer> tab;
+        for (const Layer& L : s->m->layers) {
+            const size_t l = L.kind_idx;
+            B1Layer t{L.m.in_proj.p, L.m.out_proj.p, L.m.norm_g, L.m.b_gamma, L.m.c_gamma, L.m.b_bias, L.m.c_bias, L.m.d_skip, L.m.dt_bias,
+                      s->h + l * B * state_h_per_seq(c), s->xprev + l * B * c.d_inner(), s->bprev + l * B * c.n_heads * c.d_state,
+                      s->cum + l * B * c.n_heads * (c.d_state / 2)};
+            tab.push_back(t);
+        }
+        LUMI_CUDA(cudaMalloc(&s->b1_layers, sizeof(B1Layer) * tab.size()));
+        LUMI_CUDA(cudaMemcpy(s->b1_layers, tab.data(), sizeof(B1Layer) * tab.size(), cudaMemcpyHostToDevice));
+        LUMI_CUDA(cudaMalloc(&s->b1_grid_ctl, 64));
+        LUMI_CUDA(cudaMalloc(&s->b1_amax_val, sizeof(float) * 1024));
+        LUMI_CUDA(cudaMalloc(&s->b1_amax_idx, sizeof(int) * 1024));
+        const size_t ntag = (size_t)c.d_model + c.in_proj_out() + c.d_inner();
+        LUMI_CUDA(cudaMalloc(&s->b1_tagged, ntag * 8));
+        LUMI_CUDA(cudaMemset(s->b1_tagged, 0, ntag * 8));          // epoch 0 is never used
+    }
     return LUMI_OK;
 }
 
@@ -411,6 +432,7 @@ extern "C" int32_t lumi_session_create(lumi_model* m, int32_t max_batch, int32_t
     s->max_tokens_kv = max_tokens_kv;
     if (const char* e = getenv("LUMI_PDL")) s->opt_pdl = atoi(e) ? 1 : 0;       // default for new sessions
     if (const char* e = getenv("LUMI_GRAPH")) s->opt_graph = atoi(e) ? 1 : 0;
+    if (const char* e = getenv("LUMI_MEGAKERNEL")) s->opt_mega = atoi(e) ? 1 : 0;
     int32_t st = session_alloc(s);
     if (st == LUMI_OK) st = lumi_session_reset(s, nullptr, 0);
     if (st != LUMI_OK) {
@@ -465,6 +487,7 @@ extern "C" int32_t lumi_session_set_option(lumi_session* s, const char* name, in
     else if (n == "split_activations") s->opt_split = value ? 1 : 0;
     else if (n == "graph") s->opt_graph = value ? 1 : 0;
     else if (n == "pdl") s->opt_pdl = value ? 1 : 0;
+    else if (n == "megakernel") s->opt_mega = value ? 1 : 0;
     else return fail(LUMI_E_INVALID, "unknown option '%s'", name);
     for (auto& g : s->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);   // captured choices are stale
     s->graphs.clear();
@@ -670,9 +693,85 @@ int32_t run_step(lumi_session* s, int B, bool with_head) {
     return LUMI_OK;
 }
 
+bool use_b1(const lumi_session* s, int batch) { return batch == 1 && s->b1_ok && s->opt_mega; }
+
+// n_tokens forward steps of sequence 0 in one persistent kernel (decode_b1.cu)
+int32_t run_b1(lumi_session* s, int n_tokens, int head_mode, int do_argmax) {
+    if (n_tokens <= 0) return LUMI_OK;
+    const Config& c = s->m->cfg;
+    B1Args a{};
+    a.layers = s->b1_layers; a.n_layers = c.n_layers;
+    a.emb = s->m->embedding.p; a.final_g = s->m->final_norm_g;
+    a.vocab = c.vocab; a.D = c.d_model; a.DI = c.d_inner(); a.R = c.in_proj_out(); a.H = c.n_heads; a.G = c.n_groups; a.BC = c.bc();
+    a.eps = c.eps;
+    a.xt = s->b1_tagged; a.pt = a.xt + c.d_model; a.yt = a.pt + c.in_proj_out();
+    a.logits = s->logits;
+    // epochs never repeat within a session: (layers + 1) per token, and a margin per launch
+    const uint64_t need = (uint64_t)n_tokens * (c.n_layers + 1) + 2;
+    if ((uint64_t)s->b1_epoch + need >= 0xffffff00ull) {
+        LUMI_CUDA(cudaMemsetAsync(s->b1_tagged, 0, ((size_t)c.d_model + c.in_proj_out() + c.d_inner()) * 8, s->stream));
+        s->b1_epoch = 1;
+    }
+    a.epoch_base = s->b1_epoch;
+    s->b1_epoch += (uint32_t)need;
+    a.tok_cur = s->tok_cur; a.finished = s->finished; a.out_len = s->out_len;
+    a.ctl = s->ctl;
+    a.grid_ctl = s->b1_grid_ctl; a.amax_val = s->b1_amax_val; a.amax_idx = s->b1_amax_idx;
+    a.n_tokens = n_tokens; a.head_mode = head_mode; a.do_argmax = do_argmax;
+    // LUMI_B1_TIMING=1 (tuning aid): per-phase timestamps of the last token, printed to stderr
+    static const bool want_timing = getenv("LUMI_B1_TIMING") && atoi(getenv("LUMI_B1_TIMING"));
+    if (want_timing && !s->b1_timing) {
+        LUMI_CUDA(cudaMalloc(&s->b1_timing, sizeof(unsigned long long) * 2 * c.n_layers * 10));
+    }
+    a.timing = want_timing ? s->b1_timing : nullptr;
+    if (want_timing) LUMI_CUDA(cudaMemsetAsync(s->b1_timing, 0, sizeof(unsigned long long) * 2 * c.n_layers * 10, s->stream));
+    LUMI_CUDA(launch_decode_b1(a, s->m->wdtype, s->m->device, s->stream));
+    s->launches += 1;
+    if (want_timing && n_tokens > 1) {
+        std::vector<unsigned long long> tm((size_t)2 * c.n_layers * 10);
+        LUMI_CUDA(cudaMemcpyAsync(tm.data(), s->b1_timing, tm.size() * 8, cudaMemcpyDeviceToHost, s->stream));
+        LUMI_CUDA(cudaStreamSynchronize(s->stream));
+        static const char* names[9] = {"gatherX", "rowsA", "-", "pollB", "stepB", "-", "gatherY", "rowsC", "sync"};
+        for (int sel = 0; sel < 2; ++sel) {
+            double acc[9] = {0};
+            int n = 0;
+            for (int l = 1; l < c.n_layers; ++l) {
+                const unsigned long long* r = &tm[((size_t)sel * c.n_layers + l) * 10];
+                if (!r[0] || !r[9]) continue;
+                unsigned long long prev = r[0];
+                for (int i = 1; i < 10; ++i) {
+                    if (!r[i]) continue;           // stamps a CTA without a head never writes
+                    acc[i - 1] += (double)(r[i] - prev);
+                    prev = r[i];
+                }
+                ++n;
+            }
+            fprintf(stderr, "[b1 timing] CTA %d, mean ns per layer over %d layers:", sel == 0 ? 0 : 100, n);
+            double tot = 0;
+            for (int i = 0; i < 9; ++i) { fprintf(stderr, " %s %.0f", names[i], n ? acc[i] / n : 0.0); tot += n ? acc[i] / n : 0.0; }
+            fprintf(stderr, " | layer %.0f\n", tot);
+        }
+    }
+    return LUMI_OK;
+}
+
+// after run_b1(..., do_argmax = 0): temperature / top-k sampling of the logits it left behind
+int32_t sample_after_b1(lumi_session* s) {
+    const Config& c = s->m->cfg;
+    LUMI_CUDA(launch_sample(s->logits, 1, c.vocab, s->ctl, s->tok_cur, s->finished, s->out_len, s->stream));
+    LUMI_CUDA(launch_advance_step(s->ctl, nullptr, 1, 1, s->stream));
+    s->launches += 2;
+    return LUMI_OK;
+}
+
 int32_t check_status(lumi_session* s) {
     const int st = s->ctl_host->status;
-    if (st & STATUS_TIMEOUT) return fail(LUMI_E_TIMEOUT, "a bounded device-side wait expired inside the tensor-core GEMM");
+    if (st & STATUS_TIMEOUT) {
+        unsigned words[8] = {0};
+        if (s->b1_grid_ctl) cudaMemcpy(words, s->b1_grid_ctl, sizeof(words), cudaMemcpyDeviceToHost);
+        return fail(LUMI_E_TIMEOUT, "a bounded device-side wait expired (tensor-core GEMM or persistent decode kernel; barrier words %u %u %u %u %u %u abort %u diag 0x%x)",
+                    words[0], words[1], words[2], words[3], words[4], words[5], words[6], words[7]);
+    }
     if (st & STATUS_BAD_TOKEN) return fail(LUMI_E_TOKEN, "a token id was >= vocab_size (%d)", s->m->cfg.vocab);
     if (st & STATUS_KV_FULL) return fail(LUMI_E_KV_FULL, "attention cache capacity (%d tokens per sequence) exceeded", s->max_tokens_kv);
     return LUMI_OK;
@@ -739,7 +838,9 @@ extern "C" int32_t lumi_prefill(lumi_session* s, const uint32_t* tokens, int32_t
     s->ctl_host->prompt = s->prompt_dev;
     s->ctl_host->prompt_len = T;
     LUMI_TRY(push_ctl(s));
-    for (int t = 0; t < T; ++t) LUMI_TRY(run_step(s, batch, last_logits != nullptr && t == T - 1));
+    if (use_b1(s, batch)) LUMI_TRY(run_b1(s, T, last_logits != nullptr ? 1 : 0, 1));
+    else
+        for (int t = 0; t < T; ++t) LUMI_TRY(run_step(s, batch, last_logits != nullptr && t == T - 1));
     if (last_logits)
         LUMI_CUDA(cudaMemcpyAsync(last_logits, s->logits, sizeof(float) * batch * s->m->cfg.vocab, cudaMemcpyDeviceToHost, s->stream));
     LUMI_TRY(pull_ctl(s));
@@ -757,7 +858,13 @@ extern "C" int32_t lumi_decode_step(lumi_session* s, const uint32_t* in_tokens, 
     LUMI_TRY(push_ctl(s));
     memcpy(s->pin_tokens, in_tokens, sizeof(uint32_t) * batch);
     LUMI_CUDA(cudaMemcpyAsync(s->tok_cur, s->pin_tokens, sizeof(uint32_t) * batch, cudaMemcpyHostToDevice, s->stream));
-    LUMI_TRY(run_step(s, batch, true));
+    if (use_b1(s, batch)) {
+        const bool greedy = !sp || sp->temperature <= 0.f;
+        LUMI_TRY(run_b1(s, 1, 1, greedy ? 1 : 0));
+        if (!greedy) LUMI_TRY(sample_after_b1(s));
+    } else {
+        LUMI_TRY(run_step(s, batch, true));
+    }
     LUMI_CUDA(cudaMemcpyAsync(s->pin_tokens, s->tok_cur, sizeof(uint32_t) * batch, cudaMemcpyDeviceToHost, s->stream));
     if (logits_out)
         LUMI_CUDA(cudaMemcpyAsync(logits_out, s->logits, sizeof(float) * batch * s->m->cfg.vocab, cudaMemcpyDeviceToHost, s->stream));
@@ -792,9 +899,22 @@ extern "C" int32_t lumi_generate(lumi_session* s, const uint32_t* prompts, int32
     LUMI_CUDA(cudaEventRecord(s->ev0, s->stream));
     // main.rs:121-125: the prompt goes through forward_step token by token; the last position's
     // logits give generated token 0
-    for (int t = 0; t < T; ++t) LUMI_TRY(run_step(s, batch, n_new > 0 && t == T - 1));
+    const bool b1 = use_b1(s, batch);
+    const bool greedy = sp->temperature <= 0.f;
+    if (b1) {
+        LUMI_TRY(run_b1(s, T, n_new > 0 ? 1 : 0, greedy ? 1 : 0));
+        if (n_new > 0 && !greedy) LUMI_TRY(sample_after_b1(s));
+    } else {
+        for (int t = 0; t < T; ++t) LUMI_TRY(run_step(s, batch, n_new > 0 && t == T - 1));
+    }
     LUMI_CUDA(cudaEventRecord(s->ev1, s->stream));
-    for (int i = 1; i < n_new; ++i) LUMI_TRY(run_step(s, batch, true));      // main.rs:136-170
+    if (b1 && greedy) {
+        LUMI_TRY(run_b1(s, n_new - 1, 1, 1));                                // main.rs:136-170, all tokens in one launch
+    } else if (b1) {
+        for (int i = 1; i < n_new; ++i) { LUMI_TRY(run_b1(s, 1, 1, 0)); LUMI_TRY(sample_after_b1(s)); }
+    } else {
+        for (int i = 1; i < n_new; ++i) LUMI_TRY(run_step(s, batch, true));      // main.rs:136-170
+    }
     LUMI_CUDA(cudaEventRecord(s->ev2, s->stream));
     std::vector<uint32_t> tmp((size_t)n_new * batch);
     if (n_new > 0) LUMI_CUDA(cudaMemcpyAsync(tmp.data(), s->gen_out, tmp.size() * sizeof(uint32_t), cudaMemcpyDeviceToHost, s->stream));
@@ -831,7 +951,9 @@ extern "C" int32_t lumi_decode_loop_device(lumi_session* s, int32_t batch, int32
     LUMI_TRY(push_ctl(s));
     const int64_t l0 = s->launches;
     LUMI_CUDA(cudaEventRecord(s->ev0, s->stream));
-    for (int i = 0; i < n_steps; ++i) LUMI_TRY(run_step(s, batch, true));
+    if (use_b1(s, batch)) LUMI_TRY(run_b1(s, n_steps, 1, 1));
+    else
+        for (int i = 0; i < n_steps; ++i) LUMI_TRY(run_step(s, batch, true));
     LUMI_CUDA(cudaEventRecord(s->ev1, s->stream));
     LUMI_TRY(pull_ctl(s));
     LUMI_CUDA(cudaStreamSynchronize(s->stream));

@@ -127,13 +127,24 @@ struct GraphEntry {
 
 }  // namespace lumi
 
+namespace lumi { struct B1Layer; }
+
 struct lumi_session {
     lumi_model* m = nullptr;
     int max_batch = 0, max_tokens_kv = 0;
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;
     // options
-    int opt_gemm = 0, opt_split = 1, opt_graph = 1, opt_pdl = 1;
+    int opt_gemm = 0, opt_split = 1, opt_graph = 1, opt_pdl = 1, opt_mega = 0;
+    // batch-1 persistent kernel
+    bool b1_ok = false;
+    lumi::B1Layer* b1_layers = nullptr;
+    void* b1_grid_ctl = nullptr;
+    float* b1_amax_val = nullptr;
+    int* b1_amax_idx = nullptr;
+    unsigned long long* b1_timing = nullptr;
+    unsigned long long* b1_tagged = nullptr;   // xt | pt | yt
+    uint32_t b1_epoch = 1;
     // state, per Mamba layer l: base + l * max_batch * per-sequence size
     float *h = nullptr, *xprev = nullptr, *bprev = nullptr, *cum = nullptr;
     // attention cache: pool of pages of kPageTokens tokens, [n_attn][pages][2][kPageTokens][kv_dim] bf16
@@ -235,6 +246,33 @@ struct GemmArgs {
 };
 int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st);   // returns LUMI_* status
 int32_t gemm_tcgen05_init();                                        // resolves the driver entry point
+
+// ---- batch-1 persistent decode kernel (decode_b1.cu) ---------------------------------------------
+struct B1Layer {
+    const void *in_proj, *out_proj;
+    const float *norm_g, *bg, *cg, *bb, *cb, *dskip, *dtb;
+    float *h, *xprev, *bprev, *cum;          // slot 0 of this layer's state
+};
+struct B1Args {
+    const B1Layer* layers; int n_layers;
+    const void* emb; const float* final_g;
+    int vocab, D, DI, R, H, G, BC;
+    float eps;
+    unsigned long long *xt, *pt, *yt;        // epoch-tagged activations: [D], [R], [DI]
+    uint32_t epoch_base;                     // epochs used by this launch start at epoch_base (+1 per layer, token, ...)
+    float* logits;
+    uint32_t* tok_cur;
+    int32_t *finished, *out_len;
+    StepCtl* ctl;
+    void* grid_ctl;                          // 32 bytes of barrier counters, zeroed per launch
+    float* amax_val; int* amax_idx;          // [grid] argmax partials
+    int n_tokens;
+    int head_mode;                           // 0: never run the lm_head; 1: at the last prompt position and every decode position
+    int do_argmax;                           // 1: pick the greedy token on the device and advance the step counter
+    unsigned long long* timing;              // optional: [2][n_layers][10] globaltimer stamps of the last token (CTA 0 and CTA 100)
+};
+bool decode_b1_supported(const Config& c, int n_attn, int device);
+cudaError_t launch_decode_b1(const B1Args& a, int w_dtype, int device, cudaStream_t st);
 
 cudaError_t launch_gate_mul(const float* gu, int ld, float* out32, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int mlp,
                             cudaStream_t st);

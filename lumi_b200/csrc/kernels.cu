@@ -10,6 +10,7 @@
 
 #include <cfloat>
 #include <cmath>
+#include <cstdlib>
 
 namespace lumi {
 
@@ -20,11 +21,6 @@ namespace {
 // Without the attribute both instructions are no-ops.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-// Pulls `bytes` (multiple of 16, 16-byte aligned) into L2 ahead of use.
-__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -189,13 +185,26 @@ __global__ void __launch_bounds__(256) gemv_kernel(const float* __restrict__ A, 
     }
     __syncthreads();
     if (gamma != nullptr) {
-        for (int b = warp; b < nb; b += 8) {
-            float* xr = xs + b * K;
+        // RMSNorm of the NB staged rows by the whole CTA: per-thread partials in ascending k, xor tree,
+        // then the 8 warp sums in warp order
+        __shared__ float nred[NB][8];
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
             float s = 0.f;
-            for (int k = lane; k < K; k += 32) s = fmaf(xr[k], xr[k], s);
+            if (b < nb) for (int k = threadIdx.x; k < K; k += 256) s = fmaf(xs[b * K + k], xs[b * K + k], s);
             s = warp_sum(s);
-            float r = rms_scale(s, K, eps);
-            for (int k = lane; k < K; k += 32) xr[k] = __fmul_rn(__fmul_rn(xr[k], r), gamma[k]);
+            if (lane == 0) nred[b][warp] = s;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            if (b < nb) {
+                float t = 0.f;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) t += nred[b][w];
+                const float r = rms_scale(t, K, eps);
+                for (int k = threadIdx.x; k < K; k += 256) xs[b * K + k] = __fmul_rn(__fmul_rn(xs[b * K + k], r), gamma[k]);
+            }
         }
         __syncthreads();
     }
@@ -279,8 +288,8 @@ struct SsmSmem {
 // WPH warps share one head: each owns P / WPH consecutive state rows.  WPH = 1 at large batch (a
 // warp streams a whole 8 KiB tile); WPH = 4 at small batch, where the tile compute of one warp
 // would otherwise sit on the critical path of the token.
-template <int P, int N, int WPH>
-__global__ void __launch_bounds__(256, 2) ssm_step_kernel(SsmArgs a) {
+template <int P, int N, int WPH, int MINB>
+__global__ void __launch_bounds__(256, MINB) ssm_step_kernel(SsmArgs a) {
     __shared__ SsmSmem<P, N> sm_all[8];
     __shared__ float red[2][8];
     constexpr int CG = N / 4;              // lanes sharing one state row
@@ -326,6 +335,32 @@ __global__ void __launch_bounds__(256, 2) ssm_step_kernel(SsmArgs a) {
     const float* lam_raw = dt + H;
     const float* dda = dt + 2 * H;
     const float* theta = dt + 3 * H;
+    const int hh = active ? h : H - 1;
+    const int g = hh / (H / a.G);
+
+    // every global value the prologue needs is requested here, ahead of the block barrier, so the
+    // loads overlap instead of forming a chain of round trips
+    const float v_dt = dt[hh], v_dtb = a.dtb[hh], v_dda = dda[hh], v_lam = lam_raw[hh], v_dskip = a.dskip[hh];
+    constexpr int NJ = (N / 2 + 31) / 32;
+    float v_th[NJ], v_b0[NJ], v_b1[NJ], v_c0[NJ], v_c1[NJ], g_b0[NJ], g_b1[NJ], g_c0[NJ], g_c1[NJ], o_b0[NJ], o_b1[NJ], o_c0[NJ], o_c1[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        const int k = min(lane + 32 * j, HN - 1);
+        const int i0 = g * N + 2 * k;
+        v_th[j] = theta[hh * HN + k];
+        v_b0[j] = Bp[i0]; v_b1[j] = Bp[i0 + 1]; v_c0[j] = Cp[i0]; v_c1[j] = Cp[i0 + 1];
+        g_b0[j] = a.bg[i0]; g_b1[j] = a.bg[i0 + 1]; g_c0[j] = a.cg[i0]; g_c1[j] = a.cg[i0 + 1];
+        o_b0[j] = a.bb[i0]; o_b1[j] = a.bb[i0 + 1]; o_c0[j] = a.cb[i0]; o_c1[j] = a.cb[i0 + 1];
+    }
+    constexpr int ROWS_PL = (P / WPH + 31) / 32;
+    float v_x[ROWS_PL], v_z[ROWS_PL], v_xp[ROWS_PL];
+#pragma unroll
+    for (int j = 0; j < ROWS_PL; ++j) {
+        const int row = min(sub * ROWS + lane + 32 * j, P - 1);
+        v_x[j] = pr[hh * P + row];
+        v_z[j] = pr[DI + hh * P + row];
+        v_xp[j] = a.xprev[bh * P + row];
+    }
 
     // BCNorm statistics (model.rs:311-312: the norm runs over the whole bc vector)
     float sb = 0.f, sc = 0.f;
@@ -338,7 +373,7 @@ __global__ void __launch_bounds__(256, 2) ssm_step_kernel(SsmArgs a) {
     sb = warp_sum(sb);
     sc = warp_sum(sc);
     if (lane == 0) { red[0][warp] = sb; red[1][warp] = sc; }
-    __syncthreads();       // also orders every warp's reads of bprev / cum above before the writes below
+    __syncthreads();       // also orders every warp's reads of bprev / cum / xprev above before the writes below
     if (!active) return;
     float tb = 0.f, tc = 0.f;
     for (int w = 0; w < nwarp; ++w) { tb += red[0][w]; tc += red[1][w]; }
@@ -347,32 +382,30 @@ __global__ void __launch_bounds__(256, 2) ssm_step_kernel(SsmArgs a) {
     SsmSmem<P, N>& sm = sm_all[warp];
 
     // per-head scalars (model.rs:307, 314-317, 355-359)
-    const float dtp = softplus_ref(__fadd_rn(dt[h], a.dtb[h]));
-    float av = -softplus_ref(dda[h]);
+    const float dtp = softplus_ref(__fadd_rn(v_dt, v_dtb));
+    float av = -softplus_ref(v_dda);
     av = fminf(fmaxf(av, -1e6f), -1e-4f);
     const float abar = expf(__fmul_rn(av, dtp));
-    const float lam = sigmoid_ref(lam_raw[h]);
+    const float lam = sigmoid_ref(v_lam);
     const float oml = __fadd_rn(__fmul_rn(lam, -1.0f), 1.0f);
     const float c2 = __fmul_rn(abar, oml);
-    const int g = h / (H / a.G);
 
     // DD-RoPE (model.rs:338-350): lane k rotates pair (2k, 2k+1) of the normalised B and C
     const float PI_F = 3.14159265358979323846f;
     const float TWO_PI = __fmul_rn(2.0f, PI_F);
 #pragma unroll
-    for (int j = 0; j < (HN + 31) / 32; ++j) {
+    for (int j = 0; j < NJ; ++j) {
         const int k = lane + 32 * j;
         if (k < HN) {
-            float angle = __fmul_rn(tanhf(theta[h * HN + k]), PI_F);
+            float angle = __fmul_rn(tanhf(v_th[j]), PI_F);
             float cu = fmodf(__fadd_rn(cu_old[j], __fmul_rn(dtp, angle)), TWO_PI);
             if (sub == 0) a.cum[bh * HN + k] = cu;
             float sa, ca;
             sincosf(cu, &sa, &ca);
-            const int i0 = g * N + 2 * k;
-            float b0 = __fadd_rn(__fmul_rn(__fmul_rn(Bp[i0], rb), a.bg[i0]), a.bb[i0]);
-            float b1 = __fadd_rn(__fmul_rn(__fmul_rn(Bp[i0 + 1], rb), a.bg[i0 + 1]), a.bb[i0 + 1]);
-            float c0 = __fadd_rn(__fmul_rn(__fmul_rn(Cp[i0], rc), a.cg[i0]), a.cb[i0]);
-            float c1 = __fadd_rn(__fmul_rn(__fmul_rn(Cp[i0 + 1], rc), a.cg[i0 + 1]), a.cb[i0 + 1]);
+            float b0 = __fadd_rn(__fmul_rn(__fmul_rn(v_b0[j], rb), g_b0[j]), o_b0[j]);
+            float b1 = __fadd_rn(__fmul_rn(__fmul_rn(v_b1[j], rb), g_b1[j]), o_b1[j]);
+            float c0 = __fadd_rn(__fmul_rn(__fmul_rn(v_c0[j], rc), g_c0[j]), o_c0[j]);
+            float c1 = __fadd_rn(__fmul_rn(__fmul_rn(v_c1[j], rc), g_c1[j]), o_c1[j]);
             sm.bt[2 * k] = __fsub_rn(__fmul_rn(ca, b0), __fmul_rn(sa, b1));
             sm.bt[2 * k + 1] = __fadd_rn(__fmul_rn(sa, b0), __fmul_rn(ca, b1));
             sm.ct[2 * k] = __fsub_rn(__fmul_rn(ca, c0), __fmul_rn(sa, c1));
@@ -380,11 +413,15 @@ __global__ void __launch_bounds__(256, 2) ssm_step_kernel(SsmArgs a) {
         }
     }
     const int prow0 = sub * ROWS;          // first state row of this warp
-    for (int p = lane; p < ROWS; p += 32) {
-        const int row = prow0 + p;
-        sm.xa[row] = silu_ref(pr[h * P + row]);             // model.rs:310
-        sm.xp[row] = a.xprev[bh * P + row];
-        sm.gate[row] = silu_ref(pr[DI + h * P + row]);      // model.rs:370
+#pragma unroll
+    for (int j = 0; j < ROWS_PL; ++j) {
+        const int p = lane + 32 * j;
+        if (p < ROWS) {
+            const int row = prow0 + p;
+            sm.xa[row] = silu_ref(v_x[j]);                  // model.rs:310
+            sm.xp[row] = v_xp[j];
+            sm.gate[row] = silu_ref(v_z[j]);                // model.rs:370
+        }
     }
     __syncwarp();
 
@@ -422,7 +459,7 @@ __global__ void __launch_bounds__(256, 2) ssm_step_kernel(SsmArgs a) {
     for (int p = lane; p < ROWS; p += 32) {
         const int row = prow0 + p;
         float xv = sm.xa[row];
-        float yv = __fadd_rn(sm.yout[row], __fmul_rn(a.dskip[h], xv));   // model.rs:367-368
+        float yv = __fadd_rn(sm.yout[row], __fmul_rn(v_dskip, xv));   // model.rs:367-368
         yv = __fmul_rn(yv, sm.gate[row]);                                // model.rs:370
         const size_t o = (size_t)b * DI + h * P + row;
         if (a.y32) a.y32[o] = yv;
@@ -715,6 +752,22 @@ bool ssm_shape_supported(int P, int N) {
     return (P == 16 || P == 32 || P == 64) && (N == 16 || N == 32 || N == 64 || N == 128);
 }
 
+template <int P, int N, int WPH, int MINB>
+static cudaError_t ssm_variant(const SsmArgs& a, cudaStream_t st) {
+    int hpb = 8 / WPH;
+    if (hpb > a.H) hpb = a.H;
+    dim3 grid((a.H + hpb - 1) / hpb, a.B);
+    return launch_k(ssm_step_kernel<P, N, WPH, MINB>, grid, dim3(hpb * WPH * 32), 0, st, a);
+}
+
+// LUMI_SSM_VARIANT (tuning aid): warps per head x minimum resident blocks per SM for the
+// large-batch launch of the 32 x 64 tile; 0 / unset = the default choice.
+static int ssm_variant_env() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("LUMI_SSM_VARIANT"); v = e ? atoi(e) : 0; }
+    return v;
+}
+
 template <int P, int N>
 static cudaError_t ssm_launch(const SsmArgs& a, cudaStream_t st) {
     constexpr int IT = P / (128 / N);
@@ -722,12 +775,21 @@ static cudaError_t ssm_launch(const SsmArgs& a, cudaStream_t st) {
         if (a.B <= 8) {        // small batch: four warps per head, two heads per CTA
             int hpb = a.H < 2 ? a.H : 2;
             dim3 grid((a.H + hpb - 1) / hpb, a.B);
-            return launch_k(ssm_step_kernel<P, N, 4>, grid, dim3(hpb * 4 * 32), 0, st, a);
+            return launch_k(ssm_step_kernel<P, N, 4, 3>, grid, dim3(hpb * 4 * 32), 0, st, a);
         }
     }
-    int hpb = a.H < 8 ? a.H : 8;
-    dim3 grid((a.H + hpb - 1) / hpb, a.B);
-    return launch_k(ssm_step_kernel<P, N, 1>, grid, dim3(hpb * 32), 0, st, a);
+    if constexpr (P == 32 && N == 64) {
+        switch (ssm_variant_env()) {
+            case 1: return ssm_variant<P, N, 1, 2>(a, st);
+            case 2: return ssm_variant<P, N, 2, 3>(a, st);
+            case 3: return ssm_variant<P, N, 2, 4>(a, st);
+            case 4: return ssm_variant<P, N, 4, 4>(a, st);
+            case 5: return ssm_variant<P, N, 4, 3>(a, st);
+            case 6: return ssm_variant<P, N, 1, 3>(a, st);
+            default: break;
+        }
+    }
+    return ssm_variant<P, N, 1, 2>(a, st);
 }
 
 cudaError_t launch_ssm_step(const SsmArgs& a, cudaStream_t st) {

@@ -94,7 +94,53 @@ def test_mamba_block_alone_base_dims():
     assert np.abs(cum - rcum).max() < 1e-5
 
 
-def test_config1_shape_fp32_greedy_parity():
+@pytest.mark.parametrize("wdt", ["f32", "bf16"])
+def test_batch1_persistent_kernel_and_chain_agree_with_oracle(wdt):
+    """Base dimensions, 3 layers, batch 1: the one-kernel-per-call path and the kernel-chain path
+    both against the oracle — tokens, logits, final state — greedy and sampled."""
+    cfg = synth.base_config(n_layers=3, vocab_size=1000)
+    tens = list(synth.iter_tensors(cfg, seed=5, weights_dtype=wdt, perturb_ones=0.05))
+    prompt = synth.random_prompts(1, 9, cfg.vocab_size, seed=2)[0]
+    n_new = 20
+    om = cpu_oracle.OracleModel(cfg, tens)
+    ost = om.init_states()
+    ref_toks, ref_logits = ost.generate(prompt, n_new, ignore_eos=True, dump_logits=True)
+    uniforms = np.array([nr.sampler_uniform(99, 0, i) for i in range(n_new)], dtype=np.float32)
+    ref_sampled = om.init_states().generate(prompt, n_new, temperature=0.7, top_k=8, uniforms=uniforms, ignore_eos=True)
+    model = lumi_b200.NmModel.from_tensors(cfg, tens)
+    for mega in (1, 0):
+        sess = model.init_states(1)
+        sess.set_option("megakernel", mega)
+        toks, lens, dump, st = sess.generate(prompt[None, :], n_new, ignore_eos=True, dump_logits=True)
+        worst = max(rel_err(dump[i, 0], ref_logits[i]) for i in range(n_new))
+        assert worst < TOL_F32, (mega, worst)
+        _compare_tokens(toks[0], ref_toks, ref_logits, f"megakernel={mega}")
+        assert lens[0] == n_new
+        # the device loop stops one forward_step before the oracle's loop: catch up, then compare state
+        sess.forward_step([int(toks[0, -1])])
+        for layer in range(cfg.n_layers):
+            h, xp, bp, cum = sess.read_state(0, layer)
+            rh, rpbx, rcum = ost.read_state(layer)
+            assert np.abs(h - rh).max() <= 1e-4 * max(1.0, np.abs(rh).max()), (mega, layer)
+            assert np.abs(cum - rcum).max() < 1e-4
+        sess.reset()
+        stoks, _, _, _ = sess.generate(prompt[None, :], n_new, temperature=0.7, top_k=8, seed=99, ignore_eos=True)
+        assert np.array_equal(stoks[0], ref_sampled), (mega, stoks[0], ref_sampled)
+        # eos handling on this path
+        sess.reset()
+        eos = int(ref_toks[5])
+        first = int(np.argmax(ref_toks == eos))
+        etoks, elens, _, _ = sess.generate(prompt[None, :], n_new, eos_id=eos)
+        assert elens[0] == first
+        # bad token id is reported, not followed
+        with pytest.raises(lumi_b200.LumiError) as e:
+            sess.forward_step([cfg.vocab_size + 1])
+        assert e.value.code == -8
+        sess.close()
+
+
+@pytest.mark.parametrize("mega", [1, 0])
+def test_config1_shape_fp32_greedy_parity(mega):
     """The base 48-layer fp32 model, batch 1, 32-token prompt: identical greedy ids for the first 64
     generated tokens and logits within 1e-3."""
     cfg = synth.base_config()
@@ -105,9 +151,10 @@ def test_config1_shape_fp32_greedy_parity():
     model = lumi_b200.NmModel.from_tensors(cfg, tens)
     del tens
     sess = model.init_states(1)
+    sess.set_option("megakernel", mega)
     toks, lens, dump, st = sess.generate(prompt[None, :], n_new, ignore_eos=True, dump_logits=True)
     worst = max(rel_err(dump[i, 0], ref_logits[i]) for i in range(n_new))
-    print(f"config-1 parity: worst logits rel err {worst:.3e}; min oracle top-2 margin "
+    print(f"config-1 parity (persistent kernel {mega}): worst logits rel err {worst:.3e}; min oracle top-2 margin "
           f"{min(top2_margin(l) for l in ref_logits):.3e}; decode {st.decode_tokens / st.ms_decode * 1e3:.0f} tok/s")
     assert worst < TOL_F32
     _compare_tokens(toks[0], ref_toks, ref_logits, "config 1")
