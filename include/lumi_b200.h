@@ -188,6 +188,30 @@ int32_t lumi_k_ssm_step(uint64_t proj, int32_t ldp, uint64_t b_gamma, uint64_t c
                         uint64_t d_skip, uint64_t dt_bias, uint64_t h, uint64_t x_prev, uint64_t b_prev, uint64_t cum_angle,
                         uint64_t y, int32_t B, int32_t H, int32_t P, int32_t N, int32_t G, uint64_t stream);
 
+/* One Mamba block (RMSNorm -> in_proj -> state step -> out_proj + residual, inference/src/model.rs:296-375
+ * in arithmetic) WITHOUT any allocation.  This entry point has no counterpart in the reference.
+ *
+ * For hosts that cannot call cudaMalloc where they need the block: a process whose own memory pool
+ * already holds the whole GPU, code inside a stream capture, or a loop that must not take the
+ * device-wide synchronisation an allocation brings.  Such a host cannot create a lumi_session either,
+ * since that allocates.  Here the caller passes every input and output as device pointers —
+ * x[batch][d_model] fp32 (in/out, the residual stream) and this layer's state for `batch` sequences:
+ * h[batch][H][P][N], x_prev[batch][H][P], b_prev[batch][H][N], cum_angle[batch][H][N/2] (all updated in
+ * place; a fresh sequence has h = h_init broadcast over P and zeros elsewhere) — and the block's two
+ * intermediates live in a fixed 512 KiB array inside the library's device image (held by every GPU
+ * that loads the library, until the process exits).
+ *
+ * Limits: batch <= 8 and in_proj_out + d_inner <= 16384 floats; anything larger is refused with
+ * LUMI_E_UNSUPPORTED.  The weights come from `m` (loaded and finalized earlier).  No cudaMalloc,
+ * cudaFree or other allocating call is made.  The first call on a device looks up the array's
+ * device address (cudaGetSymbolAddress, with that device current) and keeps it: make that first
+ * call before any stream capture begins.  All calls on a device share the one array, which keeps
+ * whatever the last call left in it; nothing in it needs clearing (every element is written
+ * before it is read), but two calls whose kernels overlap on the GPU — different streams, or the same
+ * stream from different threads — race on it: serialise them. */
+int32_t lumi_mamba_block_static(lumi_model* m, int32_t layer, uint64_t x, uint64_t h, uint64_t x_prev, uint64_t b_prev,
+                                uint64_t cum_angle, int32_t batch, uint64_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -25,7 +25,7 @@ EXPORTS = [
     "lumi_model_finalize", "lumi_model_free", "lumi_model_info", "lumi_session_create", "lumi_session_reset",
     "lumi_session_free", "lumi_session_set_option", "lumi_prefill", "lumi_decode_step", "lumi_generate",
     "lumi_decode_loop_device", "lumi_profile_step", "lumi_session_read_state", "lumi_debug_run_block", "lumi_k_gemm_bf16_tcgen05",
-    "lumi_k_gemv", "lumi_k_ssm_step",
+    "lumi_k_gemv", "lumi_k_ssm_step", "lumi_mamba_block_static",
 ]
 
 
@@ -77,6 +77,7 @@ def lib():
         L.lumi_k_gemm_bf16_tcgen05.argtypes = [u64, u64, u64, u64, i32, i32, i32, i32, i32, u64]
         L.lumi_k_gemv.argtypes = [u64, u64, i32, u64, u64, u64, i32, i32, i32, u64]
         L.lumi_k_ssm_step.argtypes = [u64, i32] + [u64] * 11 + [i32] * 5 + [u64]
+        L.lumi_mamba_block_static.argtypes = [vp, i32, u64, u64, u64, u64, u64, i32, u64]
         _lib = L
     return _lib
 
