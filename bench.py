@@ -112,6 +112,7 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     from oracle import cpu_oracle
+    cores = cpu_oracle.set_threads(os.cpu_count() or 1)          # torchrun exports OMP_NUM_THREADS=1
     cfg = workload_config(args)
     tens = list(synth.iter_tensors(cfg, seed=0, weights_dtype="bf16"))
     om = cpu_oracle.OracleModel(cfg, tens)
@@ -136,7 +137,6 @@ def run_reference(args, rank, world):
         step()
     dt = time.perf_counter() - t0
     value = nseq * args.steps / dt
-    cores = os.cpu_count() or 1
     sample = f"{nseq} sequence(s) x {args.steps} decode tokens of the same 96-layer model, after a 4-token prompt"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
@@ -157,6 +157,7 @@ def WORKLOAD_NAME(args):
 def cpu_baseline(args, cfg):
     """Rank 0, N = 1: the oracle timed on the host cores on a bounded sample of the same workload."""
     from oracle import cpu_oracle
+    cores = cpu_oracle.set_threads(os.cpu_count() or 1)
     tens = list(synth.iter_tensors(cfg, seed=0, weights_dtype="bf16"))
     om = cpu_oracle.OracleModel(cfg, tens)
     del tens
@@ -170,7 +171,7 @@ def cpu_baseline(args, cfg):
     for _ in range(n):
         tok = cpu_oracle.argmax(st.forward_step(tok))
     dt = time.perf_counter() - t0
-    return {"value": n / dt, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+    return {"value": n / dt, "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"1 sequence x {n} decode tokens of the same {cfg.n_layers}-layer model after a 4-token prompt "
                       f"(the reference runs sequences one at a time: per-sequence tok/s)"}
 

@@ -30,6 +30,8 @@ def lib():
     if _lib is None:
         build()
         L = C.CDLL(_LIB_PATH)
+        L.oracle_set_threads.restype = C.c_int32
+        L.oracle_set_threads.argtypes = [C.c_int32]
         L.oracle_model_new.restype = C.c_void_p
         L.oracle_model_new.argtypes = [C.c_void_p, C.c_float, C.c_void_p, C.c_void_p]
         L.oracle_model_free.argtypes = [C.c_void_p]
@@ -132,6 +134,11 @@ class OracleState:
         n = lib().oracle_generate(self.model._m, self._s, _p(prompt), len(prompt), n_new, float(temperature),
                                   int(top_k), _p(u), int(eos), int(bool(ignore_eos)), _p(out), _p(dump))
         return (out[:n], dump[:n]) if dump_logits else out[:n]
+
+
+def set_threads(n: int) -> int:
+    """Sets the OpenMP thread count of the oracle's matvecs; returns the count in effect."""
+    return int(lib().oracle_set_threads(int(n)))
 
 
 def argmax(logits: np.ndarray) -> int:

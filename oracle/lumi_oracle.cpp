@@ -36,6 +36,9 @@
 #include <string>
 #include <vector>
 #include <algorithm>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 namespace {
 
@@ -334,6 +337,17 @@ uint32_t sample(const float* logits, int n, double temperature, int top_k, float
 }  // namespace
 
 extern "C" {
+
+// Launchers such as torchrun export OMP_NUM_THREADS=1; a timed CPU baseline sets its thread count itself.
+int32_t oracle_set_threads(int32_t n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
 
 // cfg: d_model, n_layers, d_state, expand, n_heads, n_groups, vocab, attn_n_heads, attn_kv_heads, mlp_dim
 void* oracle_model_new(const int32_t* cfg, float rope_base, const uint8_t* is_attn, const int32_t* window) {
