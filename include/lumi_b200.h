@@ -121,6 +121,9 @@ void    lumi_session_free(lumi_session* s);
  *                         "graph" = 1 (default) replays the decode step as a CUDA graph;
  *                         "pdl" = 1 (default) launches the weight-streaming kernels with programmatic
  *                         dependent launch so each one prefetches its weights while its predecessor runs;
+ *                         "overlap" = minimum batch (default 0 = never) from which the tensor-core path runs two
+ *                         lanes of sequences side by side on prioritised streams (measured neutral: the state
+ *                         step needs its L1 and cannot share an SM with the 198 KB GEMM);
  *                         "megakernel" = 1 runs batch-1 calls on Mamba-only models (head_dim 32, d_state 64) as
  *                         one persistent cooperative kernel per call (default 0: measured on par with the
  *                         graph-replayed kernel chain, which needs no device-side waits). */

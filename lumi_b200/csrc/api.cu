@@ -344,6 +344,14 @@ extern "C" void lumi_session_free(lumi_session* s) {
     if (s->ev0) cudaEventDestroy(s->ev0);
     if (s->ev1) cudaEventDestroy(s->ev1);
     if (s->ev2) cudaEventDestroy(s->ev2);
+    for (int i = 0; i < 2; ++i) {
+        if (s->lane_hi[i]) cudaStreamDestroy(s->lane_hi[i]);
+        if (s->lane_lo[i]) cudaStreamDestroy(s->lane_lo[i]);
+        for (int j = 0; j < 2; ++j) if (s->lane_ev[i][j]) cudaEventDestroy(s->lane_ev[i][j]);
+        if (s->ev_join[i]) cudaEventDestroy(s->ev_join[i]);
+    }
+    if (s->ev_fork) cudaEventDestroy(s->ev_fork);
+    if (s->ev_stagger) cudaEventDestroy(s->ev_stagger);
     if (s->stream) cudaStreamDestroy(s->stream);
     delete s;
 }
@@ -356,6 +364,18 @@ static int32_t session_alloc(lumi_session* s) {
     LUMI_CUDA(cudaEventCreate(&s->ev0));
     LUMI_CUDA(cudaEventCreate(&s->ev1));
     LUMI_CUDA(cudaEventCreate(&s->ev2));
+    {
+        int lo_prio = 0, hi_prio = 0;                     // numerically lower = higher priority
+        LUMI_CUDA(cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio));
+        for (int i = 0; i < 2; ++i) {
+            LUMI_CUDA(cudaStreamCreateWithPriority(&s->lane_hi[i], cudaStreamNonBlocking, hi_prio));
+            LUMI_CUDA(cudaStreamCreateWithPriority(&s->lane_lo[i], cudaStreamNonBlocking, lo_prio));
+            for (int j = 0; j < 2; ++j) LUMI_CUDA(cudaEventCreateWithFlags(&s->lane_ev[i][j], cudaEventDisableTiming));
+            LUMI_CUDA(cudaEventCreateWithFlags(&s->ev_join[i], cudaEventDisableTiming));
+        }
+        LUMI_CUDA(cudaEventCreateWithFlags(&s->ev_fork, cudaEventDisableTiming));
+        LUMI_CUDA(cudaEventCreateWithFlags(&s->ev_stagger, cudaEventDisableTiming));
+    }
     if (nm > 0) {
         LUMI_CUDA(cudaMalloc(&s->h, sizeof(float) * nm * B * state_h_per_seq(c)));
         LUMI_CUDA(cudaMalloc(&s->xprev, sizeof(float) * nm * B * c.d_inner()));
@@ -384,6 +404,7 @@ static int32_t session_alloc(lumi_session* s) {
     if (s->m->wdtype == LUMI_DTYPE_BF16) {
         // rows padded to a whole 128-row tile so TMA boxes never start outside the allocation
         const size_t rows = (B + 127) / 128 * 128;
+        s->act_ld = kmax;
         LUMI_CUDA(cudaMalloc(&s->act_hi, sizeof(__nv_bfloat16) * rows * kmax));
         LUMI_CUDA(cudaMalloc(&s->act_lo, sizeof(__nv_bfloat16) * rows * kmax));
         LUMI_CUDA(cudaMemset(s->act_hi, 0, sizeof(__nv_bfloat16) * rows * kmax));
@@ -433,6 +454,7 @@ extern "C" int32_t lumi_session_create(lumi_model* m, int32_t max_batch, int32_t
     if (const char* e = getenv("LUMI_PDL")) s->opt_pdl = atoi(e) ? 1 : 0;       // default for new sessions
     if (const char* e = getenv("LUMI_GRAPH")) s->opt_graph = atoi(e) ? 1 : 0;
     if (const char* e = getenv("LUMI_MEGAKERNEL")) s->opt_mega = atoi(e) ? 1 : 0;
+    if (const char* e = getenv("LUMI_OVERLAP")) s->opt_overlap = atoi(e) < 0 ? 0 : atoi(e);
     int32_t st = session_alloc(s);
     if (st == LUMI_OK) st = lumi_session_reset(s, nullptr, 0);
     if (st != LUMI_OK) {
@@ -488,6 +510,7 @@ extern "C" int32_t lumi_session_set_option(lumi_session* s, const char* name, in
     else if (n == "graph") s->opt_graph = value ? 1 : 0;
     else if (n == "pdl") s->opt_pdl = value ? 1 : 0;
     else if (n == "megakernel") s->opt_mega = value ? 1 : 0;
+    else if (n == "overlap") s->opt_overlap = value < 0 ? 0 : (int)value;
     else return fail(LUMI_E_INVALID, "unknown option '%s'", name);
     for (auto& g : s->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);   // captured choices are stale
     s->graphs.clear();
@@ -504,6 +527,8 @@ struct StepPlan {
     int B;
     bool tc;         // tensor-core GEMMs (bf16 weights, batch > 8) or the weight-streaming GEMV
     int64_t n = 0;   // launches enqueued
+    int row0 = 0;                                                 // first sequence of this plan's rows (B of them)
+    cudaStream_t st_hi = nullptr, st_lo = nullptr;               // GEMM / norm stream and state-step stream (both = session stream unless two lanes run)
     int fam = FAM_EMBED;                                          // family of the launches that follow
     std::vector<std::pair<int, cudaEvent_t>>* prof = nullptr;     // profiling: an event before every launch
 };
@@ -534,45 +559,61 @@ int32_t linear(StepPlan& p, const DevTensor& W, const float* in32, int K, float*
     if (!p.tc) {
         GemvArgs g{in32, K, W.p, W.dtype, out, ldd, residual, gamma, p.B, N, K, c.eps, act};
         mark(p);
-        LUMI_CUDA(launch_gemv(g, s->stream));
+        LUMI_CUDA(launch_gemv(g, p.st_hi));
         return LUMI_OK;
     }
-    // tensor-core path: the caller has already put the bf16 halves of the input into act_hi / act_lo
-    GemmArgs g{s->act_hi, s->opt_split ? s->act_lo : nullptr, (const __nv_bfloat16*)W.p, out, ldd, p.B, N, K,
+    // tensor-core path: the caller has already put the bf16 halves of the input into this plan's
+    // region of act_hi / act_lo (rows packed with leading dimension K from the region's start)
+    const size_t aoff = (size_t)p.row0 * s->act_ld;
+    GemmArgs g{s->act_hi + aoff, s->opt_split ? s->act_lo + aoff : nullptr, (const __nv_bfloat16*)W.p, out, ldd, p.B, N, K,
                residual != nullptr ? 1 : 0, &s->ctl->status};
     mark(p);
-    LUMI_TRY(launch_gemm_tcgen05(g, s->stream));
+    LUMI_TRY(launch_gemm_tcgen05(g, p.st_hi));
     return LUMI_OK;
 }
 
-int32_t mamba_block(StepPlan& p, const Layer& L) {
+// One Mamba block for rows [p.row0, p.row0 + p.B).  With two lanes running, `between` (if given) is
+// recorded/awaited around the state step so that it runs on the lane's low-priority stream.
+int32_t mamba_block(StepPlan& p, const Layer& L, cudaEvent_t ev_gemm_done = nullptr, cudaEvent_t ev_ssm_done = nullptr) {
     lumi_session* s = p.s;
     const Config& c = s->m->cfg;
-    const size_t B = s->max_batch, l = L.kind_idx;
+    const size_t B = s->max_batch, l = L.kind_idx, r0 = p.row0;
     const int D = c.d_model, DI = c.d_inner(), R = c.in_proj_out();
+    const size_t aoff = r0 * s->act_ld;
+    float* x = s->x + r0 * D;
+    float* proj = s->proj + r0 * R;
+    float* y32 = s->y32 ? s->y32 + r0 * DI : nullptr;
     if (p.tc) {
         p.fam = FAM_NORM;
         mark(p);
-        LUMI_CUDA(launch_norm_split(s->x, L.m.norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, D, c.eps, s->stream));
+        LUMI_CUDA(launch_norm_split(x, L.m.norm_g, s->act_hi + aoff, s->opt_split ? s->act_lo + aoff : nullptr, p.B, D, c.eps, p.st_hi));
     }
     p.fam = FAM_IN_PROJ;
-    LUMI_TRY(linear(p, L.m.in_proj, s->x, D, s->proj, R, nullptr, L.m.norm_g, 0, R));
+    LUMI_TRY(linear(p, L.m.in_proj, x, D, proj, R, nullptr, L.m.norm_g, 0, R));
+    if (ev_gemm_done) {
+        LUMI_CUDA(cudaEventRecord(ev_gemm_done, p.st_hi));
+        LUMI_CUDA(cudaStreamWaitEvent(p.st_lo, ev_gemm_done, 0));
+    }
     SsmArgs a{};
-    a.proj = s->proj; a.ldp = R;
+    a.proj = proj; a.ldp = R;
     a.bg = L.m.b_gamma; a.cg = L.m.c_gamma; a.bb = L.m.b_bias; a.cb = L.m.c_bias; a.dskip = L.m.d_skip; a.dtb = L.m.dt_bias;
-    a.h = s->h + l * B * state_h_per_seq(c);
-    a.xprev = s->xprev + l * B * DI;
-    a.bprev = s->bprev + l * B * c.n_heads * c.d_state;
-    a.cum = s->cum + l * B * c.n_heads * (c.d_state / 2);
-    a.y32 = p.tc ? nullptr : s->y32;
-    a.yhi = p.tc ? s->act_hi : nullptr;
-    a.ylo = (p.tc && s->opt_split) ? s->act_lo : nullptr;
+    a.h = s->h + (l * B + r0) * state_h_per_seq(c);
+    a.xprev = s->xprev + (l * B + r0) * DI;
+    a.bprev = s->bprev + (l * B + r0) * c.n_heads * c.d_state;
+    a.cum = s->cum + (l * B + r0) * c.n_heads * (c.d_state / 2);
+    a.y32 = p.tc ? nullptr : y32;
+    a.yhi = p.tc ? s->act_hi + aoff : nullptr;
+    a.ylo = (p.tc && s->opt_split) ? s->act_lo + aoff : nullptr;
     a.B = p.B; a.H = c.n_heads; a.P = c.head_dim(); a.N = c.d_state; a.G = c.n_groups; a.eps = c.eps;
     p.fam = FAM_SSM;
     mark(p);
-    LUMI_CUDA(launch_ssm_step(a, s->stream));
+    LUMI_CUDA(launch_ssm_step(a, p.st_lo));
+    if (ev_ssm_done) {
+        LUMI_CUDA(cudaEventRecord(ev_ssm_done, p.st_lo));
+        LUMI_CUDA(cudaStreamWaitEvent(p.st_hi, ev_ssm_done, 0));
+    }
     p.fam = FAM_OUT_PROJ;
-    LUMI_TRY(linear(p, L.m.out_proj, s->y32, DI, s->x, D, s->x, nullptr, 0, D));
+    LUMI_TRY(linear(p, L.m.out_proj, y32, DI, x, D, x, nullptr, 0, D));
     return LUMI_OK;
 }
 
@@ -583,7 +624,7 @@ int32_t attention_block(StepPlan& p, const Layer& L) {
     p.fam = FAM_ATTN;
     if (p.tc) {
         mark(p);
-        LUMI_CUDA(launch_norm_split(s->x, L.a.attn_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, D, c.eps, s->stream));
+        LUMI_CUDA(launch_norm_split(s->x, L.a.attn_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, D, c.eps, p.st_hi));
     }
     LUMI_TRY(linear(p, L.a.qkv, s->x, D, s->proj, Q, nullptr, L.a.attn_norm_g, 0, Q));
     AttnArgs a{};
@@ -601,17 +642,17 @@ int32_t attention_block(StepPlan& p, const Layer& L) {
     a.rope_base = c.attn_rope_base;
     a.ctl = s->ctl;
     mark(p);
-    cudaError_t e = launch_attention_decode(a, s->stream);
+    cudaError_t e = launch_attention_decode(a, p.st_hi);
     if (e == cudaErrorInvalidValue) return fail(LUMI_E_UNSUPPORTED, "attention head_dim %d with %d query heads per kv head is not built", a.head_dim, a.n_heads / a.kv_heads);
     LUMI_CUDA(e);
     LUMI_TRY(linear(p, L.a.o, s->y32, D, s->x, D, s->x, nullptr, 0, D));
     // sigmoid-gated MLP (model.rs:546-555)
     if (p.tc) {
         mark(p);
-        LUMI_CUDA(launch_norm_split(s->x, L.a.mlp_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, D, c.eps, s->stream));
+        LUMI_CUDA(launch_norm_split(s->x, L.a.mlp_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, D, c.eps, p.st_hi));
         LUMI_TRY(linear(p, L.a.gate_up, nullptr, D, s->proj, 2 * MLP, nullptr, nullptr, 0, 2 * MLP));
         mark(p);
-        LUMI_CUDA(launch_gate_mul(s->proj, 2 * MLP, nullptr, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, MLP, s->stream));
+        LUMI_CUDA(launch_gate_mul(s->proj, 2 * MLP, nullptr, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, MLP, p.st_hi));
     } else {
         LUMI_TRY(linear(p, L.a.gate_up, s->x, D, s->y32, MLP, nullptr, L.a.mlp_norm_g, 1, MLP));
     }
@@ -628,11 +669,45 @@ int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches,
     // dependent launch overlaps each kernel's prologue (weight prefetch) with its predecessor; it is
     // used on the weight-streaming path, where launch gaps are the same order as the kernels
     struct PdlScope { PdlScope(bool on) { set_launch_pdl(on); } ~PdlScope() { set_launch_pdl(false); } } pdl_scope(s->opt_pdl && !p.tc && prof == nullptr);
+    p.st_hi = p.st_lo = s->stream;
     mark(p);
     LUMI_CUDA(launch_embed(s->m->embedding.p, s->m->embedding.dtype, s->tok_cur, s->x, B, c.d_model, c.vocab, s->ctl, s->stream));
-    for (const Layer& L : s->m->layers) {
-        if (L.is_attn) LUMI_TRY(attention_block(p, L));
-        else LUMI_TRY(mamba_block(p, L));
+    const bool two_lanes = p.tc && prof == nullptr && s->opt_overlap > 0 && B >= s->opt_overlap && s->m->n_attn == 0 && B >= 2;
+    if (!two_lanes) {
+        for (const Layer& L : s->m->layers) {
+            if (L.is_attn) LUMI_TRY(attention_block(p, L));
+            else LUMI_TRY(mamba_block(p, L));
+        }
+    } else {
+        // Two lanes of sequences run the whole layer chain independently.  The GEMMs (tensor pipe,
+        // shared memory) of one lane are meant to run under the state step (HBM) of the other, so
+        // GEMM kernels go to high-priority streams — pending high-priority CTAs are placed before
+        // the thousands of pending state-step CTAs — and lane 1 starts one GEMM ahead of lane 0.
+        const int half = (B / 2 + 127) / 128 * 128 < B ? (B / 2 + 127) / 128 * 128 : B / 2;
+        StepPlan lane[2] = {p, p};
+        lane[0].row0 = 0; lane[0].B = half;
+        lane[1].row0 = half; lane[1].B = B - half;
+        LUMI_CUDA(cudaEventRecord(s->ev_fork, s->stream));
+        for (int i = 0; i < 2; ++i) {
+            lane[i].n = 0;
+            lane[i].st_hi = s->lane_hi[i];
+            lane[i].st_lo = s->lane_lo[i];
+            LUMI_CUDA(cudaStreamWaitEvent(s->lane_hi[i], s->ev_fork, 0));
+        }
+        bool first = true;
+        for (const Layer& L : s->m->layers) {
+            LUMI_TRY(mamba_block(lane[1], L, s->lane_ev[1][0], s->lane_ev[1][1]));
+            if (first) {        // lane 0 begins once lane 1's first in_proj is done
+                LUMI_CUDA(cudaStreamWaitEvent(s->lane_hi[0], s->lane_ev[1][0], 0));
+                first = false;
+            }
+            LUMI_TRY(mamba_block(lane[0], L, s->lane_ev[0][0], s->lane_ev[0][1]));
+        }
+        for (int i = 0; i < 2; ++i) {
+            LUMI_CUDA(cudaEventRecord(s->ev_join[i], s->lane_hi[i]));
+            LUMI_CUDA(cudaStreamWaitEvent(s->stream, s->ev_join[i], 0));
+            p.n += lane[i].n;
+        }
     }
     if (with_head) {
         p.fam = FAM_HEAD;
@@ -1019,6 +1094,7 @@ extern "C" int32_t lumi_debug_run_block(lumi_session* s, int32_t layer, float* x
     LUMI_TRY(push_ctl(s));
     LUMI_CUDA(cudaMemcpyAsync(s->x, x, sizeof(float) * batch * c.d_model, cudaMemcpyHostToDevice, s->stream));
     StepPlan p{s, batch, use_tc(s, batch)};
+    p.st_hi = p.st_lo = s->stream;
     const Layer& L = s->m->layers[layer];
     if (L.is_attn) {
         LUMI_TRY(attention_block(p, L));

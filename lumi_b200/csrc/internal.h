@@ -134,6 +134,12 @@ struct lumi_session {
     int max_batch = 0, max_tokens_kv = 0;
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;
+    // two-lane execution of large tensor-core batches: GEMM kernels of each lane on a high-priority
+    // stream, state steps on a low-priority one
+    cudaStream_t lane_hi[2] = {nullptr, nullptr}, lane_lo[2] = {nullptr, nullptr};
+    cudaEvent_t lane_ev[2][2] = {{nullptr, nullptr}, {nullptr, nullptr}}, ev_fork = nullptr, ev_stagger = nullptr, ev_join[2] = {nullptr, nullptr};
+    int opt_overlap = 0;              // minimum batch for two-lane execution (0 = never)
+    size_t act_ld = 0;                // elements per row of the activation-half buffers
     // options
     int opt_gemm = 0, opt_split = 1, opt_graph = 1, opt_pdl = 1, opt_mega = 0;
     // batch-1 persistent kernel

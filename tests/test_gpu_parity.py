@@ -185,6 +185,28 @@ def test_bf16_batched_parity(gemm, split, tol):
             _compare_tokens(toks[b], ref_toks, ref_logits, f"bf16 batch slot {b}")
 
 
+def test_two_lane_execution_matches_single_lane():
+    """Large tensor-core batches run as two lanes of sequences on separate streams; rows are
+    independent, so tokens and logits must not change at all."""
+    cfg = synth.base_config(n_layers=4, vocab_size=2048)
+    tens = list(synth.iter_tensors(cfg, seed=2, weights_dtype="bf16"))
+    B, T, n_new = 96, 6, 10
+    prompts = synth.random_prompts(B, T, cfg.vocab_size, seed=4)
+    model = lumi_b200.NmModel.from_tensors(cfg, tens)
+    outs = []
+    for overlap in (0, 32):
+        sess = model.init_states(B)
+        sess.set_option("overlap", overlap)
+        toks, lens, dump, st = sess.generate(prompts, n_new, ignore_eos=True, dump_logits=True)
+        outs.append((toks.copy(), dump.copy()))
+        sess.close()
+    assert np.array_equal(outs[0][0], outs[1][0])
+    assert np.array_equal(outs[0][1], outs[1][1])
+    ref_toks, ref_logits = cpu_oracle.OracleModel(cfg, tens).init_states().generate(prompts[95], n_new, ignore_eos=True, dump_logits=True)
+    assert max(rel_err(outs[1][1][i, 95], ref_logits[i]) for i in range(n_new)) < TOL_F32
+    _compare_tokens(outs[1][0][95], ref_toks, ref_logits, "two lanes, last sequence")
+
+
 def test_hybrid_bf16_tensor_core_path():
     cfg = synth.tiny_config(attention_interval=2, attn_rope_base=10000.0, attn_mlp_dim=320)
     tens = list(synth.iter_tensors(cfg, seed=8, weights_dtype="bf16", perturb_ones=0.1))
