@@ -121,6 +121,10 @@ void    lumi_session_free(lumi_session* s);
  *                         "graph" = 1 (default) replays the decode step as a CUDA graph;
  *                         "pdl" = 1 (default) launches the weight-streaming kernels with programmatic
  *                         dependent launch so each one prefetches its weights while its predecessor runs;
+ *                         "chunked_prefill" = minimum prompt length (default 128, 0 = never) from which bf16
+ *                         Mamba-only models prefill with the chunked SSD scan (chunk 64) and tensor-core GEMMs over
+ *                         all prompt tokens instead of token by token (same state to rounding); "prefill_rows" =
+ *                         token rows per pass of that path (default 32768; sets its workspace size);
  *                         "overlap" = minimum batch (default 0 = never) from which the tensor-core path runs two
  *                         lanes of sequences side by side on prioritised streams (measured neutral: the state
  *                         step needs its L1 and cannot share an SM with the 198 KB GEMM);

@@ -16,7 +16,7 @@ LIBDIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIBDIR, "liblumi_b200.so")
 CLI = os.path.join(LIBDIR, "lumi-infer-b200")
 
-SOURCES = ["api.cu", "kernels.cu", "gemm_tcgen05.cu", "attention.cu", "decode_b1.cu", "block_static.cu", "safetensors.cpp"]
+SOURCES = ["api.cu", "kernels.cu", "gemm_tcgen05.cu", "attention.cu", "decode_b1.cu", "block_static.cu", "prefill_ssd.cu", "safetensors.cpp"]
 HEADERS = ["internal.h", "json_min.h", os.path.join("..", "..", "include", "lumi_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-ccbin", "/usr/bin/g++"]

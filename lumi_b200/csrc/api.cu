@@ -337,6 +337,7 @@ extern "C" void lumi_session_free(lumi_session* s) {
     for (auto& g : s->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
     void* dev[] = {s->h, s->xprev, s->bprev, s->cum, s->kv_pool, s->page_table, s->kv_pos, s->x, s->proj, s->y32, s->logits,
                    s->act_hi, s->act_lo, s->tok_cur, s->finished, s->out_len, s->ctl, s->gen_out, s->prompt_dev, s->gen_dump,
+                   s->pf_x, s->pf_proj, s->pf_rb, s->pf_rc, s->pf_hi, s->pf_lo,
                    s->b1_layers, s->b1_grid_ctl, s->b1_amax_val, s->b1_amax_idx, s->b1_timing, s->b1_tagged};
     for (void* p : dev) if (p) cudaFree(p);
     if (s->ctl_host) cudaFreeHost(s->ctl_host);
@@ -454,6 +455,7 @@ extern "C" int32_t lumi_session_create(lumi_model* m, int32_t max_batch, int32_t
     if (const char* e = getenv("LUMI_PDL")) s->opt_pdl = atoi(e) ? 1 : 0;       // default for new sessions
     if (const char* e = getenv("LUMI_GRAPH")) s->opt_graph = atoi(e) ? 1 : 0;
     if (const char* e = getenv("LUMI_MEGAKERNEL")) s->opt_mega = atoi(e) ? 1 : 0;
+    if (const char* e = getenv("LUMI_CHUNKED_PREFILL")) s->opt_chunked_prefill = atoi(e) < 0 ? 0 : atoi(e);
     if (const char* e = getenv("LUMI_OVERLAP")) s->opt_overlap = atoi(e) < 0 ? 0 : atoi(e);
     int32_t st = session_alloc(s);
     if (st == LUMI_OK) st = lumi_session_reset(s, nullptr, 0);
@@ -511,6 +513,8 @@ extern "C" int32_t lumi_session_set_option(lumi_session* s, const char* name, in
     else if (n == "pdl") s->opt_pdl = value ? 1 : 0;
     else if (n == "megakernel") s->opt_mega = value ? 1 : 0;
     else if (n == "overlap") s->opt_overlap = value < 0 ? 0 : (int)value;
+    else if (n == "chunked_prefill") s->opt_chunked_prefill = value < 0 ? 0 : (int)value;
+    else if (n == "prefill_rows") s->opt_prefill_rows = value < 64 ? 64 : (int)value;
     else return fail(LUMI_E_INVALID, "unknown option '%s'", name);
     for (auto& g : s->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);   // captured choices are stale
     s->graphs.clear();
@@ -839,6 +843,83 @@ int32_t sample_after_b1(lumi_session* s) {
     return LUMI_OK;
 }
 
+bool use_chunked_prefill(const lumi_session* s, int batch, int T) {
+    return s->opt_chunked_prefill > 0 && T >= s->opt_chunked_prefill && s->m->n_attn == 0 && s->m->wdtype == LUMI_DTYPE_BF16 &&
+           s->opt_gemm != 1 && prefill_ssd_supported(s->m->cfg) && (s->m->cfg.d_model % 64) == 0 && (s->m->cfg.d_inner() % 64) == 0;
+}
+
+// Prompt of T tokens for sequences 0..batch-1 through the chunked SSD scan; tokens come from
+// prompt_dev[T][batch].  Leaves the decode state of every layer as the step-by-step path would, the
+// last position's residual in x, and (with_head) its logits plus the sampled first token.
+int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head) {
+    const Config& c = s->m->cfg;
+    const int D = c.d_model, DI = c.d_inner(), R = c.in_proj_out();
+    const int nb_max = std::min(batch, 2048);
+    int TS = std::max(64, (std::max(64, s->opt_prefill_rows) / nb_max) / 64 * 64);
+    if (TS > T) TS = T;
+    const size_t rows_max = (size_t)nb_max * TS;
+    if (rows_max > s->pf_rows) {
+        void* olds[] = {s->pf_x, s->pf_proj, s->pf_rb, s->pf_rc, s->pf_hi, s->pf_lo};
+        for (void* q : olds) if (q) LUMI_CUDA(cudaFree(q));
+        s->pf_x = s->pf_proj = s->pf_rb = s->pf_rc = nullptr; s->pf_hi = s->pf_lo = nullptr; s->pf_rows = 0;
+        const size_t rp = (rows_max + 127) / 128 * 128;
+        LUMI_CUDA(cudaMalloc(&s->pf_x, sizeof(float) * rp * D));
+        LUMI_CUDA(cudaMalloc(&s->pf_proj, sizeof(float) * rp * R));
+        LUMI_CUDA(cudaMalloc(&s->pf_rb, sizeof(float) * rp));
+        LUMI_CUDA(cudaMalloc(&s->pf_rc, sizeof(float) * rp));
+        LUMI_CUDA(cudaMalloc(&s->pf_hi, sizeof(__nv_bfloat16) * rp * DI));
+        LUMI_CUDA(cudaMalloc(&s->pf_lo, sizeof(__nv_bfloat16) * rp * DI));
+        s->pf_rows = rows_max;
+    }
+    const size_t B = s->max_batch;
+    __nv_bfloat16* lo = s->opt_split ? s->pf_lo : nullptr;
+    for (int b0 = 0; b0 < batch; b0 += nb_max) {
+        const int nb = std::min(nb_max, batch - b0);
+        for (int t0 = 0; t0 < T; t0 += TS) {
+            const int ts = std::min(TS, T - t0);
+            const int M = nb * ts;
+            LUMI_CUDA(launch_prefill_embed(s->m->embedding.p, s->m->embedding.dtype, s->prompt_dev, s->pf_x, D, c.vocab, M, ts, t0, b0,
+                                           batch, s->ctl, s->stream));
+            s->launches += 1;
+            for (const Layer& L : s->m->layers) {
+                const size_t l = L.kind_idx;
+                LUMI_CUDA(launch_norm_split(s->pf_x, L.m.norm_g, s->pf_hi, lo, M, D, c.eps, s->stream));
+                GemmArgs g1{s->pf_hi, lo, (const __nv_bfloat16*)L.m.in_proj.p, s->pf_proj, R, M, R, D, 0, &s->ctl->status};
+                LUMI_TRY(launch_gemm_tcgen05(g1, s->stream));
+                PrefillArgs a{};
+                a.proj = s->pf_proj; a.ldp = R;
+                a.bg = L.m.b_gamma; a.cg = L.m.c_gamma; a.bb = L.m.b_bias; a.cb = L.m.c_bias; a.dskip = L.m.d_skip; a.dtb = L.m.dt_bias;
+                a.h = s->h + l * B * state_h_per_seq(c);
+                a.xprev = s->xprev + l * B * DI;
+                a.bprev = s->bprev + l * B * c.n_heads * c.d_state;
+                a.cum = s->cum + l * B * c.n_heads * (c.d_state / 2);
+                a.rb = s->pf_rb; a.rc = s->pf_rc;
+                a.yhi = s->pf_hi; a.ylo = lo;
+                a.H = c.n_heads; a.G = c.n_groups; a.ts = ts; a.nb = nb; a.b0 = b0; a.eps = c.eps;
+                LUMI_CUDA(launch_prefill_scan(a, s->stream));
+                GemmArgs g2{s->pf_hi, lo, (const __nv_bfloat16*)L.m.out_proj.p, s->pf_x, D, M, D, DI, 1, &s->ctl->status};
+                LUMI_TRY(launch_gemm_tcgen05(g2, s->stream));
+                s->launches += 5;
+            }
+            if (t0 + ts >= T) {
+                LUMI_CUDA(launch_gather_last(s->pf_x, s->x, D, ts, nb, b0, s->stream));
+                s->launches += 1;
+            }
+        }
+    }
+    if (with_head) {
+        StepPlan p{s, batch, true};
+        p.st_hi = p.st_lo = s->stream;
+        LUMI_CUDA(launch_norm_split(s->x, s->m->final_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, batch, D, c.eps, s->stream));
+        p.fam = FAM_HEAD;
+        LUMI_TRY(linear(p, s->m->embedding, s->x, D, s->logits, c.vocab, nullptr, s->m->final_norm_g, 0, c.vocab));
+        LUMI_CUDA(launch_sample(s->logits, batch, c.vocab, s->ctl, s->tok_cur, s->finished, s->out_len, s->stream));
+        LUMI_CUDA(launch_advance_step(s->ctl, nullptr, batch, 1, s->stream));
+        s->launches += 3 + p.n;
+    }
+    return LUMI_OK;
+}
+
 int32_t check_status(lumi_session* s) {
     const int st = s->ctl_host->status;
     if (st & STATUS_TIMEOUT) {
@@ -912,8 +993,11 @@ extern "C" int32_t lumi_prefill(lumi_session* s, const uint32_t* tokens, int32_t
     fill_ctl(s, batch, nullptr);
     s->ctl_host->prompt = s->prompt_dev;
     s->ctl_host->prompt_len = T;
+    const bool chunked = !use_b1(s, batch) && use_chunked_prefill(s, batch, T);
+    if (chunked) s->ctl_host->prompt_pos = T;          // the scan consumes the whole prompt itself
     LUMI_TRY(push_ctl(s));
     if (use_b1(s, batch)) LUMI_TRY(run_b1(s, T, last_logits != nullptr ? 1 : 0, 1));
+    else if (chunked) LUMI_TRY(prefill_chunked(s, batch, T, last_logits != nullptr));
     else
         for (int t = 0; t < T; ++t) LUMI_TRY(run_step(s, batch, last_logits != nullptr && t == T - 1));
     if (last_logits)
@@ -967,6 +1051,8 @@ extern "C" int32_t lumi_generate(lumi_session* s, const uint32_t* prompts, int32
     c.want_dump = logits_dump ? 1 : 0;
     c.out_tokens = s->gen_out;
     c.dump = s->gen_dump;
+    const bool chunked = !use_b1(s, batch) && use_chunked_prefill(s, batch, T);
+    if (chunked) c.prompt_pos = T;
     LUMI_TRY(push_ctl(s));
     LUMI_CUDA(cudaMemsetAsync(s->finished, 0, sizeof(int32_t) * batch, s->stream));
     LUMI_CUDA(cudaMemsetAsync(s->out_len, 0, sizeof(int32_t) * batch, s->stream));
@@ -979,6 +1065,8 @@ extern "C" int32_t lumi_generate(lumi_session* s, const uint32_t* prompts, int32
     if (b1) {
         LUMI_TRY(run_b1(s, T, n_new > 0 ? 1 : 0, greedy ? 1 : 0));
         if (n_new > 0 && !greedy) LUMI_TRY(sample_after_b1(s));
+    } else if (chunked) {
+        LUMI_TRY(prefill_chunked(s, batch, T, n_new > 0));
     } else {
         for (int t = 0; t < T; ++t) LUMI_TRY(run_step(s, batch, n_new > 0 && t == T - 1));
     }

@@ -140,6 +140,12 @@ struct lumi_session {
     cudaEvent_t lane_ev[2][2] = {{nullptr, nullptr}, {nullptr, nullptr}}, ev_fork = nullptr, ev_stagger = nullptr, ev_join[2] = {nullptr, nullptr};
     int opt_overlap = 0;              // minimum batch for two-lane execution (0 = never)
     size_t act_ld = 0;                // elements per row of the activation-half buffers
+    int opt_chunked_prefill = 128;    // minimum prompt length for the chunked SSD prefill (0 = never)
+    int opt_prefill_rows = 32768;     // token rows processed per chunked-prefill pass (workspace size)
+    // chunked-prefill workspace (grow-only): residual rows, in_proj output, bf16 halves, BCNorm scales
+    float *pf_x = nullptr, *pf_proj = nullptr, *pf_rb = nullptr, *pf_rc = nullptr;
+    __nv_bfloat16 *pf_hi = nullptr, *pf_lo = nullptr;
+    size_t pf_rows = 0;
     // options
     int opt_gemm = 0, opt_split = 1, opt_graph = 1, opt_pdl = 1, opt_mega = 0;
     // batch-1 persistent kernel
@@ -279,6 +285,22 @@ struct B1Args {
 };
 bool decode_b1_supported(const Config& c, int n_attn, int device);
 cudaError_t launch_decode_b1(const B1Args& a, int w_dtype, int device, cudaStream_t st);
+
+// ---- chunked SSD prefill (prefill_ssd.cu) ----------------------------------------------------------
+struct PrefillArgs {
+    const float* proj; int ldp;              // [nb * ts][in_proj_out], row = sequence * ts + token
+    const float *bg, *cg, *bb, *cb, *dskip, *dtb;
+    float *h, *xprev, *bprev, *cum;          // this layer's state, slot 0
+    float *rb, *rc;                          // [nb * ts] BCNorm scales (scratch)
+    __nv_bfloat16 *yhi, *ylo;                // [nb * ts][d_inner] gated output halves
+    int H, G, ts, nb, b0;                    // heads, groups, tokens per sequence in this launch, sequences, first slot
+    float eps;
+};
+bool prefill_ssd_supported(const Config& c);
+cudaError_t launch_prefill_embed(const void* emb, int dtype, const uint32_t* prompt, float* x, int D, int vocab, int rows, int ts,
+                                 int t_abs0, int b_abs0, int batch_total, StepCtl* ctl, cudaStream_t st);
+cudaError_t launch_prefill_scan(const PrefillArgs& a, cudaStream_t st);
+cudaError_t launch_gather_last(const float* xr, float* x, int D, int ts, int nb, int b0, cudaStream_t st);
 
 cudaError_t launch_gate_mul(const float* gu, int ld, float* out32, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int mlp,
                             cudaStream_t st);

@@ -185,6 +185,45 @@ def test_bf16_batched_parity(gemm, split, tol):
             _compare_tokens(toks[b], ref_toks, ref_logits, f"bf16 batch slot {b}")
 
 
+@pytest.mark.parametrize("rows", [32768, 192])
+def test_chunked_ssd_prefill_matches_stepwise_and_oracle(rows):
+    """bf16 Mamba-only model, 200-token prompts (three full chunks of 64 and a ragged one): the
+    chunked scan against the token-by-token prefill on the GPU and against the oracle's sequential
+    prefill — last-position logits, every layer's state, and the greedy continuation.  rows = 192
+    forces several passes (64 tokens each), so the state hand-over between launches is covered."""
+    cfg = synth.base_config(n_layers=3, vocab_size=1000)
+    tens = list(synth.iter_tensors(cfg, seed=6, weights_dtype="bf16", perturb_ones=0.05))
+    B, T, n_new = 3, 200, 8
+    prompts = synth.random_prompts(B, T, cfg.vocab_size, seed=9)
+    model = lumi_b200.NmModel.from_tensors(cfg, tens)
+    step = model.init_states(B)
+    step.set_option("chunked_prefill", 0)
+    lg_step = step.prefill(prompts)
+    chk = model.init_states(B)
+    chk.set_option("chunked_prefill", 64)
+    chk.set_option("prefill_rows", rows)
+    lg_chk = chk.prefill(prompts)
+    two_pi = 2 * np.pi
+    for b in range(B):
+        assert rel_err(lg_chk[b], lg_step[b]) < 1e-4
+        for layer in range(cfg.n_layers):
+            h1, xp1, bp1, cu1 = chk.read_state(b, layer)
+            h0, xp0, bp0, cu0 = step.read_state(b, layer)
+            assert np.abs(h1 - h0).max() <= 2e-4 * max(1.0, np.abs(h0).max()), (b, layer)
+            assert np.abs(xp1 - xp0).max() <= 1e-4 * max(1.0, np.abs(xp0).max())
+            assert np.abs(bp1 - bp0).max() <= 1e-3 * max(1.0, np.abs(bp0).max())     # follows the accumulated angle
+            d = np.abs(np.mod(cu1 - cu0 + np.pi, two_pi) - np.pi)          # equal modulo 2 pi
+            assert d.max() < 1e-3, (b, layer, d.max())   # 200 accumulated increments from two differently rounded GEMM paths
+    # against the oracle, including what decode makes of the handed-over state
+    ost = cpu_oracle.OracleModel(cfg, tens).init_states()
+    ref_toks, ref_logits = ost.generate(prompts[1], n_new, ignore_eos=True, dump_logits=True)
+    chk.reset()
+    toks, lens, dump, st = chk.generate(prompts, n_new, ignore_eos=True, dump_logits=True)
+    assert max(rel_err(dump[i, 1], ref_logits[i]) for i in range(n_new)) < TOL_F32
+    _compare_tokens(toks[1], ref_toks, ref_logits, "chunked prefill, sequence 1")
+    assert st.ms_prefill > 0
+
+
 def test_two_lane_execution_matches_single_lane():
     """Large tensor-core batches run as two lanes of sequences on separate streams; rows are
     independent, so tokens and logits must not change at all."""
