@@ -197,6 +197,63 @@ def batch1_line(args, peak_gbs):
             "value": toks, "unit": UNIT, "bytes_per_step": per_step, "achieved_gbs": ach, "peak_gbs": peak_gbs, "frac": ach / peak_gbs}
 
 
+CONFIGS = {
+    # name: (config kwargs, weights dtype, batch, prompt length, decode tokens, sampling)
+    "config1": (dict(), "f32", 1, 32, 256, dict()),
+    "config2": (dict(), "bf16", 64, 128, 512, dict()),
+    "config3": (dict(n_layers=96), "bf16", 256, 2048, 256, dict()),
+    "config4": (dict(attention_interval=6, attn_mlp_dim=2816, attn_rope_base=10000.0), "bf16", 128, 1024, 1024,
+                dict(temperature=0.8, top_k=50, seed=1234)),
+}
+
+
+def run_named_config(args, rank, local_rank, world):
+    """The other benchmark configurations, one GPU, through Session.generate (prefill + decode timed
+    by CUDA events inside the library).  Sequences would shard over ranks exactly as in the sweep."""
+    if rank != 0:
+        return
+    import lumi_b200
+    kw, wdt, batch, T, n_new, samp = CONFIGS[args.workload]
+    if args.steps_override:
+        n_new = args.steps_override
+    cfg = synth.base_config(max_seq_len=4096, **kw)
+    peak_gbs, peak_src = measured_peak_gbs()
+    model = lumi_b200.NmModel.from_tensors(cfg, synth.iter_tensors(cfg, seed=0, weights_dtype=wdt), device=local_rank)
+    info = model.info()
+    sess = model.init_states(batch, T + n_new + 1)
+    prompts = synth.random_prompts(batch, T, cfg.vocab_size, seed=0)
+    sess.generate(prompts[:, :min(T, 128)], 4, ignore_eos=True, **samp)        # warm-up (graphs, attributes)
+    sess.reset()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    t0 = time.perf_counter()
+    toks, lens, _, st = sess.generate(prompts, n_new + 1, ignore_eos=True, **samp)
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop()
+    S = state_bytes_per_seq_step(cfg)
+    kv = 0
+    if info["n_attention"]:
+        t_mean = T + n_new / 2.0
+        kv = int(info["n_attention"] * (2 * t_mean * cfg.attn_kv_dim * 2 + 2 * cfg.attn_kv_dim * 2))
+    step_bytes = info["weight_bytes"] + batch * (info["n_mamba"] * S + kv)
+    dec_tps = st.decode_tokens / (st.ms_decode * 1e-3)
+    gbs = step_bytes * (st.decode_tokens / batch) / (st.ms_decode * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": METRIC, "value": dec_tps, "unit": UNIT, "n_gpus": 1, "steps": int(st.decode_tokens // batch), "warmup": 4,
+        "ms_per_step": st.ms_decode / (st.decode_tokens / batch), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {cfg.n_layers} layers ({info['n_attention']} attention), {wdt} weights, batch {batch}, "
+                               f"{T}-token prompts, {n_new} decode tokens, sampling {samp or 'greedy'}"},
+        "gpu_launches": int(st.kernel_launches),
+        "prefill": {"tokens_per_second": st.prompt_tokens / (st.ms_prefill * 1e-3), "ms": st.ms_prefill},
+        "e2e": {"value": (st.decode_tokens + batch) / wall, "unit": UNIT, "note": "whole generate call incl. prefill, wall clock",
+                "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "roofline": {"bound": "hbm", "kernel": "whole decode step", "achieved": gbs, "peak": peak_gbs, "unit": "GB/s", "frac": gbs / peak_gbs,
+                     "traffic": None, "peak_source": peak_src, "bytes_per_step": step_bytes},
+        "clocks": clocks,
+    }), flush=True)
+
+
 def run_ours(args, rank, local_rank, world):
     import torch
     import torch.distributed as dist
@@ -221,6 +278,7 @@ def run_ours(args, rank, local_rank, world):
     S = state_bytes_per_seq_step(cfg)
     t_dev_ms, t_e2e_ms, launches = 0.0, 0.0, 0
     fam_ms, fam_n, ssm_batch = {}, {}, 0
+    single_ms, single_nb = None, 0
     sampler = ClockSampler(local_rank)
     h2d = d2h = 0
     for wi, (a, b) in enumerate(my_waves):
@@ -248,6 +306,14 @@ def run_ours(args, rank, local_rank, world):
         t_e2e_ms += (time.perf_counter() - t0) * 1e3
         h2d += nb * 4 + 80
         d2h += nb * 4 + 80
+        # secondary figure: activations rounded to bf16 once instead of the hi + lo split (half the MMAs)
+        if wi == len(my_waves) - 1 and args.split:
+            sess.set_option("split_activations", 0)
+            sess.decode_loop_device(nb, 3)
+            ms1, _ = sess.decode_loop_device(nb, args.steps)
+            single_ms = ms1 / args.steps
+            single_nb = nb
+            sess.set_option("split_activations", 1)
         # live per-kernel times (an event in front of every launch), second of two profiled steps
         sess.profile_step(nb)
         prof = sess.profile_step(nb)
@@ -301,6 +367,10 @@ def run_ours(args, rank, local_rank, world):
                          "whole_step": {"bytes_per_step": step_bytes, "achieved": step_gbs, "frac": step_gbs / peak_gbs,
                                         "frac_of_8TBs_nominal": step_gbs / 8000.0}},
             "kernel_ms_per_step": fam_ms, "kernel_launches_per_step": fam_n,
+            "single_rounded_activations": None if single_ms is None else {
+                "note": "same step with activations rounded to bf16 once (logit tolerance 2e-2 instead of 1e-3); last wave only",
+                "ms_per_wave_step": single_ms, "tok_per_s_this_wave": single_nb / (single_ms * 1e-3),
+                "whole_step_frac": (info["weight_bytes"] + single_nb * info["n_mamba"] * S) / (single_ms * 1e-3) / 1e9 / peak_gbs},
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu:
@@ -334,11 +404,15 @@ def main():
     ap.add_argument("--no-batch1", action="store_true")
     ap.add_argument("--only-batch1", action="store_true", help="run just the batch-1 figure (profiling)")
     ap.add_argument("--b1-layers", type=int, default=48)
+    ap.add_argument("--workload", default="sweep", choices=["sweep"] + sorted(CONFIGS))
+    ap.add_argument("--steps-override", type=int, default=0, help="decode tokens for --workload configN (0 = the configuration's own)")
     args = ap.parse_args()
     rank, local_rank, world = shard.env_rank_world()
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE {world}")
-    if args.only_batch1:
+    if args.workload != "sweep":
+        run_named_config(args, rank, local_rank, world)
+    elif args.only_batch1:
         print(json.dumps({"batch1": batch1_line(args, measured_peak_gbs()[0])}), flush=True)
     elif args.impl == "reference":
         run_reference(args, rank, world)
