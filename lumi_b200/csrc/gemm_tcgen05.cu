@@ -16,6 +16,7 @@
 #include "internal.h"
 
 #include <cuda.h>
+#include <cstdlib>
 
 namespace lumi {
 
@@ -106,21 +107,24 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int BN, bool SPLIT>
+// OCC = CTAs meant to share an SM: with 2, each gets half the stage budget and the epilogue of one
+// tile runs under the main loop of the other.
+template <int BN, bool SPLIT, int OCC>
 struct Tile {
     static constexpr int A_BYTES = BM * BK * 2;                 // 16 KiB
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE = A_BYTES * (SPLIT ? 2 : 1) + B_BYTES;
-    static constexpr int STAGES = kSmemBudget / STAGE;
+    static constexpr int STAGES = (kSmemBudget / OCC) / STAGE;
     static constexpr int SMEM = STAGES * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
+    static_assert(STAGES >= 2, "pipeline needs at least two stages");
 };
 
-template <int BN, bool SPLIT>
-__global__ void __launch_bounds__(192, 1)
+template <int BN, bool SPLIT, int OCC>
+__global__ void __launch_bounds__(192, OCC)
 gemm_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
             const __grid_constant__ CUtensorMap map_w, float* __restrict__ D, int ldd, int M, int N, int K,
             int accumulate, int32_t* status) {
-    using T = Tile<BN, SPLIT>;
+    using T = Tile<BN, SPLIT, OCC>;
     constexpr int S = T::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -265,14 +269,14 @@ int32_t make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_row
     return LUMI_OK;
 }
 
-template <int BN, bool SPLIT>
+template <int BN, bool SPLIT, int OCC>
 int32_t launch_t(const GemmArgs& a, cudaStream_t st) {
-    using T = Tile<BN, SPLIT>;
+    using T = Tile<BN, SPLIT, OCC>;
     CUtensorMap mh, ml, mw;
     LUMI_TRY(make_map(&mh, a.a_hi, a.M, a.K, BM));
     LUMI_TRY(make_map(&ml, SPLIT ? a.a_lo : a.a_hi, a.M, a.K, BM));
     LUMI_TRY(make_map(&mw, a.w, a.N, a.K, BN));
-    auto kern = gemm_kernel<BN, SPLIT>;
+    auto kern = gemm_kernel<BN, SPLIT, OCC>;
     LUMI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
     dim3 grid((a.N + BN - 1) / BN, (a.M + BM - 1) / BM);
     kern<<<grid, 192, T::SMEM, st>>>(mh, ml, mw, a.d, a.ldd, a.M, a.N, a.K, a.accumulate, a.status_word);
@@ -300,10 +304,16 @@ int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st) {
         return fail(LUMI_E_INVALID, "tcgen05 GEMM operands must be 16-byte aligned");
     LUMI_TRY(gemm_tcgen05_init());
     const bool split = a.a_lo != nullptr;
+    // LUMI_GEMM_MODE (tuning aid): 0 = default choice, 1 = 128-wide tiles two CTAs per SM, 2 = 128-wide one CTA per SM,
+    // 3 = 256-wide one CTA per SM
+    static const int mode = getenv("LUMI_GEMM_MODE") ? atoi(getenv("LUMI_GEMM_MODE")) : 0;
+    if (mode == 1) return split ? launch_t<128, true, 2>(a, st) : launch_t<128, false, 2>(a, st);
+    if (mode == 2) return split ? launch_t<128, true, 1>(a, st) : launch_t<128, false, 1>(a, st);
+    if (mode == 3) return split ? launch_t<256, true, 1>(a, st) : launch_t<256, false, 1>(a, st);
     // wide tiles when the problem has enough of them to fill the GPU
     const long tiles256 = (long)((a.N + 255) / 256) * ((a.M + BM - 1) / BM);
-    if (tiles256 >= 148) return split ? launch_t<256, true>(a, st) : launch_t<256, false>(a, st);
-    return split ? launch_t<128, true>(a, st) : launch_t<128, false>(a, st);
+    if (tiles256 >= 148) return split ? launch_t<256, true, 1>(a, st) : launch_t<256, false, 1>(a, st);
+    return split ? launch_t<128, true, 1>(a, st) : launch_t<128, false, 1>(a, st);
 }
 
 }  // namespace lumi
