@@ -561,7 +561,7 @@ int32_t linear(StepPlan& p, const DevTensor& W, const float* in32, int K, float*
     lumi_session* s = p.s;
     const Config& c = s->m->cfg;
     if (!p.tc) {
-        GemvArgs g{in32, K, W.p, W.dtype, out, ldd, residual, gamma, p.B, N, K, c.eps, act};
+        GemvArgs g{in32, K, W.p, W.dtype, out, ldd, residual, gamma, p.B, N, K, c.eps, act, &s->ctl->status};
         mark(p);
         LUMI_CUDA(launch_gemv(g, p.st_hi));
         return LUMI_OK;

@@ -197,6 +197,7 @@ struct GemvArgs {
     int M, N, K;
     float eps;
     int act;                         // 0 none; 1: D = sigmoid(W_gate a) * (W_up a), W = [gate rows | up rows], N = rows of each
+    int32_t* status = nullptr;       // device word that receives STATUS_TIMEOUT if a bounded wait gives up; may be null
 };
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);
 // Kernels of kernels.cu launched by the calling thread from now on carry (or not) the

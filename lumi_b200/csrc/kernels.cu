@@ -7,6 +7,7 @@
 // products use FMA with a fixed summation order (per-lane strided partials, xor-shuffle tree), so
 // results are bit-stable from run to run.
 #include "internal.h"
+#include <type_traits>
 
 #include <cfloat>
 #include <cmath>
@@ -18,9 +19,39 @@ namespace {
 
 // Programmatic dependent launch: a kernel launched with the attribute may start while its
 // predecessor still runs; everything that touches the predecessor's results comes after pdl_wait().
+// Pointers to data that an earlier kernel of the chain produced (activations, residuals, logits) are NOT
+// declared `const __restrict__`: that qualifier lets the compiler treat their loads as invariant and move
+// them above the wait, where they would read the values of the previous layer.  Only weights carry it.
 // Without the attribute both instructions are no-ops.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#ifdef LUMI_TIMELINE
+// debugging aid (not compiled by default): per-kernel time stamps of a few CTAs
+__device__ unsigned long long g_tl[65536 * 10];
+__device__ unsigned g_tl_n;
+__device__ __forceinline__ unsigned long long tl_now() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ bool tl_on() { return threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x / 2 || blockIdx.x == gridDim.x - 1) && blockIdx.y == 0; }
+__device__ __forceinline__ void tl_rec(int kind, const unsigned long long (&m)[6], unsigned long long cend) {
+    unsigned i = atomicAdd(&g_tl_n, 1u);
+    if (i < 65536u) {
+        unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        g_tl[i * 10] = kind; g_tl[i * 10 + 1] = blockIdx.x; g_tl[i * 10 + 2] = smid;
+        for (int j = 0; j < 6; ++j) g_tl[i * 10 + 3 + j] = m[j];
+        g_tl[i * 10 + 9] = cend;
+    }
+}
+// slot 0: start (global ns); slots 1..4: SM cycle counter at the marks; slot 5: global ns at the wait's end
+#define TL_T0 unsigned long long tlm[6] = {tl_now(), 0, 0, 0, 0, 0};
+#define TL_T1 tlm[5] = tl_now(); tlm[1] = clock64();
+#define TL_MARK(i) tlm[i] = clock64();
+#define TL_END(kind) if (tl_on()) { tl_rec(kind, tlm, clock64()); }
+#else
+#define TL_T0
+#define TL_T1
+#define TL_MARK(i)
+#define TL_END(kind)
+#endif
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -65,7 +96,7 @@ template <> struct WLoad<__nv_bfloat16> {
 
 // ---- embedding gather (model.rs:772-773) -----------------------------------------------------------
 template <typename WT>
-__global__ void embed_kernel(const WT* __restrict__ emb, const uint32_t* __restrict__ tok_cur, float* __restrict__ x,
+__global__ void embed_kernel(const WT* __restrict__ emb, const uint32_t* tok_cur, float* x,
                              int D, int vocab, StepCtl* ctl) {
     const int b = blockIdx.x;
     pdl_launch_dependents();
@@ -88,8 +119,8 @@ __global__ void embed_kernel(const WT* __restrict__ emb, const uint32_t* __restr
 }
 
 // ---- RMSNorm to bf16 halves for the tensor-core GEMMs (model.rs:100-106) ---------------------------
-__global__ void __launch_bounds__(256) norm_split_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
-                                                         __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
+__global__ void __launch_bounds__(256) norm_split_kernel(const float* x, const float* __restrict__ gamma,
+                                                         __nv_bfloat16* hi, __nv_bfloat16* lo,
                                                          int D, float eps) {
     __shared__ float red[8];
     const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -144,8 +175,8 @@ template <> struct WRaw<__nv_bfloat16> {
 };
 
 template <typename WT, int NB, int RPW, int ACT>
-__global__ void __launch_bounds__(256) gemv_kernel(const float* __restrict__ A, int lda, const WT* __restrict__ W,
-                                                   float* __restrict__ D, int ldd, const float* __restrict__ R,
+__global__ void __launch_bounds__(256) gemv_kernel(const float* A, int lda, const WT* __restrict__ W,
+                                                   float* D, int ldd, const float* R,
                                                    const float* __restrict__ gamma, int M, int N, int K, float eps, int KS) {
     extern __shared__ float4 gemv_smem4[];
     float* xs = reinterpret_cast<float*>(gemv_smem4);
@@ -275,6 +306,330 @@ __global__ void __launch_bounds__(256) gemv_kernel(const float* __restrict__ A, 
     }
 }
 
+// ---- single-wave GEMV whose whole weight share is requested before the dependency wait ---------------
+// For the smallest batches the chain of a token is latency-bound: each kernel waits for its predecessor,
+// then for HBM.  Here a CTA owns N / gridDim.x consecutive output rows and asks for ALL of their weights
+// the moment it becomes resident — the first 8 * RPW rows straight into registers (RPW rows per warp), the
+// rest by bulk copies into shared memory (one mbarrier per row) — and only then executes the dependency
+// wait.  Launched with programmatic dependent launch, the CTAs become resident while the predecessors
+// still run, so the HBM stream of this kernel overlaps them; after the wait only the activation staging,
+// the RMSNorm and the dot products from on-chip memory remain.  One wave, at most one CTA per SM; the
+// register / shared-memory split is chosen so that the three kernels of a block fit on an SM together.
+// Summation order of a row: per-lane partials over chunks lane, lane + 32, ... in ascending k, then the
+// 5-step xor tree.
+constexpr int kPreMaxSmemRows = 64;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+template <typename WT, int NB, int U, int RPW>
+__global__ void __launch_bounds__(256, 2) gemv_pre_kernel(const float* A, int lda, const WT* __restrict__ W,
+                                                          float* D, int ldd, const float* R,
+                                                          const float* __restrict__ gamma, int M, int N, int K, float eps,
+                                                          int rows_per_cta, int pace_ns, int32_t* status) {
+    extern __shared__ float4 gemv_smem4[];
+    constexpr int E = WLoad<WT>::E;
+    constexpr int GN = (U * E + 7) / 8;                 // gamma values per thread: K / 256 rounded up
+    constexpr int RR = 8 * RPW;                         // rows held in registers
+    constexpr int GR = U >= 16 ? 2 : (RPW <= 1 ? 6 : 4);   // shared-memory rows of a warp evaluated together
+    // One sequence and a short row: every warp keeps the whole activation row in registers (lane l owns the
+    // 16-byte chunks l, l + 32, ... — exactly the ones it multiplies), computes the RMSNorm scale itself and
+    // never touches shared memory or a block barrier for the activations.
+    constexpr bool XREG = (NB == 1) && (U * E <= 32);
+    __shared__ __align__(8) uint64_t bars[kPreMaxSmemRows];
+    __shared__ float nred[NB][8];
+    float* xs = reinterpret_cast<float*>(gemv_smem4);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int K4 = K >> 2, KC = K / E;
+    const int nb = min(NB, M);
+    const int row_base = blockIdx.x * rows_per_cta;
+    const int nrows = min(rows_per_cta, N - row_base);
+    const int ns = max(0, nrows - RR);                  // rows that go through shared memory
+    const uint32_t row_bytes = (uint32_t)K * (uint32_t)sizeof(WT);
+    unsigned char* wrows = reinterpret_cast<unsigned char*>(xs + (size_t)NB * K);
+
+    TL_T0
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int j = 0; j < ns; ++j) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bars[j])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    uint4 wreg[RPW > 0 ? RPW : 1][U];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+        const int lr = warp + 8 * r;                    // this warp's r-th register row
+        const WT* wp = W + (size_t)(row_base + min(lr, max(nrows - 1, 0))) * K;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = lane + 32 * u;
+            wreg[r][u] = lr < nrows ? __ldg(reinterpret_cast<const uint4*>(wp + (size_t)c * E)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+    // bulk copies of the other rows: all at once, or one every pace_ns so that the stream does not
+    // swamp the memory system while the kernels ahead in the chain wait for their few dependent loads
+    if (pace_ns <= 0) {
+        if ((int)threadIdx.x < ns) {
+            const int j = threadIdx.x;
+            const uint32_t bar = smem_u32(&bars[j]);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(row_bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(wrows + (size_t)j * row_bytes)), "l"(W + (size_t)(row_base + RR + j) * K), "r"(row_bytes), "r"(bar) : "memory");
+        }
+    } else if (threadIdx.x == 224) {
+        for (int j = 0; j < ns; ++j) {
+            const uint32_t bar = smem_u32(&bars[j]);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(row_bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(wrows + (size_t)j * row_bytes)), "l"(W + (size_t)(row_base + RR + j) * K), "r"(row_bytes), "r"(bar) : "memory");
+            __nanosleep(pace_ns);
+        }
+    }
+    float gam[XREG ? 1 : GN];
+    if constexpr (XREG) {
+        // the norm weights wait in the staging area (the activations themselves never go there)
+        if (gamma != nullptr) {
+            for (int i = threadIdx.x; i < K4; i += 256) reinterpret_cast<float4*>(xs)[i] = reinterpret_cast<const float4*>(gamma)[i];
+        }
+        gam[0] = 0.f;
+        __syncthreads();
+    } else {
+#pragma unroll
+        for (int i = 0; i < GN; ++i) {
+            const int k = threadIdx.x + 256 * i;
+            gam[i] = (gamma != nullptr && k < K) ? gamma[k] : 0.f;
+        }
+    }
+    pdl_wait();
+    TL_T1
+
+    // residuals of the rows whose stores this lane owns (register rows, first shared-memory group)
+    float rres_r[NB], rres_s[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) rres_r[b] = rres_s[b] = 0.f;
+    if (R != nullptr) {
+        if (lane < RPW && warp + 8 * lane < nrows) {
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+                if (b < nb) rres_r[b] = R[(size_t)b * ldd + row_base + warp + 8 * lane];
+        }
+        if (lane < GR && warp + 8 * lane < ns) {
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+                if (b < nb) rres_s[b] = R[(size_t)b * ldd + row_base + RR + warp + 8 * lane];
+        }
+    }
+
+    float xr[XREG ? U * E : 1];
+    if constexpr (XREG) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = lane + 32 * u;
+#pragma unroll
+            for (int q = 0; q < E / 4; ++q) {
+                const float4 v = *reinterpret_cast<const float4*>(A + c * E + 4 * q);
+                xr[u * E + 4 * q] = v.x; xr[u * E + 4 * q + 1] = v.y; xr[u * E + 4 * q + 2] = v.z; xr[u * E + 4 * q + 3] = v.w;
+            }
+        }
+        if (gamma != nullptr) {
+            // sum of squares: four running sums per lane (elements 0, 1, 2, 3 of its quads in ascending k),
+            // (s0 + s1) + (s2 + s3), then the xor tree
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < U * E; i += 4) {
+                s0 = fmaf(xr[i], xr[i], s0); s1 = fmaf(xr[i + 1], xr[i + 1], s1);
+                s2 = fmaf(xr[i + 2], xr[i + 2], s2); s3 = fmaf(xr[i + 3], xr[i + 3], s3);
+            }
+            const float tot = warp_sum(__fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3)));
+            const float rs = rms_scale(tot, K, eps);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int c = lane + 32 * u;
+#pragma unroll
+                for (int q = 0; q < E / 4; ++q) {
+                    const float4 gq = *reinterpret_cast<const float4*>(xs + c * E + 4 * q);
+                    const int i = u * E + 4 * q;
+                    xr[i] = __fmul_rn(__fmul_rn(xr[i], rs), gq.x); xr[i + 1] = __fmul_rn(__fmul_rn(xr[i + 1], rs), gq.y);
+                    xr[i + 2] = __fmul_rn(__fmul_rn(xr[i + 2], rs), gq.z); xr[i + 3] = __fmul_rn(__fmul_rn(xr[i + 3], rs), gq.w);
+                }
+            }
+        }
+        TL_MARK(2)
+    } else {
+        for (int i = threadIdx.x; i < NB * K4; i += 256) {
+            int b = i / K4, k4 = i - b * K4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (b < nb) v = *reinterpret_cast<const float4*>(A + (size_t)b * lda + 4 * k4);
+            reinterpret_cast<float4*>(xs)[i] = v;
+        }
+        __syncthreads();
+        TL_MARK(2)
+        if (gamma != nullptr) {
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                float s = 0.f;
+                if (b < nb) for (int k = threadIdx.x; k < K; k += 256) s = fmaf(xs[b * K + k], xs[b * K + k], s);
+                s = warp_sum(s);
+                if (lane == 0) nred[b][warp] = s;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                if (b < nb) {
+                    float t = 0.f;
+#pragma unroll
+                    for (int w = 0; w < 8; ++w) t += nred[b][w];
+                    const float r = rms_scale(t, K, eps);
+#pragma unroll
+                    for (int i = 0; i < GN; ++i) {
+                        const int k = threadIdx.x + 256 * i;
+                        if (k < K) xs[b * K + k] = __fmul_rn(__fmul_rn(xs[b * K + k], r), gam[i]);
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    // Rows are evaluated several at a time so that their multiply-add chains overlap; each row keeps two
+    // accumulators (even and odd chunks) that are added at the end.  Lane s of a warp owns the residual
+    // and the store of the warp's s-th row of a pass.
+    auto accum = [&](const uint4& wv, int u, int c, float (&acc)[NB]) {
+        float w[E];
+        WRaw<WT>::cvt(wv, w);
+        if constexpr (XREG) {
+#pragma unroll
+            for (int e = 0; e < E; ++e) acc[0] = fmaf(w[e], xr[u * E + e], acc[0]);
+        } else {
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+#pragma unroll
+                for (int q = 0; q < E / 4; ++q) {
+                    const float4 v = *reinterpret_cast<const float4*>(xs + b * K + c * E + 4 * q);
+                    acc[b] = fmaf(w[4 * q], v.x, acc[b]);
+                    acc[b] = fmaf(w[4 * q + 1], v.y, acc[b]);
+                    acc[b] = fmaf(w[4 * q + 2], v.z, acc[b]);
+                    acc[b] = fmaf(w[4 * q + 3], v.w, acc[b]);
+                }
+            }
+        }
+    };
+
+    if constexpr (RPW > 0) {
+        float acc[RPW][2][NB];
+#pragma unroll
+        for (int r = 0; r < RPW; ++r)
+#pragma unroll
+            for (int b = 0; b < NB; ++b) acc[r][0][b] = acc[r][1][b] = 0.f;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = lane + 32 * u;
+#pragma unroll
+            for (int r = 0; r < RPW; ++r) accum(wreg[r][u], u, c, acc[r][u & 1]);
+        }
+#pragma unroll
+        for (int r = 0; r < RPW; ++r)
+#pragma unroll
+            for (int b = 0; b < NB; ++b) acc[r][0][b] = warp_sum(__fadd_rn(acc[r][0][b], acc[r][1][b]));
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+            if (lane == r && warp + 8 * r < nrows) {
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+                    if (b < nb) {
+                        float v = acc[r][0][b];
+                        if (R != nullptr) v = __fadd_rn(v, rres_r[b]);
+                        D[(size_t)b * ldd + row_base + warp + 8 * r] = v;
+                    }
+            }
+        }
+    }
+    TL_MARK(3)
+    bool timed_out = false;
+    for (int j0 = warp; j0 < ns && !timed_out; j0 += 8 * GR) {
+        if (j0 != warp) {            // later groups (rare): their residuals are fetched here
+#pragma unroll
+            for (int b = 0; b < NB; ++b) rres_s[b] = 0.f;
+            if (R != nullptr && lane < GR && j0 + 8 * lane < ns) {
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+                    if (b < nb) rres_s[b] = R[(size_t)b * ldd + row_base + RR + j0 + 8 * lane];
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < GR; ++g) {
+            const int j = j0 + 8 * g;
+            if (j >= ns) break;
+            const uint32_t bar = smem_u32(&bars[j]);
+            uint32_t done = 0, polls = 0;
+            uint64_t t0 = 0;
+            while (true) {
+                asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\nselp.u32 %0, 1, 0, p;\n}"
+                             : "=r"(done) : "r"(bar) : "memory");
+                if (done) break;
+                if ((++polls & 255u) == 0u) {           // the clock is read rarely: it is slow to read
+                    const uint64_t now = globaltimer_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > 500000000ull) { timed_out = true; break; }
+                }
+            }
+            if (timed_out) break;
+        }
+        if (timed_out) break;
+        if (j0 == warp) { TL_MARK(4) }
+        const int ng = min(GR, (ns - j0 + 7) / 8);      // valid rows of this group
+        // one straight-line body per row count, so that no branch sits between the loads and their use
+        auto body = [&](auto ngc) {
+            constexpr int NG = decltype(ngc)::value;
+            float acc[NG][2][NB];
+#pragma unroll
+            for (int g = 0; g < NG; ++g)
+#pragma unroll
+                for (int b = 0; b < NB; ++b) acc[g][0][b] = acc[g][1][b] = 0.f;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int c = lane + 32 * u;
+                uint4 wv[NG];
+#pragma unroll
+                for (int g = 0; g < NG; ++g) wv[g] = reinterpret_cast<const uint4*>(wrows + (size_t)(j0 + 8 * g) * row_bytes)[c];
+#pragma unroll
+                for (int g = 0; g < NG; ++g) accum(wv[g], u, c, acc[g][u & 1]);
+            }
+#pragma unroll
+            for (int g = 0; g < NG; ++g)
+#pragma unroll
+                for (int b = 0; b < NB; ++b) acc[g][0][b] = warp_sum(__fadd_rn(acc[g][0][b], acc[g][1][b]));
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                if (lane == g) {
+#pragma unroll
+                    for (int b = 0; b < NB; ++b)
+                        if (b < nb) {
+                            float v = acc[g][0][b];
+                            if (R != nullptr) v = __fadd_rn(v, rres_s[b]);
+                            D[(size_t)b * ldd + row_base + RR + j0 + 8 * g] = v;
+                        }
+                }
+            }
+        };
+        switch (ng) {
+            case 1: body(std::integral_constant<int, 1>{}); break;
+            case 2: body(std::integral_constant<int, 2>{}); break;
+            case 3: body(std::integral_constant<int, 3>{}); break;
+            case 4: body(std::integral_constant<int, 4>{}); break;
+            case 5: if constexpr (GR >= 5) body(std::integral_constant<int, 5>{}); break;
+            case 6: if constexpr (GR >= 6) body(std::integral_constant<int, 6>{}); break;
+            default: break;
+        }
+    }
+    if (timed_out && lane == 0 && status != nullptr) atomicOr(status, STATUS_TIMEOUT);
+    TL_END(K == 1024 ? 1 : 3)
+}
+
 // ---- fused Mamba-3 decode step ---------------------------------------------------------------------
 // One warp per (sequence, head).  Prologue: BCNorm statistics over all n_groups*d_state elements
 // (block-wide), per-head scalars, DD-RoPE with one rotation pair per lane, staged in shared memory.
@@ -310,6 +665,7 @@ __global__ void __launch_bounds__(256, MINB) ssm_step_kernel(SsmArgs a) {
     const size_t bh = (size_t)b * H + (active ? h : H - 1);
     const int c = lane % CG, r0 = lane / CG;
 
+    TL_T0
     pdl_launch_dependents();
     // State is only ever written by this same kernel one token earlier, and every step starts with a
     // kernel that is not launched early, so the whole previous step has finished before this line:
@@ -326,7 +682,25 @@ __global__ void __launch_bounds__(256, MINB) ssm_step_kernel(SsmArgs a) {
 #pragma unroll
         for (int j = 0; j < (HN + 31) / 32; ++j) cu_old[j] = (lane + 32 * j < HN) ? a.cum[bh * HN + lane + 32 * j] : 0.f;
     }
+    // parameters of the layer and the factor of the previous token: not produced by the predecessor either
+    const int hh = active ? h : H - 1;
+    const int g = hh / (H / a.G);
+    const float v_dtb = a.dtb[hh], v_dskip = a.dskip[hh];
+    constexpr int NJ = (N / 2 + 31) / 32;
+    float g_b0[NJ], g_b1[NJ], g_c0[NJ], g_c1[NJ], o_b0[NJ], o_b1[NJ], o_c0[NJ], o_c1[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        const int k = min(lane + 32 * j, HN - 1);
+        const int i0 = g * N + 2 * k;
+        g_b0[j] = a.bg[i0]; g_b1[j] = a.bg[i0 + 1]; g_c0[j] = a.cg[i0]; g_c1[j] = a.cg[i0 + 1];
+        o_b0[j] = a.bb[i0]; o_b1[j] = a.bb[i0 + 1]; o_c0[j] = a.cb[i0]; o_c1[j] = a.cb[i0 + 1];
+    }
+    constexpr int ROWS_PL = (P / WPH + 31) / 32;
+    float v_xp[ROWS_PL];
+#pragma unroll
+    for (int j = 0; j < ROWS_PL; ++j) v_xp[j] = a.xprev[bh * P + min(sub * ROWS + lane + 32 * j, P - 1)];
     pdl_wait();
+    TL_T1
 
     const float* pr = a.proj + (size_t)b * a.ldp;
     const float* Bp = pr + 2 * DI;
@@ -335,36 +709,72 @@ __global__ void __launch_bounds__(256, MINB) ssm_step_kernel(SsmArgs a) {
     const float* lam_raw = dt + H;
     const float* dda = dt + 2 * H;
     const float* theta = dt + 3 * H;
-    const int hh = active ? h : H - 1;
-    const int g = hh / (H / a.G);
 
-    // every global value the prologue needs is requested here, ahead of the block barrier, so the
+    // every value of the predecessor that the prologue needs is requested here, ahead of any use, so the
     // loads overlap instead of forming a chain of round trips
-    const float v_dt = dt[hh], v_dtb = a.dtb[hh], v_dda = dda[hh], v_lam = lam_raw[hh], v_dskip = a.dskip[hh];
-    constexpr int NJ = (N / 2 + 31) / 32;
-    float v_th[NJ], v_b0[NJ], v_b1[NJ], v_c0[NJ], v_c1[NJ], g_b0[NJ], g_b1[NJ], g_c0[NJ], g_c1[NJ], o_b0[NJ], o_b1[NJ], o_c0[NJ], o_c1[NJ];
+    const float v_dt = dt[hh], v_dda = dda[hh], v_lam = lam_raw[hh];
+    float v_th[NJ], v_b0[NJ], v_b1[NJ], v_c0[NJ], v_c1[NJ];
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
         const int k = min(lane + 32 * j, HN - 1);
         const int i0 = g * N + 2 * k;
         v_th[j] = theta[hh * HN + k];
         v_b0[j] = Bp[i0]; v_b1[j] = Bp[i0 + 1]; v_c0[j] = Cp[i0]; v_c1[j] = Cp[i0 + 1];
-        g_b0[j] = a.bg[i0]; g_b1[j] = a.bg[i0 + 1]; g_c0[j] = a.cg[i0]; g_c1[j] = a.cg[i0 + 1];
-        o_b0[j] = a.bb[i0]; o_b1[j] = a.bb[i0 + 1]; o_c0[j] = a.cb[i0]; o_c1[j] = a.cb[i0 + 1];
     }
-    constexpr int ROWS_PL = (P / WPH + 31) / 32;
-    float v_x[ROWS_PL], v_z[ROWS_PL], v_xp[ROWS_PL];
+    float v_x[ROWS_PL], v_z[ROWS_PL];
 #pragma unroll
     for (int j = 0; j < ROWS_PL; ++j) {
         const int row = min(sub * ROWS + lane + 32 * j, P - 1);
         v_x[j] = pr[hh * P + row];
         v_z[j] = pr[DI + hh * P + row];
-        v_xp[j] = a.xprev[bh * P + row];
+    }
+    // BCNorm statistics (model.rs:311-312: the norm runs over the whole bc vector): the first NQ rounds of
+    // 16-byte loads go out together; what is left (large BC, small CTAs, odd layouts) runs as a plain loop.
+    // Order of the sum: per thread its quads in ascending position (x, y, z, w within a quad), then the rest
+    // loop, the xor tree, and the warps in order.
+    constexpr int NQ = WPH == 1 ? 1 : 2;
+    const bool vec_ok = ((a.ldp | (2 * DI) | BC) & 3) == 0 && (reinterpret_cast<uintptr_t>(a.proj) & 15) == 0;
+    const int BC4 = vec_ok ? (BC >> 2) : 0;
+    float4 qb[NQ], qc[NQ];
+#pragma unroll
+    for (int j = 0; j < NQ; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        qb[j] = i < BC4 ? reinterpret_cast<const float4*>(Bp)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        qc[j] = i < BC4 ? reinterpret_cast<const float4*>(Cp)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 
-    // BCNorm statistics (model.rs:311-312: the norm runs over the whole bc vector)
+    // per-head scalars (model.rs:307, 314-317, 355-359) and the rotation angles (model.rs:338-345): they do not
+    // need the statistics, so their arithmetic runs while the loads above are still in flight
+    const float dtp = softplus_ref(__fadd_rn(v_dt, v_dtb));
+    float av = -softplus_ref(v_dda);
+    av = fminf(fmaxf(av, -1e6f), -1e-4f);
+    const float abar = expf(__fmul_rn(av, dtp));
+    const float lam = sigmoid_ref(v_lam);
+    const float oml = __fadd_rn(__fmul_rn(lam, -1.0f), 1.0f);
+    const float c2 = __fmul_rn(abar, oml);
+    const float PI_F = 3.14159265358979323846f;
+    const float TWO_PI = __fmul_rn(2.0f, PI_F);
+    float cu_new[NJ], sa[NJ], ca[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        const float angle = __fmul_rn(tanhf(v_th[j]), PI_F);
+        cu_new[j] = fmodf(__fadd_rn(cu_old[j], __fmul_rn(dtp, angle)), TWO_PI);
+        sincosf(cu_new[j], &sa[j], &ca[j]);
+    }
+    float xa_v[ROWS_PL], gate_v[ROWS_PL];
+#pragma unroll
+    for (int j = 0; j < ROWS_PL; ++j) {
+        xa_v[j] = silu_ref(v_x[j]);                          // model.rs:310
+        gate_v[j] = silu_ref(v_z[j]);                        // model.rs:370
+    }
+
     float sb = 0.f, sc = 0.f;
-    for (int i = threadIdx.x; i < BC; i += blockDim.x) {
+#pragma unroll
+    for (int j = 0; j < NQ; ++j) {
+        sb = fmaf(qb[j].x, qb[j].x, sb); sb = fmaf(qb[j].y, qb[j].y, sb); sb = fmaf(qb[j].z, qb[j].z, sb); sb = fmaf(qb[j].w, qb[j].w, sb);
+        sc = fmaf(qc[j].x, qc[j].x, sc); sc = fmaf(qc[j].y, qc[j].y, sc); sc = fmaf(qc[j].z, qc[j].z, sc); sc = fmaf(qc[j].w, qc[j].w, sc);
+    }
+    for (int i = (vec_ok ? 4 * NQ * (int)blockDim.x : 0) + threadIdx.x; i < BC; i += blockDim.x) {
         float v = Bp[i];
         sb = fmaf(v, v, sb);
         v = Cp[i];
@@ -374,6 +784,7 @@ __global__ void __launch_bounds__(256, MINB) ssm_step_kernel(SsmArgs a) {
     sc = warp_sum(sc);
     if (lane == 0) { red[0][warp] = sb; red[1][warp] = sc; }
     __syncthreads();       // also orders every warp's reads of bprev / cum / xprev above before the writes below
+    TL_MARK(2)
     if (!active) return;
     float tb = 0.f, tc = 0.f;
     for (int w = 0; w < nwarp; ++w) { tb += red[0][w]; tc += red[1][w]; }
@@ -381,35 +792,20 @@ __global__ void __launch_bounds__(256, MINB) ssm_step_kernel(SsmArgs a) {
 
     SsmSmem<P, N>& sm = sm_all[warp];
 
-    // per-head scalars (model.rs:307, 314-317, 355-359)
-    const float dtp = softplus_ref(__fadd_rn(v_dt, v_dtb));
-    float av = -softplus_ref(v_dda);
-    av = fminf(fmaxf(av, -1e6f), -1e-4f);
-    const float abar = expf(__fmul_rn(av, dtp));
-    const float lam = sigmoid_ref(v_lam);
-    const float oml = __fadd_rn(__fmul_rn(lam, -1.0f), 1.0f);
-    const float c2 = __fmul_rn(abar, oml);
-
-    // DD-RoPE (model.rs:338-350): lane k rotates pair (2k, 2k+1) of the normalised B and C
-    const float PI_F = 3.14159265358979323846f;
-    const float TWO_PI = __fmul_rn(2.0f, PI_F);
+    // DD-RoPE (model.rs:346-350): lane k rotates pair (2k, 2k+1) of the normalised B and C
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
         const int k = lane + 32 * j;
         if (k < HN) {
-            float angle = __fmul_rn(tanhf(v_th[j]), PI_F);
-            float cu = fmodf(__fadd_rn(cu_old[j], __fmul_rn(dtp, angle)), TWO_PI);
-            if (sub == 0) a.cum[bh * HN + k] = cu;
-            float sa, ca;
-            sincosf(cu, &sa, &ca);
+            if (sub == 0) a.cum[bh * HN + k] = cu_new[j];
             float b0 = __fadd_rn(__fmul_rn(__fmul_rn(v_b0[j], rb), g_b0[j]), o_b0[j]);
             float b1 = __fadd_rn(__fmul_rn(__fmul_rn(v_b1[j], rb), g_b1[j]), o_b1[j]);
             float c0 = __fadd_rn(__fmul_rn(__fmul_rn(v_c0[j], rc), g_c0[j]), o_c0[j]);
             float c1 = __fadd_rn(__fmul_rn(__fmul_rn(v_c1[j], rc), g_c1[j]), o_c1[j]);
-            sm.bt[2 * k] = __fsub_rn(__fmul_rn(ca, b0), __fmul_rn(sa, b1));
-            sm.bt[2 * k + 1] = __fadd_rn(__fmul_rn(sa, b0), __fmul_rn(ca, b1));
-            sm.ct[2 * k] = __fsub_rn(__fmul_rn(ca, c0), __fmul_rn(sa, c1));
-            sm.ct[2 * k + 1] = __fadd_rn(__fmul_rn(sa, c0), __fmul_rn(ca, c1));
+            sm.bt[2 * k] = __fsub_rn(__fmul_rn(ca[j], b0), __fmul_rn(sa[j], b1));
+            sm.bt[2 * k + 1] = __fadd_rn(__fmul_rn(sa[j], b0), __fmul_rn(ca[j], b1));
+            sm.ct[2 * k] = __fsub_rn(__fmul_rn(ca[j], c0), __fmul_rn(sa[j], c1));
+            sm.ct[2 * k + 1] = __fadd_rn(__fmul_rn(sa[j], c0), __fmul_rn(ca[j], c1));
         }
     }
     const int prow0 = sub * ROWS;          // first state row of this warp
@@ -418,13 +814,14 @@ __global__ void __launch_bounds__(256, MINB) ssm_step_kernel(SsmArgs a) {
         const int p = lane + 32 * j;
         if (p < ROWS) {
             const int row = prow0 + p;
-            sm.xa[row] = silu_ref(v_x[j]);                  // model.rs:310
+            sm.xa[row] = xa_v[j];
             sm.xp[row] = v_xp[j];
-            sm.gate[row] = silu_ref(v_z[j]);                // model.rs:370
+            sm.gate[row] = gate_v[j];
         }
     }
     __syncwarp();
 
+    TL_MARK(3)
     const float4 bq = reinterpret_cast<const float4*>(sm.bt)[c];
     const float4 cq = reinterpret_cast<const float4*>(sm.ct)[c];
 #pragma unroll 1
@@ -456,6 +853,7 @@ __global__ void __launch_bounds__(256, MINB) ssm_step_kernel(SsmArgs a) {
         }
     }
     __syncwarp();
+    TL_MARK(4)
     for (int p = lane; p < ROWS; p += 32) {
         const int row = prow0 + p;
         float xv = sm.xa[row];
@@ -473,6 +871,7 @@ __global__ void __launch_bounds__(256, MINB) ssm_step_kernel(SsmArgs a) {
     }
     if (sub == 0)
         for (int s2 = lane; s2 < N; s2 += 32) a.bprev[bh * N + s2] = sm.bt[s2];
+    TL_END(2)
 }
 
 // h <- h_init broadcast over head_dim (model.rs:744-748); factors and angles <- 0 (:751-752)
@@ -528,7 +927,7 @@ constexpr int kMaxTopK = 256;
 // One block per sequence.  Greedy: argmax with the lowest index on ties.  Otherwise temperature
 // softmax over the top-k survivors (or the whole vocabulary) and the walk over the cumulative
 // distribution in vocabulary order.
-__global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ logits, int V, StepCtl* ctl,
+__global__ void __launch_bounds__(1024) sample_kernel(const float* logits, int V, StepCtl* ctl,
                                                       uint32_t* tok_cur, int32_t* finished, int32_t* out_len) {
     __shared__ BestPair red[32];
     __shared__ float top_v[kMaxTopK];
@@ -645,7 +1044,7 @@ __global__ void advance_step_kernel(StepCtl* ctl, int32_t* kv_pos, int B, int sa
 }
 
 // D = sigmoid(gate) * up for the attention block's MLP (model.rs:550-552); gu = [gate | up] per row
-__global__ void gate_mul_kernel(const float* __restrict__ gu, int ld, float* out32, __nv_bfloat16* hi, __nv_bfloat16* lo,
+__global__ void gate_mul_kernel(const float* gu, int ld, float* out32, __nv_bfloat16* hi, __nv_bfloat16* lo,
                                 int mlp) {
     const int b = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -743,8 +1142,97 @@ static cudaError_t gemv_by_batch(const GemvArgs& a, cudaStream_t st) {
     return gemv_dispatch<WT, 8, 0>(a, st);
 }
 
+// ---- the preloading single-wave variant: when it applies and how it is launched ----
+static int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
+// LUMI_GEMV_PRE=0 keeps every small-batch product on the multi-wave kernel (tuning aid).
+static bool gemv_pre_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("LUMI_GEMV_PRE"); v = e ? atoi(e) : 1; }
+    return v != 0;
+}
+
+// LUMI_GEMV_PACE_NS: pause between the bulk copies of a CTA's shared-memory rows (0 = all at once).
+static int gemv_pre_pace_ns() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("LUMI_GEMV_PACE_NS"); v = e ? atoi(e) : 0; }
+    return v;
+}
+
+static int gemv_pre_policy() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("LUMI_GEMV_PRE_POLICY"); v = e ? atoi(e) : 0; }
+    return v;
+}
+
+constexpr size_t kPreSmemBudget = 176 * 1024;      // leaves room on the SM for the neighbouring kernels of the chain
+constexpr size_t kPreAllSmemBytes = 64 * 1024;     // a CTA share up to this size goes through shared memory only
+
+template <typename WT, int NB, int U, int RPW>
+static cudaError_t gemv_pre_launch(const GemvArgs& a, int rows_per_cta, size_t smem, cudaStream_t st) {
+    auto kern = gemv_pre_kernel<WT, NB, U, RPW>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    dim3 grid((a.N + rows_per_cta - 1) / rows_per_cta);
+    return launch_k(kern, grid, dim3(256), smem, st, a.A, a.lda, (const WT*)a.W, a.D, a.ldd, a.R, a.gamma, a.M, a.N, a.K, a.eps,
+                    rows_per_cta, gemv_pre_pace_ns(), a.status);
+}
+
+// Returns true (and the launch result in *err) when the product was given to the preloading kernel.
+template <typename WT>
+static bool gemv_pre_try(const GemvArgs& a, cudaStream_t st, cudaError_t* err) {
+    constexpr int E = WLoad<WT>::E;
+    if (!gemv_pre_enabled() || a.act != 0 || a.M > 4 || a.M < 1 || (a.K % E) != 0 || a.K < E) return false;
+    const int KC = a.K / E;
+    const int U = (KC + 31) / 32;
+    if (U > 16 || KC != 32 * U || (U & (U - 1)) != 0) return false;     // rows of exactly 32 * U chunks, U a power of two
+    const int NB = a.M <= 1 ? 1 : (a.M <= 2 ? 2 : 4);
+    const int rows_per_cta = (a.N + sm_count() - 1) / sm_count();
+    const size_t row_bytes = (size_t)a.K * sizeof(WT);
+    // small shares: shared memory only (few registers); larger ones: two rows per warp in registers
+    // (one when a row is long), the rest in shared memory
+    // one register row per warp plus shared-memory rows measured best for the chain of a block at batch 1;
+    // LUMI_GEMV_PRE_POLICY=1 (tuning aid): small shares through shared memory only, large ones with two
+    // register rows per warp
+    int RPW = 1;
+    if (gemv_pre_policy() == 1) {
+        RPW = 0;
+        if (rows_per_cta * row_bytes > kPreAllSmemBytes) RPW = U <= 8 ? 2 : 1;
+    }
+    const int smem_rows = rows_per_cta > 8 * RPW ? rows_per_cta - 8 * RPW : 0;
+    const size_t smem = (size_t)NB * a.K * sizeof(float) + smem_rows * row_bytes;
+    if (smem_rows > kPreMaxSmemRows || smem > kPreSmemBudget) return false;
+#define LUMI_PRE_CASE(NBV, UV)                                                                                    \
+    if (NB == NBV && U <= UV) {                                                                                  \
+        if (RPW == 0) *err = gemv_pre_launch<WT, NBV, UV, 0>(a, rows_per_cta, smem, st);                         \
+        else if (RPW == 1) *err = gemv_pre_launch<WT, NBV, UV, 1>(a, rows_per_cta, smem, st);                    \
+        else *err = gemv_pre_launch<WT, NBV, UV, (UV <= 8 ? 2 : 1)>(a, rows_per_cta, smem, st);                  \
+        return true;                                                                                             \
+    }
+    LUMI_PRE_CASE(1, 1) LUMI_PRE_CASE(1, 2) LUMI_PRE_CASE(1, 4) LUMI_PRE_CASE(1, 8) LUMI_PRE_CASE(1, 16)
+    LUMI_PRE_CASE(2, 1) LUMI_PRE_CASE(2, 2) LUMI_PRE_CASE(2, 4) LUMI_PRE_CASE(2, 8) LUMI_PRE_CASE(2, 16)
+    LUMI_PRE_CASE(4, 1) LUMI_PRE_CASE(4, 2) LUMI_PRE_CASE(4, 4) LUMI_PRE_CASE(4, 8) LUMI_PRE_CASE(4, 16)
+#undef LUMI_PRE_CASE
+    return false;
+}
+
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st) {
-    if (a.w_dtype == LUMI_DTYPE_BF16) return gemv_by_batch<__nv_bfloat16>(a, st);
+    cudaError_t e = cudaSuccess;
+    if (a.w_dtype == LUMI_DTYPE_BF16) {
+        if (gemv_pre_try<__nv_bfloat16>(a, st, &e)) return e;
+        return gemv_by_batch<__nv_bfloat16>(a, st);
+    }
+    if (gemv_pre_try<float>(a, st, &e)) return e;
     return gemv_by_batch<float>(a, st);
 }
 
@@ -773,7 +1261,9 @@ static cudaError_t ssm_launch(const SsmArgs& a, cudaStream_t st) {
     constexpr int IT = P / (128 / N);
     if constexpr (IT % 4 == 0) {
         if (a.B <= 8) {        // small batch: four warps per head, two heads per CTA
-            int hpb = a.H < 2 ? a.H : 2;
+            static int hpb_env = -1;
+            if (hpb_env < 0) { const char* e = getenv("LUMI_SSM_HPB"); hpb_env = e ? atoi(e) : 1; }
+            int hpb = a.H < hpb_env ? a.H : hpb_env;
             dim3 grid((a.H + hpb - 1) / hpb, a.B);
             return launch_k(ssm_step_kernel<P, N, 4, 3>, grid, dim3(hpb * 4 * 32), 0, st, a);
         }
@@ -823,3 +1313,16 @@ cudaError_t launch_gate_mul(const float* gu, int ld, float* out32, __nv_bfloat16
 }
 
 }  // namespace lumi
+
+#ifdef LUMI_TIMELINE
+extern "C" int lumi_debug_timeline(unsigned long long* out, int max_records, int reset) {
+    unsigned n = 0;
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(&n, lumi::g_tl_n, sizeof(n));
+    if (n > 65536u) n = 65536u;
+    if ((int)n > max_records) n = max_records;
+    if (out && n) cudaMemcpyFromSymbol(out, lumi::g_tl, (size_t)n * 10 * sizeof(unsigned long long));
+    if (reset) { unsigned z = 0; cudaMemcpyToSymbol(lumi::g_tl_n, &z, sizeof(z)); }
+    return (int)n;
+}
+#endif

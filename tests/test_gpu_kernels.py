@@ -14,7 +14,8 @@ def _torch():
 
 
 @pytest.mark.parametrize("wdt", ["f32", "bf16"])
-@pytest.mark.parametrize("M,N,K", [(1, 7360, 1024), (3, 1000, 2048), (8, 259, 1024), (20, 512, 128)])
+@pytest.mark.parametrize("M,N,K", [(1, 7360, 1024), (3, 1000, 2048), (8, 259, 1024), (20, 512, 128),
+                                   (1, 1024, 2048), (2, 7360, 1024), (4, 3000, 512), (1, 100, 128), (1, 9000, 1024), (2, 2960, 4096)])
 def test_gemv_matches_fp64(wdt, M, N, K):
     torch = _torch()
     g = np.random.default_rng(M * 1000 + N)
