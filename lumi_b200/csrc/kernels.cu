@@ -330,7 +330,7 @@ template <typename WT, int NB, int U, int RPW>
 __global__ void __launch_bounds__(256, 2) gemv_pre_kernel(const float* A, int lda, const WT* __restrict__ W,
                                                           float* D, int ldd, const float* R,
                                                           const float* __restrict__ gamma, int M, int N, int K, float eps,
-                                                          int rows_per_cta, int pace_ns, int32_t* status) {
+                                                          int rows_per_cta, int pace_ns, int pre_delay_ns, int32_t* status) {
     extern __shared__ float4 gemv_smem4[];
     constexpr int E = WLoad<WT>::E;
     constexpr int GN = (U * E + 7) / 8;                 // gamma values per thread: K / 256 rounded up
@@ -340,7 +340,7 @@ __global__ void __launch_bounds__(256, 2) gemv_pre_kernel(const float* A, int ld
     // 16-byte chunks l, l + 32, ... — exactly the ones it multiplies), computes the RMSNorm scale itself and
     // never touches shared memory or a block barrier for the activations.
     constexpr bool XREG = (NB == 1) && (U * E <= 32);
-    __shared__ __align__(8) uint64_t bars[kPreMaxSmemRows];
+    __shared__ __align__(8) uint64_t bars[8];           // one per warp: completes when all of that warp's rows have landed
     __shared__ float nred[NB][8];
     float* xs = reinterpret_cast<float*>(gemv_smem4);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -355,10 +355,15 @@ __global__ void __launch_bounds__(256, 2) gemv_pre_kernel(const float* A, int ld
     TL_T0
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
-        for (int j = 0; j < ns; ++j) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bars[j])));
+        for (int j = 0; j < 8; ++j) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bars[j])));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    if (threadIdx.x < 8 && (int)threadIdx.x < ns) {     // rows threadIdx.x, threadIdx.x + 8, ... belong to that warp
+        const uint32_t bytes = (uint32_t)((ns - (int)threadIdx.x + 7) / 8) * row_bytes;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&bars[threadIdx.x])), "r"(bytes) : "memory");
+    }
+    if (pre_delay_ns > 0) __nanosleep(pre_delay_ns);
     uint4 wreg[RPW > 0 ? RPW : 1][U];
 #pragma unroll
     for (int r = 0; r < RPW; ++r) {
@@ -375,15 +380,13 @@ __global__ void __launch_bounds__(256, 2) gemv_pre_kernel(const float* A, int ld
     if (pace_ns <= 0) {
         if ((int)threadIdx.x < ns) {
             const int j = threadIdx.x;
-            const uint32_t bar = smem_u32(&bars[j]);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(row_bytes) : "memory");
+            const uint32_t bar = smem_u32(&bars[j & 7]);
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                          ::"r"(smem_u32(wrows + (size_t)j * row_bytes)), "l"(W + (size_t)(row_base + RR + j) * K), "r"(row_bytes), "r"(bar) : "memory");
         }
     } else if (threadIdx.x == 224) {
         for (int j = 0; j < ns; ++j) {
-            const uint32_t bar = smem_u32(&bars[j]);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(row_bytes) : "memory");
+            const uint32_t bar = smem_u32(&bars[j & 7]);
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                          ::"r"(smem_u32(wrows + (size_t)j * row_bytes)), "l"(W + (size_t)(row_base + RR + j) * K), "r"(row_bytes), "r"(bar) : "memory");
             __nanosleep(pace_ns);
@@ -560,11 +563,8 @@ __global__ void __launch_bounds__(256, 2) gemv_pre_kernel(const float* A, int ld
                     if (b < nb) rres_s[b] = R[(size_t)b * ldd + row_base + RR + j0 + 8 * lane];
             }
         }
-#pragma unroll
-        for (int g = 0; g < GR; ++g) {
-            const int j = j0 + 8 * g;
-            if (j >= ns) break;
-            const uint32_t bar = smem_u32(&bars[j]);
+        if (j0 == warp) {
+            const uint32_t bar = smem_u32(&bars[warp]);
             uint32_t done = 0, polls = 0;
             uint64_t t0 = 0;
             while (true) {
@@ -1173,6 +1173,14 @@ static int gemv_pre_policy() {
     return v;
 }
 
+// LUMI_GEMV_PRE_DELAY_NS: a CTA with a large share waits this long before it requests its weights, so that
+// the few dependent loads of the kernel that has just been released go ahead of the burst.
+static int gemv_pre_delay_ns() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("LUMI_GEMV_PRE_DELAY_NS"); v = e ? atoi(e) : 0; }
+    return v;
+}
+
 constexpr size_t kPreSmemBudget = 176 * 1024;      // leaves room on the SM for the neighbouring kernels of the chain
 constexpr size_t kPreAllSmemBytes = 64 * 1024;     // a CTA share up to this size goes through shared memory only
 
@@ -1185,7 +1193,7 @@ static cudaError_t gemv_pre_launch(const GemvArgs& a, int rows_per_cta, size_t s
     }
     dim3 grid((a.N + rows_per_cta - 1) / rows_per_cta);
     return launch_k(kern, grid, dim3(256), smem, st, a.A, a.lda, (const WT*)a.W, a.D, a.ldd, a.R, a.gamma, a.M, a.N, a.K, a.eps,
-                    rows_per_cta, gemv_pre_pace_ns(), a.status);
+                    rows_per_cta, gemv_pre_pace_ns(), smem > 64 * 1024 ? gemv_pre_delay_ns() : 0, a.status);
 }
 
 // Returns true (and the launch result in *err) when the product was given to the preloading kernel.
