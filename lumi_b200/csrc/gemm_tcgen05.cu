@@ -251,6 +251,166 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__
     }
 }
 
+// ---- persistent form: one CTA per SM walks over tiles, two accumulators in TMEM ---------------------
+// Used when a problem has more tiles than SMs.  The epilogue of tile i (TMEM -> registers -> global)
+// runs while the tensor core already works on tile i + 1 in the other accumulator, and TMEM allocation,
+// barrier set-up and pipeline fill are paid once per CTA instead of once per tile.  Tiles are numbered
+// with the row-tile index fastest, so the CTAs running at the same time share weight tiles in L2.
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN, bool SPLIT>
+__global__ void __launch_bounds__(192, 1)
+gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
+                       const __grid_constant__ CUtensorMap map_w, float* D, int ldd, int M, int N, int K,
+                       int accumulate, int tiles_m, int ntiles, int32_t* status) {
+    using T = Tile<BN, SPLIT, 1>;
+    constexpr int S = T::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(base + S * T::STAGE);
+    uint64_t* empty_bar = full_bar + S;
+    uint64_t* tmem_full = empty_bar + S;          // [2]
+    uint64_t* tmem_empty = tmem_full + 2;         // [2]
+    uint64_t* drain_bar = tmem_empty + 2;         // failure path only
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = K / BK;
+
+    if (status != nullptr && (*reinterpret_cast<volatile int32_t*>(status) & STATUS_TIMEOUT)) return;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&tmem_full[i], 1); mbar_init(&tmem_empty[i], 4); }
+        mbar_init(drain_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    constexpr uint32_t ACC_COLS = BN > 128 ? 256u : (BN > 64 ? 128u : 64u);      // TMEM columns per accumulator (allocation is a power of two)
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2u * ACC_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    bool timed_out = false;
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t kbg = 0;                    // k-blocks issued so far, over all tiles of this CTA
+            for (int t = blockIdx.x; t < ntiles && !timed_out; t += gridDim.x) {
+                const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++kbg) {
+                    const int s = kbg % S;
+                    const uint32_t ph = (kbg / S) & 1u;
+                    if (!mbar_wait(&empty_bar[s], ph ^ 1u)) { timed_out = true; break; }
+                    uint8_t* st = base + s * T::STAGE;
+                    mbar_expect_tx(&full_bar[s], (uint32_t)T::STAGE);
+                    tma_load_2d(st, &map_ahi, &full_bar[s], kb * BK, m0);
+                    if (SPLIT) tma_load_2d(st + T::A_BYTES, &map_alo, &full_bar[s], kb * BK, m0);
+                    tma_load_2d(st + T::A_BYTES * (SPLIT ? 2 : 1), &map_w, &full_bar[s], kb * BK, n0);
+                }
+            }
+            if (timed_out) {
+                // drain: wait (bounded) for the copies this thread issued and nobody may consume
+                for (uint32_t k = kbg > (uint32_t)S ? kbg - S : 0; k < kbg; ++k) mbar_wait(&full_bar[k % S], (k / S) & 1u);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            uint32_t kbg = 0, it = 0;
+            for (int t = blockIdx.x; t < ntiles && !timed_out; t += gridDim.x, ++it) {
+                const uint32_t as = it & 1u, aph = (it >> 1) & 1u;
+                if (!mbar_wait(&tmem_empty[as], aph ^ 1u)) { timed_out = true; break; }     // the epilogue has drained this accumulator
+                tc_fence_after();
+                const uint32_t acc = tmem_base + as * ACC_COLS;
+                for (int kb = 0; kb < num_kb; ++kb, ++kbg) {
+                    const int s = kbg % S;
+                    const uint32_t ph = (kbg / S) & 1u;
+                    if (!mbar_wait(&full_bar[s], ph)) { timed_out = true; break; }
+                    tc_fence_after();
+                    const uint32_t a_hi = smem_u32(base + s * T::STAGE);
+                    const uint32_t b_addr = a_hi + T::A_BYTES * (SPLIT ? 2 : 1);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_bf16(acc, make_smem_desc(a_hi + k * 32), make_smem_desc(b_addr + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    if (SPLIT) {
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k)
+                            umma_bf16(acc, make_smem_desc(a_hi + T::A_BYTES + k * 32), make_smem_desc(b_addr + k * 32), idesc, 1u);
+                    }
+                    umma_commit(&empty_bar[s]);
+                }
+                if (timed_out) break;
+                umma_commit(&tmem_full[as]);
+            }
+            if (timed_out) {                     // let every MMA issued so far finish before TMEM is freed
+                umma_commit(drain_bar);
+                mbar_wait(drain_bar, 0);         // bounded
+            }
+        }
+    } else {
+        const int q = warp & 3;                  // TMEM lane quarter this warp may read
+        const bool vec_ok = (ldd & 3) == 0;
+        uint32_t it = 0;
+        for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+            const uint32_t as = it & 1u, aph = (it >> 1) & 1u;
+            const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+            if (!mbar_wait(&tmem_full[as], aph)) timed_out = true;
+            timed_out = __any_sync(0xffffffffu, timed_out);     // tcgen05.ld below is warp-collective
+            if (timed_out) break;
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+            for (int cb = 0; cb < (BN + 31) / 32; ++cb) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + as * ACC_COLS + (uint32_t)(cb * 32), r);
+                const int col0 = n0 + cb * 32;
+                const int nlim = min(N, n0 + BN);            // columns of this tile that exist
+                if (row < M && col0 < nlim) {
+                    float* dp = D + (size_t)row * ldd + col0;
+                    if (vec_ok && col0 + 32 <= nlim) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                            if (accumulate) {
+                                float4 o = *reinterpret_cast<const float4*>(dp + 4 * j);
+                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                            }
+                            *reinterpret_cast<float4*>(dp + 4 * j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (col0 + j < nlim) {
+                                float v = __uint_as_float(r[j]);
+                                if (accumulate) v += dp[j];
+                                dp[j] = v;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[as]);          // this warp has read its quarter of the accumulator
+        }
+    }
+    if (timed_out && status != nullptr) atomicOr(status, STATUS_TIMEOUT);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2u * ACC_COLS) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -284,6 +444,33 @@ int32_t launch_t(const GemmArgs& a, cudaStream_t st) {
     return LUMI_OK;
 }
 
+int sm_count_gemm() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
+template <int BN, bool SPLIT>
+int32_t launch_persistent(const GemmArgs& a, cudaStream_t st) {
+    using T = Tile<BN, SPLIT, 1>;
+    CUtensorMap mh, ml, mw;
+    LUMI_TRY(make_map(&mh, a.a_hi, a.M, a.K, BM));
+    LUMI_TRY(make_map(&ml, SPLIT ? a.a_lo : a.a_hi, a.M, a.K, BM));
+    LUMI_TRY(make_map(&mw, a.w, a.N, a.K, BN));
+    auto kern = gemm_persistent_kernel<BN, SPLIT>;
+    LUMI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
+    const int tiles_m = (a.M + BM - 1) / BM, tiles_n = (a.N + BN - 1) / BN;
+    const int ntiles = tiles_m * tiles_n;
+    const int grid = ntiles < sm_count_gemm() ? ntiles : sm_count_gemm();
+    kern<<<grid, 192, T::SMEM, st>>>(mh, ml, mw, a.d, a.ldd, a.M, a.N, a.K, a.accumulate, tiles_m, ntiles, a.status_word);
+    LUMI_CUDA(cudaGetLastError());
+    return LUMI_OK;
+}
+
 }  // namespace
 
 int32_t gemm_tcgen05_init() {
@@ -310,8 +497,28 @@ int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st) {
     if (mode == 1) return split ? launch_t<128, true, 2>(a, st) : launch_t<128, false, 2>(a, st);
     if (mode == 2) return split ? launch_t<128, true, 1>(a, st) : launch_t<128, false, 1>(a, st);
     if (mode == 3) return split ? launch_t<256, true, 1>(a, st) : launch_t<256, false, 1>(a, st);
-    // wide tiles when the problem has enough of them to fill the GPU
+    // wide tiles when the problem has enough of them to fill the GPU; more than one tile per SM: persistent CTAs
     const long tiles256 = (long)((a.N + 255) / 256) * ((a.M + BM - 1) / BM);
+    static const int persist = getenv("LUMI_GEMM_PERSIST") ? atoi(getenv("LUMI_GEMM_PERSIST")) : 1;     // 0: tuning aid
+    if (persist) {
+        // Tile width: the GPU works in rounds of one tile per SM, a round costs about its tile's width, so take
+        // the width with the least rounds x width (7360 columns x 16 row tiles: 208 -> 4 rounds of 576 tiles,
+        // against 4 rounds of 464 tiles at 256).  Ties go to the wider tile (less operand traffic per flop).
+        static const int widths[] = {256, 224, 208, 192, 160, 128, 96, 64};
+        const long tiles_m = (a.M + BM - 1) / BM;
+        int best = 256;
+        long best_cost = -1;
+        for (int w : widths) {
+            const long tiles = tiles_m * ((a.N + w - 1) / w);
+            const long rounds = (tiles + sm_count_gemm() - 1) / sm_count_gemm();
+            const long cost = rounds * (w + 32);             // + 32: the part of a tile's time that does not shrink with its width
+            if (best_cost < 0 || cost < best_cost) { best = w; best_cost = cost; }
+        }
+#define LUMI_PERSIST_CASE(W) if (best == W) return split ? launch_persistent<W, true>(a, st) : launch_persistent<W, false>(a, st);
+        LUMI_PERSIST_CASE(256) LUMI_PERSIST_CASE(224) LUMI_PERSIST_CASE(208) LUMI_PERSIST_CASE(192) LUMI_PERSIST_CASE(160) LUMI_PERSIST_CASE(128)
+        LUMI_PERSIST_CASE(96) LUMI_PERSIST_CASE(64)
+#undef LUMI_PERSIST_CASE
+    }
     if (tiles256 >= 148) return split ? launch_t<256, true, 1>(a, st) : launch_t<256, false, 1>(a, st);
     return split ? launch_t<128, true, 1>(a, st) : launch_t<128, false, 1>(a, st);
 }
