@@ -175,6 +175,19 @@ int32_t lumi_session_read_state(lumi_session* s, int32_t slot, int32_t layer, fl
  * using and updating the session state — for per-layer parity tests. */
 int32_t lumi_debug_run_block(lumi_session* s, int32_t layer, float* x, int32_t batch);
 
+/* ---- sequence snapshots: park a sequence on the host and resume it later, in any slot of any session of
+ * the same model (slot reuse when a sequence ends, resuming a long generation).  The state is what
+ * inference/src/model.rs:112-159 keeps per sequence (SsmState, KvCache); the reference has no call that
+ * saves it.  A snapshot holds, for one slot: h, x_prev, B_prev and the cumulative angles of every Mamba
+ * layer, the K/V pages and the position of every attention layer.  The token that the next step consumes
+ * is NOT part of it (the caller feeds tokens to lumi_decode_step).
+ * lumi_session_state_bytes: size of one snapshot for this session's model and max_tokens_kv.
+ * save/load synchronise the session's stream; load checks the header written by save (LUMI_E_TENSOR on
+ * a snapshot of another model or cache size). */
+int32_t lumi_session_state_bytes(const lumi_session* s, int64_t* bytes);
+int32_t lumi_session_save_state(lumi_session* s, int32_t slot, void* host_buf, int64_t nbytes);
+int32_t lumi_session_load_state(lumi_session* s, int32_t slot, const void* host_buf, int64_t nbytes);
+
 /* ---- single kernels over caller-owned DEVICE pointers (tests, profiling) -------------------- */
 
 /* D[M][N] (fp32, row-major, leading dimension ldd) = A[M][K] * W[N][K]^T (+ D if accumulate != 0),

@@ -24,7 +24,7 @@ EXPORTS = [
     "lumi_last_error", "lumi_model_create", "lumi_model_load_tensor", "lumi_model_load_safetensors",
     "lumi_model_finalize", "lumi_model_free", "lumi_model_info", "lumi_session_create", "lumi_session_reset",
     "lumi_session_free", "lumi_session_set_option", "lumi_prefill", "lumi_decode_step", "lumi_generate",
-    "lumi_decode_loop_device", "lumi_profile_step", "lumi_session_read_state", "lumi_debug_run_block", "lumi_k_gemm_bf16_tcgen05",
+    "lumi_decode_loop_device", "lumi_profile_step", "lumi_session_read_state", "lumi_session_state_bytes", "lumi_session_save_state", "lumi_session_load_state", "lumi_debug_run_block", "lumi_k_gemm_bf16_tcgen05",
     "lumi_k_gemv", "lumi_k_ssm_step", "lumi_mamba_block_static",
 ]
 
@@ -73,6 +73,9 @@ def lib():
         L.lumi_decode_loop_device.argtypes = [vp, i32, i32, C.POINTER(C.c_float), C.POINTER(i64)]
         L.lumi_profile_step.argtypes = [vp, i32, C.POINTER(C.c_float), C.POINTER(i64)]
         L.lumi_session_read_state.argtypes = [vp, i32, i32, vp, vp, vp, vp]
+        L.lumi_session_state_bytes.argtypes = [vp, vp]
+        L.lumi_session_save_state.argtypes = [vp, i32, vp, C.c_int64]
+        L.lumi_session_load_state.argtypes = [vp, i32, vp, C.c_int64]
         L.lumi_debug_run_block.argtypes = [vp, i32, vp, i32]
         L.lumi_k_gemm_bf16_tcgen05.argtypes = [u64, u64, u64, u64, i32, i32, i32, i32, i32, u64]
         L.lumi_k_gemv.argtypes = [u64, u64, i32, u64, u64, u64, i32, i32, i32, u64]
@@ -244,6 +247,18 @@ class Session:
         cum = np.empty((c.n_heads, c.d_state // 2), dtype=np.float32)
         check(lib().lumi_session_read_state(self._h, slot, layer, _ptr(h), _ptr(xp), _ptr(bp), _ptr(cum)))
         return h, xp, bp, cum
+
+    def save_state(self, slot: int) -> np.ndarray:
+        """Snapshot of one sequence (SSM state, K/V pages, position) as bytes on the host."""
+        n = C.c_int64()
+        check(lib().lumi_session_state_bytes(self._h, C.byref(n)))
+        buf = np.empty(n.value, dtype=np.uint8)
+        check(lib().lumi_session_save_state(self._h, slot, _ptr(buf), n.value))
+        return buf
+
+    def load_state(self, slot: int, snapshot: np.ndarray) -> None:
+        snapshot = np.ascontiguousarray(snapshot, dtype=np.uint8)
+        check(lib().lumi_session_load_state(self._h, slot, _ptr(snapshot), snapshot.nbytes))
 
     def run_block(self, layer: int, x: np.ndarray) -> np.ndarray:
         x = np.array(np.atleast_2d(x), dtype=np.float32, copy=True)

@@ -1173,6 +1173,91 @@ extern "C" int32_t lumi_session_read_state(lumi_session* s, int32_t slot, int32_
     return LUMI_OK;
 }
 
+// ---- sequence snapshots ---------------------------------------------------------------------------
+namespace {
+struct SnapHeader {
+    uint32_t magic, version, n_mamba, n_attn;
+    uint64_t payload_bytes;
+    int32_t kv_pos;
+    uint32_t reserved;
+};
+constexpr uint32_t kSnapMagic = 0x4c4d5353u;     // "LMSS"
+
+struct SnapLayout {
+    size_t nh, nx, nb, nc;      // floats per sequence per Mamba layer: h, x_prev, B_prev, angles
+    size_t kv_seq_bytes;        // bytes per sequence per attention layer (its pages_per_seq pages)
+    size_t payload;
+};
+SnapLayout snap_layout(const lumi_session* s) {
+    const Config& c = s->m->cfg;
+    SnapLayout L{};
+    L.nh = state_h_per_seq(c); L.nx = c.d_inner(); L.nb = (size_t)c.n_heads * c.d_state; L.nc = (size_t)c.n_heads * (c.d_state / 2);
+    L.kv_seq_bytes = s->m->n_attn > 0 ? s->kv_layer_bytes / (size_t)s->max_batch : 0;
+    L.payload = (size_t)s->m->n_mamba * (L.nh + L.nx + L.nb + L.nc) * sizeof(float) + (size_t)s->m->n_attn * L.kv_seq_bytes;
+    return L;
+}
+}  // namespace
+
+extern "C" int32_t lumi_session_state_bytes(const lumi_session* s, int64_t* bytes) {
+    if (!s || !bytes) return fail(LUMI_E_INVALID, "null argument");
+    *bytes = (int64_t)(sizeof(SnapHeader) + snap_layout(s).payload);
+    return LUMI_OK;
+}
+
+static int32_t snap_copy(lumi_session* s, int32_t slot, char* buf, bool save) {
+    const SnapLayout L = snap_layout(s);
+    const size_t B = s->max_batch;
+    const cudaMemcpyKind kind = save ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice;
+    auto xfer = [&](void* dev, size_t bytes) -> cudaError_t {
+        cudaError_t e = save ? cudaMemcpyAsync(buf, dev, bytes, kind, s->stream) : cudaMemcpyAsync(dev, buf, bytes, kind, s->stream);
+        buf += bytes;
+        return e;
+    };
+    for (size_t l = 0; l < (size_t)s->m->n_mamba; ++l) {
+        LUMI_CUDA(xfer(s->h + (l * B + slot) * L.nh, L.nh * sizeof(float)));
+        LUMI_CUDA(xfer(s->xprev + (l * B + slot) * L.nx, L.nx * sizeof(float)));
+        LUMI_CUDA(xfer(s->bprev + (l * B + slot) * L.nb, L.nb * sizeof(float)));
+        LUMI_CUDA(xfer(s->cum + (l * B + slot) * L.nc, L.nc * sizeof(float)));
+    }
+    for (size_t a = 0; a < (size_t)s->m->n_attn; ++a)      // slot b owns pages [b * pages_per_seq, (b + 1) * pages_per_seq)
+        LUMI_CUDA(xfer((char*)s->kv_pool + a * s->kv_layer_bytes + (size_t)slot * L.kv_seq_bytes, L.kv_seq_bytes));
+    return LUMI_OK;
+}
+
+extern "C" int32_t lumi_session_save_state(lumi_session* s, int32_t slot, void* host_buf, int64_t nbytes) {
+    if (!s || !host_buf) return fail(LUMI_E_INVALID, "null argument");
+    if (slot < 0 || slot >= s->max_batch) return fail(LUMI_E_INVALID, "slot %d out of range", slot);
+    const SnapLayout L = snap_layout(s);
+    if (nbytes < (int64_t)(sizeof(SnapHeader) + L.payload))
+        return fail(LUMI_E_INVALID, "snapshot buffer of %lld bytes, %zu needed", (long long)nbytes, sizeof(SnapHeader) + L.payload);
+    LUMI_CUDA(cudaSetDevice(s->m->device));
+    SnapHeader hd{kSnapMagic, 1u, (uint32_t)s->m->n_mamba, (uint32_t)s->m->n_attn, (uint64_t)L.payload, 0, 0u};
+    LUMI_CUDA(cudaMemcpyAsync(&hd.kv_pos, s->kv_pos + slot, sizeof(int32_t), cudaMemcpyDeviceToHost, s->stream));
+    LUMI_TRY(snap_copy(s, slot, (char*)host_buf + sizeof(SnapHeader), true));
+    LUMI_CUDA(cudaStreamSynchronize(s->stream));
+    memcpy(host_buf, &hd, sizeof(hd));
+    return LUMI_OK;
+}
+
+extern "C" int32_t lumi_session_load_state(lumi_session* s, int32_t slot, const void* host_buf, int64_t nbytes) {
+    if (!s || !host_buf) return fail(LUMI_E_INVALID, "null argument");
+    if (slot < 0 || slot >= s->max_batch) return fail(LUMI_E_INVALID, "slot %d out of range", slot);
+    const SnapLayout L = snap_layout(s);
+    SnapHeader hd;
+    if (nbytes < (int64_t)sizeof(hd)) return fail(LUMI_E_INVALID, "snapshot shorter than its header");
+    memcpy(&hd, host_buf, sizeof(hd));
+    if (hd.magic != kSnapMagic || hd.version != 1u) return fail(LUMI_E_INVALID, "not a sequence snapshot");
+    if (hd.n_mamba != (uint32_t)s->m->n_mamba || hd.n_attn != (uint32_t)s->m->n_attn || hd.payload_bytes != (uint64_t)L.payload)
+        return fail(LUMI_E_TENSOR, "snapshot of another model or cache size (%u Mamba + %u attention layers, %llu bytes; this session: %d + %d, %zu)",
+                    hd.n_mamba, hd.n_attn, (unsigned long long)hd.payload_bytes, s->m->n_mamba, s->m->n_attn, L.payload);
+    if (nbytes < (int64_t)(sizeof(hd) + L.payload)) return fail(LUMI_E_INVALID, "snapshot truncated");
+    LUMI_CUDA(cudaSetDevice(s->m->device));
+    LUMI_CUDA(cudaMemcpyAsync(s->kv_pos + slot, &hd.kv_pos, sizeof(int32_t), cudaMemcpyHostToDevice, s->stream));
+    LUMI_TRY(snap_copy(s, slot, (char*)const_cast<void*>(host_buf) + sizeof(SnapHeader), false));
+    LUMI_CUDA(cudaStreamSynchronize(s->stream));
+    return LUMI_OK;
+}
+
 extern "C" int32_t lumi_debug_run_block(lumi_session* s, int32_t layer, float* x, int32_t batch) {
     LUMI_TRY(check_batch(s, batch));
     const Config& c = s->m->cfg;

@@ -301,3 +301,35 @@ def test_session_reset_restores_initial_state():
     sess.reset([0])
     b, _, _, _ = sess.generate(np.stack([z["prompt"]] * 2), 8, ignore_eos=True)
     assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("kind", ["tiny_mamba", "tiny_hybrid"])
+def test_sequence_snapshot_resumes_in_another_slot(kind):
+    """Park a sequence on the host after a few tokens and resume it in another slot of another session:
+    the continuation is the one the uninterrupted run (and the oracle) produces."""
+    cfg = synth.tiny_config(n_layers=4, attention_layers=[1, 3] if kind == "tiny_hybrid" else [])
+    tens = list(synth.iter_tensors(cfg, seed=8, perturb_ones=0.1))
+    prompt = synth.random_prompts(1, 7, cfg.vocab_size, seed=4)[0]
+    ref = cpu_oracle.OracleModel(cfg, tens).init_states().generate(prompt, 12, ignore_eos=True)
+    model = lumi_b200.NmModel.from_tensors(cfg, tens)
+    s1 = model.init_states(1, 32)
+    s1.prefill(prompt[None, :-1], want_logits=False)
+    cur, got = prompt[-1:], []
+    for i in range(5):
+        _, cur = s1.forward_step(cur, want_logits=False)
+        got.append(int(cur[0]))
+    snap = s1.save_state(0)
+    s2 = model.init_states(3, 32)
+    other = synth.random_prompts(3, 4, cfg.vocab_size, seed=9)
+    s2.prefill(other, want_logits=False)              # the other slots hold unrelated sequences
+    s2.load_state(2, snap)
+    toks = np.array([other[0, -1], other[1, -1], cur[0]], dtype=np.uint32)
+    for i in range(7):
+        _, toks = s2.forward_step(toks, want_logits=False)
+        got.append(int(toks[2]))
+    assert got == [int(t) for t in ref]
+    # a snapshot of another model is refused
+    cfg2 = synth.tiny_config(n_layers=2)
+    m2 = lumi_b200.NmModel.from_tensors(cfg2, list(synth.iter_tensors(cfg2, seed=1)))
+    with pytest.raises(lumi_b200.LumiError):
+        m2.init_states(1, 32).load_state(0, snap)
