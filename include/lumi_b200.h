@@ -175,6 +175,12 @@ int32_t lumi_session_read_state(lumi_session* s, int32_t slot, int32_t layer, fl
  * using and updating the session state — for per-layer parity tests. */
 int32_t lumi_debug_run_block(lumi_session* s, int32_t layer, float* x, int32_t batch);
 
+/* Teacher-forced scoring for the reference's `evaluate` command (inference/src/eval.rs:39-139: perplexity and
+ * continuation scores from log-softmax over forward_window's logits, model.rs:806-826):
+ * logprobs_out[b][t] = log p(tokens[b][t+1] | tokens[b][0..t]), t = 0 .. T-2 (row stride T-1), natural log.
+ * tokens[batch][T] row-major as for lumi_prefill; afterwards the state is that of a prefill of all T tokens. */
+int32_t lumi_score(lumi_session* s, const uint32_t* tokens, int32_t batch, int32_t T, float* logprobs_out);
+
 /* ---- sequence snapshots: park a sequence on the host and resume it later, in any slot of any session of
  * the same model (slot reuse when a sequence ends, resuming a long generation).  The state is what
  * inference/src/model.rs:112-159 keeps per sequence (SsmState, KvCache); the reference has no call that

@@ -24,7 +24,7 @@ EXPORTS = [
     "lumi_last_error", "lumi_model_create", "lumi_model_load_tensor", "lumi_model_load_safetensors",
     "lumi_model_finalize", "lumi_model_free", "lumi_model_info", "lumi_session_create", "lumi_session_reset",
     "lumi_session_free", "lumi_session_set_option", "lumi_prefill", "lumi_decode_step", "lumi_generate",
-    "lumi_decode_loop_device", "lumi_profile_step", "lumi_session_read_state", "lumi_session_state_bytes", "lumi_session_save_state", "lumi_session_load_state", "lumi_debug_run_block", "lumi_k_gemm_bf16_tcgen05",
+    "lumi_decode_loop_device", "lumi_profile_step", "lumi_score", "lumi_session_read_state", "lumi_session_state_bytes", "lumi_session_save_state", "lumi_session_load_state", "lumi_debug_run_block", "lumi_k_gemm_bf16_tcgen05",
     "lumi_k_gemv", "lumi_k_ssm_step", "lumi_mamba_block_static",
 ]
 
@@ -73,6 +73,7 @@ def lib():
         L.lumi_decode_loop_device.argtypes = [vp, i32, i32, C.POINTER(C.c_float), C.POINTER(i64)]
         L.lumi_profile_step.argtypes = [vp, i32, C.POINTER(C.c_float), C.POINTER(i64)]
         L.lumi_session_read_state.argtypes = [vp, i32, i32, vp, vp, vp, vp]
+        L.lumi_score.argtypes = [vp, vp, i32, i32, vp]
         L.lumi_session_state_bytes.argtypes = [vp, vp]
         L.lumi_session_save_state.argtypes = [vp, i32, vp, C.c_int64]
         L.lumi_session_load_state.argtypes = [vp, i32, vp, C.c_int64]
@@ -209,6 +210,14 @@ class Session:
         logits = np.empty((B, self.model.config.vocab_size), dtype=np.float32) if want_logits else None
         check(lib().lumi_prefill(self._h, _ptr(prompts), B, T, _ptr(logits)))
         return logits
+
+    def score(self, tokens) -> np.ndarray:
+        """log p(tokens[b][t+1] | tokens[b][:t+1]) for every position (inference/src/eval.rs:39-139); [batch, T-1]."""
+        tokens = np.ascontiguousarray(np.atleast_2d(tokens), dtype=np.uint32)
+        B, T = tokens.shape
+        out = np.empty((B, T - 1), dtype=np.float32)
+        check(lib().lumi_score(self._h, _ptr(tokens), B, T, _ptr(out)))
+        return out
 
     def generate(self, prompts, n_new: int, temperature: float = 0.0, top_k: int = 0, seed: int = 0, eos_id: int = 2,
                  ignore_eos: bool = False, dump_logits: bool = False):

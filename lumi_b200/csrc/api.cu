@@ -1007,6 +1007,38 @@ extern "C" int32_t lumi_prefill(lumi_session* s, const uint32_t* tokens, int32_t
     return check_status(s);
 }
 
+// Teacher-forced scoring: log p(tokens[b][t+1] | tokens[b][0..t]) for t = 0 .. T-2, the quantity the reference's
+// `evaluate` command sums into perplexities and continuation scores (inference/src/eval.rs:39-139, over
+// forward_window's logits, model.rs:806-826).  The session's state ends up as after a prefill of all T tokens.
+extern "C" int32_t lumi_score(lumi_session* s, const uint32_t* tokens, int32_t batch, int32_t T, float* logprobs_out) {
+    LUMI_TRY(check_batch(s, batch));
+    if (!tokens || !logprobs_out || T < 2) return fail(LUMI_E_INVALID, "score needs tokens, an output buffer and T >= 2");
+    LUMI_CUDA(cudaSetDevice(s->m->device));
+    LUMI_TRY(upload_prompt(s, tokens, batch, T));
+    LUMI_TRY(grow(s->gen_dump, s->gen_dump_cap, (size_t)batch * (T - 1)));
+    fill_ctl(s, batch, nullptr);
+    s->ctl_host->prompt = s->prompt_dev;
+    s->ctl_host->prompt_len = T;
+    s->ctl_host->ignore_eos = 1;
+    LUMI_TRY(push_ctl(s));
+    const bool mega = s->opt_mega;
+    s->opt_mega = 0;                                    // the persistent kernel has no per-position head
+    int32_t rc = LUMI_OK;
+    for (int t = 0; t < T && rc == LUMI_OK; ++t) {
+        rc = run_step(s, batch, t < T - 1);
+        if (rc == LUMI_OK && t < T - 1) {
+            cudaError_t e = launch_logprob(s->logits, batch, s->m->cfg.vocab, s->prompt_dev + (size_t)(t + 1) * batch, s->gen_dump, T - 1, t, s->stream);
+            if (e != cudaSuccess) rc = fail(LUMI_E_CUDA, "logprob kernel: %s", cudaGetErrorString(e));
+        }
+    }
+    s->opt_mega = mega;
+    LUMI_TRY(rc);
+    LUMI_CUDA(cudaMemcpyAsync(logprobs_out, s->gen_dump, sizeof(float) * (size_t)batch * (T - 1), cudaMemcpyDeviceToHost, s->stream));
+    LUMI_TRY(pull_ctl(s));
+    LUMI_CUDA(cudaStreamSynchronize(s->stream));
+    return check_status(s);
+}
+
 extern "C" int32_t lumi_decode_step(lumi_session* s, const uint32_t* in_tokens, int32_t batch, const lumi_sampling* sp,
                                     int32_t step, uint32_t* out_tokens, float* logits_out) {
     LUMI_TRY(check_batch(s, batch));

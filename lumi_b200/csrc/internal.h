@@ -200,6 +200,8 @@ struct GemvArgs {
     int32_t* status = nullptr;       // device word that receives STATUS_TIMEOUT if a bounded wait gives up; may be null
 };
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);
+cudaError_t launch_logprob(const float* logits, int B, int V, const uint32_t* targets, float* out, int out_stride, int out_col,
+                           cudaStream_t st);
 // Kernels of kernels.cu launched by the calling thread from now on carry (or not) the
 // programmatic-dependent-launch attribute.
 void set_launch_pdl(bool on);

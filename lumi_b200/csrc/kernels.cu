@@ -1310,6 +1310,44 @@ cudaError_t launch_sample(const float* logits, int B, int V, StepCtl* ctl, uint3
     return launch_k(sample_kernel, dim3(B), dim3(1024), 0, st, logits, V, ctl, tok_cur, finished, out_len);
 }
 
+// log-probability of a given next token from a row of logits (inference/src/eval.rs:39-139 scores with
+// log-softmax over the window's logits): m = max, s = sum exp(l - m), out = l[target] - m - log(s).
+// Per-thread partials in ascending index, xor tree, the 8 warps in order.
+__global__ void __launch_bounds__(256) logprob_kernel(const float* logits, int V, const uint32_t* targets, int batch, float* out,
+                                                      int out_stride, int out_col) {
+    __shared__ float red[8];
+    const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* l = logits + (size_t)b * V;
+    float m = -FLT_MAX;
+    for (int i = threadIdx.x; i < V; i += 256) m = fmaxf(m, l[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+    __syncthreads();
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < V; i += 256) sum += expf(l[i] - m);
+    sum = warp_sum(sum);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += red[w];
+        const uint32_t tg = targets[b];
+        out[(size_t)b * out_stride + out_col] = tg < (uint32_t)V ? (l[tg] - m) - logf(t) : -INFINITY;
+    }
+}
+
+cudaError_t launch_logprob(const float* logits, int B, int V, const uint32_t* targets, float* out, int out_stride, int out_col,
+                           cudaStream_t st) {
+    logprob_kernel<<<B, 256, 0, st>>>(logits, V, targets, B, out, out_stride, out_col);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_advance_step(StepCtl* ctl, int32_t* kv_pos, int B, int sampled, cudaStream_t st) {
     return launch_k(advance_step_kernel, dim3((B + 127) / 128), dim3(128), 0, st, ctl, kv_pos, B, sampled);
 }

@@ -39,6 +39,7 @@ extern "C" {
     pub fn lumi_session_state_bytes(s: *const LumiSession, bytes: *mut i64) -> i32;
     pub fn lumi_session_save_state(s: *mut LumiSession, slot: i32, host_buf: *mut c_void, nbytes: i64) -> i32;
     pub fn lumi_session_load_state(s: *mut LumiSession, slot: i32, host_buf: *const c_void, nbytes: i64) -> i32;
+    pub fn lumi_score(s: *mut LumiSession, tokens: *const u32, batch: i32, t: i32, logprobs_out: *mut f32) -> i32;
     pub fn lumi_prefill(s: *mut LumiSession, tokens: *const u32, batch: i32, t: i32, last_logits: *mut f32) -> i32;
     pub fn lumi_decode_step(s: *mut LumiSession, in_tokens: *const u32, batch: i32, sp: *const LumiSampling, step: i32,
                             out_tokens: *mut u32, logits_out: *mut f32) -> i32;

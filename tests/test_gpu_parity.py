@@ -333,3 +333,35 @@ def test_sequence_snapshot_resumes_in_another_slot(kind):
     m2 = lumi_b200.NmModel.from_tensors(cfg2, list(synth.iter_tensors(cfg2, seed=1)))
     with pytest.raises(lumi_b200.LumiError):
         m2.init_states(1, 32).load_state(0, snap)
+
+
+@pytest.mark.parametrize("case", ["tiny_hybrid_f32", "base_bf16_batch12"])
+def test_score_matches_oracle_log_softmax(case):
+    """Teacher-forced log-probabilities at every position (what `evaluate` sums, inference/src/eval.rs:39-139)
+    against log-softmax of the oracle's per-position logits; the state afterwards continues like a prefill."""
+    if case == "tiny_hybrid_f32":
+        cfg = synth.tiny_config(n_layers=4, attention_layers=[2])
+        tens = list(synth.iter_tensors(cfg, seed=6, perturb_ones=0.1))
+        B, T, tol = 3, 11, 2e-4
+    else:
+        cfg = synth.base_config(n_layers=2, vocab_size=777)
+        tens = list(synth.iter_tensors(cfg, seed=6, weights_dtype="bf16"))
+        B, T, tol = 12, 6, 2e-3
+    toks = synth.random_prompts(B, T, cfg.vocab_size, seed=12)
+    model = lumi_b200.NmModel.from_tensors(cfg, tens)
+    sess = model.init_states(B, 64)
+    got = sess.score(toks)
+    assert got.shape == (B, T - 1)
+    om = cpu_oracle.OracleModel(cfg, tens)
+    for b in (0, B - 1):
+        st = om.init_states()
+        for t in range(T - 1):
+            lg = st.forward_step(int(toks[b, t])).astype(np.float64)
+            ref = lg[toks[b, t + 1]] - (np.log(np.exp(lg - lg.max()).sum()) + lg.max())
+            assert abs(got[b, t] - ref) < tol * max(1.0, abs(ref)), (b, t, got[b, t], ref)
+    # the state is that of a prefill of all T tokens: the same next tokens as prefill + decode
+    _, nxt = sess.forward_step(toks[:, -1] * 0 + 5, want_logits=False)
+    s2 = model.init_states(B, 64)
+    s2.prefill(toks, want_logits=False)
+    _, nxt2 = s2.forward_step(toks[:, -1] * 0 + 5, want_logits=False)
+    assert np.array_equal(nxt, nxt2)
