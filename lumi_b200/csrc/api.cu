@@ -737,21 +737,31 @@ int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches,
 }
 
 // Runs one step, through a captured graph when enabled.
-int32_t run_step(lumi_session* s, int B, bool with_head) {
+// `reps` consecutive identical steps as one graph launch (reps > 1 only for small batches, where the gap
+// between two graph launches is a visible part of a step).
+int32_t run_step(lumi_session* s, int B, bool with_head, int reps = 1) {
     if (!s->opt_graph) {
-        int64_t n = 0;
-        LUMI_TRY(enqueue_step(s, B, with_head, &n));
-        s->launches += n;
+        for (int r = 0; r < reps; ++r) {
+            int64_t n = 0;
+            LUMI_TRY(enqueue_step(s, B, with_head, &n));
+            s->launches += n;
+        }
         return LUMI_OK;
     }
-    const int64_t key = (int64_t)B * 2 + (with_head ? 1 : 0);
+    const int64_t key = (((int64_t)B * 2 + (with_head ? 1 : 0)) << 8) | (int64_t)reps;
     auto it = s->graphs.find(key);
     if (it == s->graphs.end()) {
         GraphEntry ge;
         for (int attempt = 0; attempt < 2; ++attempt) {
             cudaGraph_t graph = nullptr;
             LUMI_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
-            int32_t st = enqueue_step(s, B, with_head, &ge.launches);
+            int32_t st = LUMI_OK;
+            ge.launches = 0;
+            for (int r = 0; r < reps && st == LUMI_OK; ++r) {
+                int64_t n = 0;
+                st = enqueue_step(s, B, with_head, &n);
+                ge.launches += n;
+            }
             cudaError_t e = cudaStreamEndCapture(s->stream, &graph);
             if (st == LUMI_OK && e == cudaSuccess) {
                 e = cudaGraphInstantiate(&ge.exec, graph, 0);
@@ -769,6 +779,15 @@ int32_t run_step(lumi_session* s, int B, bool with_head) {
     }
     LUMI_CUDA(cudaGraphLaunch(it->second.exec, s->stream));
     s->launches += it->second.launches;
+    return LUMI_OK;
+}
+
+// n identical steps: at small batch in graphs of kStepsPerGraph steps, the rest one by one
+constexpr int kStepsPerGraph = 8;
+int32_t run_steps(lumi_session* s, int B, bool with_head, int n) {
+    if (s->opt_graph && B <= 16)
+        for (; n >= kStepsPerGraph; n -= kStepsPerGraph) LUMI_TRY(run_step(s, B, with_head, kStepsPerGraph));
+    for (; n > 0; --n) LUMI_TRY(run_step(s, B, with_head));
     return LUMI_OK;
 }
 
@@ -999,7 +1018,10 @@ extern "C" int32_t lumi_prefill(lumi_session* s, const uint32_t* tokens, int32_t
     if (use_b1(s, batch)) LUMI_TRY(run_b1(s, T, last_logits != nullptr ? 1 : 0, 1));
     else if (chunked) LUMI_TRY(prefill_chunked(s, batch, T, last_logits != nullptr));
     else
-        for (int t = 0; t < T; ++t) LUMI_TRY(run_step(s, batch, last_logits != nullptr && t == T - 1));
+        {
+            LUMI_TRY(run_steps(s, batch, false, T - 1));
+            LUMI_TRY(run_step(s, batch, last_logits != nullptr));
+        }
     if (last_logits)
         LUMI_CUDA(cudaMemcpyAsync(last_logits, s->logits, sizeof(float) * batch * s->m->cfg.vocab, cudaMemcpyDeviceToHost, s->stream));
     LUMI_TRY(pull_ctl(s));
@@ -1100,7 +1122,8 @@ extern "C" int32_t lumi_generate(lumi_session* s, const uint32_t* prompts, int32
     } else if (chunked) {
         LUMI_TRY(prefill_chunked(s, batch, T, n_new > 0));
     } else {
-        for (int t = 0; t < T; ++t) LUMI_TRY(run_step(s, batch, n_new > 0 && t == T - 1));
+        LUMI_TRY(run_steps(s, batch, false, T - 1));
+        LUMI_TRY(run_step(s, batch, n_new > 0));
     }
     LUMI_CUDA(cudaEventRecord(s->ev1, s->stream));
     if (b1 && greedy) {
@@ -1108,7 +1131,7 @@ extern "C" int32_t lumi_generate(lumi_session* s, const uint32_t* prompts, int32
     } else if (b1) {
         for (int i = 1; i < n_new; ++i) { LUMI_TRY(run_b1(s, 1, 1, 0)); LUMI_TRY(sample_after_b1(s)); }
     } else {
-        for (int i = 1; i < n_new; ++i) LUMI_TRY(run_step(s, batch, true));      // main.rs:136-170
+        LUMI_TRY(run_steps(s, batch, true, n_new - 1));                          // main.rs:136-170
     }
     LUMI_CUDA(cudaEventRecord(s->ev2, s->stream));
     std::vector<uint32_t> tmp((size_t)n_new * batch);
@@ -1148,7 +1171,7 @@ extern "C" int32_t lumi_decode_loop_device(lumi_session* s, int32_t batch, int32
     LUMI_CUDA(cudaEventRecord(s->ev0, s->stream));
     if (use_b1(s, batch)) LUMI_TRY(run_b1(s, n_steps, 1, 1));
     else
-        for (int i = 0; i < n_steps; ++i) LUMI_TRY(run_step(s, batch, true));
+        LUMI_TRY(run_steps(s, batch, true, n_steps));
     LUMI_CUDA(cudaEventRecord(s->ev1, s->stream));
     LUMI_TRY(pull_ctl(s));
     LUMI_CUDA(cudaStreamSynchronize(s->stream));
