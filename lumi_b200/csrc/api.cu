@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <algorithm>
 
 using namespace lumi;
@@ -335,7 +336,7 @@ extern "C" void lumi_session_free(lumi_session* s) {
     cudaSetDevice(s->m->device);
     if (s->stream) cudaStreamSynchronize(s->stream);
     for (auto& g : s->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
-    void* dev[] = {s->h, s->xprev, s->bprev, s->cum, s->kv_pool, s->page_table, s->kv_pos, s->x, s->proj, s->y32, s->logits,
+    void* dev[] = {s->gemm_counters, s->gemm_scratch, s->h, s->xprev, s->bprev, s->cum, s->kv_pool, s->page_table, s->kv_pos, s->x, s->proj, s->y32, s->logits,
                    s->act_hi, s->act_lo, s->tok_cur, s->finished, s->out_len, s->ctl, s->gen_out, s->prompt_dev, s->gen_dump,
                    s->pf_x, s->pf_proj, s->pf_rb, s->pf_rc, s->pf_hi, s->pf_lo,
                    s->b1_layers, s->b1_grid_ctl, s->b1_amax_val, s->b1_amax_idx, s->b1_timing, s->b1_tagged};
@@ -395,6 +396,9 @@ static int32_t session_alloc(lumi_session* s) {
         LUMI_CUDA(cudaMemcpy(s->page_table, pt.data(), pt.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
     }
     LUMI_CUDA(cudaMalloc(&s->kv_pos, sizeof(int32_t) * B));
+    LUMI_CUDA(cudaMalloc(&s->gemm_counters, sizeof(int32_t) * 2 * kGemmCounters));
+    LUMI_CUDA(cudaMemset(s->gemm_counters, 0, sizeof(int32_t) * 2 * kGemmCounters));
+    LUMI_CUDA(cudaMalloc(&s->gemm_scratch, sizeof(float) * 2 * kGemmScratchFloats));
     const size_t kmax = std::max<size_t>({(size_t)c.d_model, (size_t)c.d_inner(), na > 0 ? (size_t)c.mlp_dim() : 0});
     const size_t pmax = std::max<size_t>({nm > 0 ? (size_t)c.in_proj_out() : 0, na > 0 ? (size_t)(c.d_model + 2 * c.kv_dim()) : 0,
                                           na > 0 ? (size_t)(2 * c.mlp_dim()) : 0});
@@ -570,7 +574,8 @@ int32_t linear(StepPlan& p, const DevTensor& W, const float* in32, int K, float*
     // region of act_hi / act_lo (rows packed with leading dimension K from the region's start)
     const size_t aoff = (size_t)p.row0 * s->act_ld;
     GemmArgs g{s->act_hi + aoff, s->opt_split ? s->act_lo + aoff : nullptr, (const __nv_bfloat16*)W.p, out, ldd, p.B, N, K,
-               residual != nullptr ? 1 : 0, &s->ctl->status};
+               residual != nullptr ? 1 : 0, &s->ctl->status, s->gemm_counters + (p.row0 > 0 ? kGemmCounters : 0), kGemmCounters,
+               s->gemm_scratch + (p.row0 > 0 ? kGemmScratchFloats : 0), kGemmScratchFloats};
     mark(p);
     LUMI_TRY(launch_gemm_tcgen05(g, p.st_hi));
     return LUMI_OK;
@@ -1340,7 +1345,24 @@ extern "C" int32_t lumi_debug_run_block(lumi_session* s, int32_t layer, float* x
 extern "C" int32_t lumi_k_gemm_bf16_tcgen05(uint64_t a_hi, uint64_t a_lo, uint64_t w, uint64_t d, int32_t M, int32_t N, int32_t K,
                                             int32_t ldd, int32_t accumulate, uint64_t stream) {
     if (!a_hi || !w || !d) return fail(LUMI_E_INVALID, "null device pointer");
-    GemmArgs g{(const __nv_bfloat16*)a_hi, (const __nv_bfloat16*)a_lo, (const __nv_bfloat16*)w, (float*)d, ldd, M, N, K, accumulate, nullptr};
+    // split-K needs zeroed counters: one small buffer per device for this test entry, made on first use
+    static std::mutex mu;
+    static int32_t* counters[64] = {nullptr};
+    static float* scratch[64] = {nullptr};
+    int dev = 0;
+    LUMI_CUDA(cudaGetDevice(&dev));
+    int32_t* cnt = nullptr;
+    if (dev >= 0 && dev < 64) {
+        std::lock_guard<std::mutex> lock(mu);
+        if (counters[dev] == nullptr) {
+            LUMI_CUDA(cudaMalloc(&counters[dev], sizeof(int32_t) * kGemmCounters));
+            LUMI_CUDA(cudaMemset(counters[dev], 0, sizeof(int32_t) * kGemmCounters));
+            LUMI_CUDA(cudaMalloc(&scratch[dev], sizeof(float) * kGemmScratchFloats));
+        }
+        cnt = counters[dev];
+    }
+    GemmArgs g{(const __nv_bfloat16*)a_hi, (const __nv_bfloat16*)a_lo, (const __nv_bfloat16*)w, (float*)d, ldd, M, N, K, accumulate, nullptr,
+               cnt, cnt ? kGemmCounters : 0, cnt ? scratch[dev] : nullptr, cnt ? kGemmScratchFloats : 0};
     return launch_gemm_tcgen05(g, (cudaStream_t)stream);
 }
 

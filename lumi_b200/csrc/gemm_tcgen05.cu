@@ -264,7 +264,7 @@ template <int BN, bool SPLIT>
 __global__ void __launch_bounds__(192, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
                        const __grid_constant__ CUtensorMap map_w, float* D, int ldd, int M, int N, int K,
-                       int accumulate, int tiles_m, int ntiles, int32_t* status) {
+                       int accumulate, int tiles_m, int ntiles, int splits, int32_t* tile_counters, float* scratch, int32_t* status) {
     using T = Tile<BN, SPLIT, 1>;
     constexpr int S = T::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -302,9 +302,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
     if (warp == 0) {
         if (lane == 0) {
             uint32_t kbg = 0;                    // k-blocks issued so far, over all tiles of this CTA
-            for (int t = blockIdx.x; t < ntiles && !timed_out; t += gridDim.x) {
+            for (int u = blockIdx.x; u < ntiles * splits && !timed_out; u += gridDim.x) {
+                const int t = u / splits, sp = u - t * splits;
                 const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
-                for (int kb = 0; kb < num_kb; ++kb, ++kbg) {
+                const int kb0 = sp * num_kb / splits, kb1 = (sp + 1) * num_kb / splits;
+                for (int kb = kb0; kb < kb1; ++kb, ++kbg) {
                     const int s = kbg % S;
                     const uint32_t ph = (kbg / S) & 1u;
                     if (!mbar_wait(&empty_bar[s], ph ^ 1u)) { timed_out = true; break; }
@@ -324,12 +326,14 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
         if (lane == 0) {
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             uint32_t kbg = 0, it = 0;
-            for (int t = blockIdx.x; t < ntiles && !timed_out; t += gridDim.x, ++it) {
+            for (int u = blockIdx.x; u < ntiles * splits && !timed_out; u += gridDim.x, ++it) {
                 const uint32_t as = it & 1u, aph = (it >> 1) & 1u;
                 if (!mbar_wait(&tmem_empty[as], aph ^ 1u)) { timed_out = true; break; }     // the epilogue has drained this accumulator
                 tc_fence_after();
                 const uint32_t acc = tmem_base + as * ACC_COLS;
-                for (int kb = 0; kb < num_kb; ++kb, ++kbg) {
+                const int sp = u % splits;
+                const int kb0 = sp * num_kb / splits, kb1 = (sp + 1) * num_kb / splits;
+                for (int kb = kb0; kb < kb1; ++kb, ++kbg) {
                     const int s = kbg % S;
                     const uint32_t ph = (kbg / S) & 1u;
                     if (!mbar_wait(&full_bar[s], ph)) { timed_out = true; break; }
@@ -338,7 +342,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
                     const uint32_t b_addr = a_hi + T::A_BYTES * (SPLIT ? 2 : 1);
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)
-                        umma_bf16(acc, make_smem_desc(a_hi + k * 32), make_smem_desc(b_addr + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16(acc, make_smem_desc(a_hi + k * 32), make_smem_desc(b_addr + k * 32), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     if (SPLIT) {
 #pragma unroll
                         for (int k = 0; k < BK / 16; ++k)
@@ -358,13 +362,69 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
         const int q = warp & 3;                  // TMEM lane quarter this warp may read
         const bool vec_ok = (ldd & 3) == 0;
         uint32_t it = 0;
-        for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+        for (int u = blockIdx.x; u < ntiles * splits; u += gridDim.x, ++it) {
             const uint32_t as = it & 1u, aph = (it >> 1) & 1u;
+            const int t = u / splits, sp = u - t * splits;
             const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
             if (!mbar_wait(&tmem_full[as], aph)) timed_out = true;
             timed_out = __any_sync(0xffffffffu, timed_out);     // tcgen05.ld below is warp-collective
             if (timed_out) break;
             tc_fence_after();
+            const int acc_in = accumulate;
+            if (splits > 1) {
+                // K split over several CTAs: every split parks its partial tile in scratch memory; the warp that
+                // arrives last at the counter of its row quarter adds the partials in split order (a fixed order,
+                // so the result does not depend on timing) and writes D.  Nobody waits for anybody.
+                const int row_l = q * 32 + lane;
+                float* part = scratch + ((size_t)(sp * ntiles + t) * BM + row_l) * BN;
+#pragma unroll 1
+                for (int cb = 0; cb < (BN + 31) / 32; ++cb) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + as * ACC_COLS + (uint32_t)(cb * 32), r);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (cb * 32 + 4 * j < BN)
+                            *reinterpret_cast<float4*>(part + cb * 32 + 4 * j) = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                                                           __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_empty[as]);
+                __threadfence();
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) {
+                    const int32_t old = atomicAdd(tile_counters + t * 4 + q, 1);
+                    last = old == splits - 1;
+                    if (last) atomicExch(tile_counters + t * 4 + q, 0);          // ready for the next launch
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+                    const int row = m0 + row_l;
+                    const int nlim = min(N, n0 + BN);
+                    if (row < M) {
+                        for (int c4 = 0; c4 < BN; c4 += 4) {
+                            const int col = n0 + c4;
+                            if (col >= nlim) break;
+                            float* dp = D + (size_t)row * ldd + col;
+                            float v[4] = {0.f, 0.f, 0.f, 0.f};
+                            const bool vec = (ldd & 3) == 0 && col + 4 <= nlim;
+                            if (acc_in) {
+                                if (vec) { const float4 o = __ldcg(reinterpret_cast<const float4*>(dp)); v[0] = o.x; v[1] = o.y; v[2] = o.z; v[3] = o.w; }
+                                else for (int e = 0; e < 4; ++e) if (col + e < nlim) v[e] = __ldcg(dp + e);
+                            }
+                            for (int s2 = 0; s2 < splits; ++s2) {
+                                const float4 pv = __ldcg(reinterpret_cast<const float4*>(scratch + ((size_t)(s2 * ntiles + t) * BM + row_l) * BN + c4));
+                                v[0] += pv.x; v[1] += pv.y; v[2] += pv.z; v[3] += pv.w;
+                            }
+                            if (vec) *reinterpret_cast<float4*>(dp) = make_float4(v[0], v[1], v[2], v[3]);
+                            else for (int e = 0; e < 4; ++e) if (col + e < nlim) dp[e] = v[e];
+                        }
+                    }
+                }
+                continue;
+            }
             const int row = m0 + q * 32 + lane;
 #pragma unroll 1
             for (int cb = 0; cb < (BN + 31) / 32; ++cb) {
@@ -379,8 +439,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
                         for (int j = 0; j < 8; ++j) {
                             float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
                                                    __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                            if (accumulate) {
-                                float4 o = *reinterpret_cast<const float4*>(dp + 4 * j);
+                            if (acc_in) {
+                                float4 o = __ldcg(reinterpret_cast<const float4*>(dp + 4 * j));
                                 v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
                             }
                             *reinterpret_cast<float4*>(dp + 4 * j) = v;
@@ -390,7 +450,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
                         for (int j = 0; j < 32; ++j) {
                             if (col0 + j < nlim) {
                                 float v = __uint_as_float(r[j]);
-                                if (accumulate) v += dp[j];
+                                if (acc_in) v += __ldcg(dp + j);
                                 dp[j] = v;
                             }
                         }
@@ -400,6 +460,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[as]);          // this warp has read its quarter of the accumulator
+
         }
     }
     if (timed_out && status != nullptr) atomicOr(status, STATUS_TIMEOUT);
@@ -455,7 +516,7 @@ int sm_count_gemm() {
 }
 
 template <int BN, bool SPLIT>
-int32_t launch_persistent(const GemmArgs& a, cudaStream_t st) {
+int32_t launch_persistent(const GemmArgs& a, int splits, cudaStream_t st) {
     using T = Tile<BN, SPLIT, 1>;
     CUtensorMap mh, ml, mw;
     LUMI_TRY(make_map(&mh, a.a_hi, a.M, a.K, BM));
@@ -465,8 +526,10 @@ int32_t launch_persistent(const GemmArgs& a, cudaStream_t st) {
     LUMI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM));
     const int tiles_m = (a.M + BM - 1) / BM, tiles_n = (a.N + BN - 1) / BN;
     const int ntiles = tiles_m * tiles_n;
-    const int grid = ntiles < sm_count_gemm() ? ntiles : sm_count_gemm();
-    kern<<<grid, 192, T::SMEM, st>>>(mh, ml, mw, a.d, a.ldd, a.M, a.N, a.K, a.accumulate, tiles_m, ntiles, a.status_word);
+    const int units = ntiles * splits;
+    const int grid = units < sm_count_gemm() ? units : sm_count_gemm();
+    kern<<<grid, 192, T::SMEM, st>>>(mh, ml, mw, a.d, a.ldd, a.M, a.N, a.K, a.accumulate, tiles_m, ntiles, splits, a.tile_counters,
+                                     a.scratch, a.status_word);
     LUMI_CUDA(cudaGetLastError());
     return LUMI_OK;
 }
@@ -504,17 +567,27 @@ int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st) {
         // Tile width: the GPU works in rounds of one tile per SM, a round costs about its tile's width, so take
         // the width with the least rounds x width (7360 columns x 16 row tiles: 208 -> 4 rounds of 576 tiles,
         // against 4 rounds of 464 tiles at 256).  Ties go to the wider tile (less operand traffic per flop).
+        // K can be split over CTAs as well (LUMI_GEMM_SPLITK=2, 4 or 8; at least four k-blocks per split) when the
+        // tiles do not fill the SMs.  Off by default: measured slower at 64-512 rows, because the fix-up (the last
+        // warp to arrive adds the parked partial tiles in split order) is a chain of L2 round trips in few warps.
         static const int widths[] = {256, 224, 208, 192, 160, 128, 96, 64};
+        static const int max_splits = getenv("LUMI_GEMM_SPLITK") ? atoi(getenv("LUMI_GEMM_SPLITK")) : 1;
         const long tiles_m = (a.M + BM - 1) / BM;
-        int best = 256;
+        const int num_kb = a.K / BK;
+        int best = 256, best_splits = 1;
         long best_cost = -1;
         for (int w : widths) {
             const long tiles = tiles_m * ((a.N + w - 1) / w);
-            const long rounds = (tiles + sm_count_gemm() - 1) / sm_count_gemm();
-            const long cost = rounds * (w + 32);             // + 32: the part of a tile's time that does not shrink with its width
-            if (best_cost < 0 || cost < best_cost) { best = w; best_cost = cost; }
+            for (int sp = 1; sp <= max_splits; sp *= 2) {
+                if (sp > 1 && (a.tile_counters == nullptr || a.scratch == nullptr || 4 * tiles > a.n_counters ||
+                               (size_t)sp * tiles * BM * w > a.scratch_floats || num_kb / sp < 4))
+                    break;
+                const long rounds = (tiles * sp + sm_count_gemm() - 1) / sm_count_gemm();
+                const long cost = rounds * (w / sp + 32 + (sp > 1 ? 12 : 0));    // + 32: the part of a tile's time that does not shrink
+                if (best_cost < 0 || cost < best_cost) { best = w; best_splits = sp; best_cost = cost; }
+            }
         }
-#define LUMI_PERSIST_CASE(W) if (best == W) return split ? launch_persistent<W, true>(a, st) : launch_persistent<W, false>(a, st);
+#define LUMI_PERSIST_CASE(W) if (best == W) return split ? launch_persistent<W, true>(a, best_splits, st) : launch_persistent<W, false>(a, best_splits, st);
         LUMI_PERSIST_CASE(256) LUMI_PERSIST_CASE(224) LUMI_PERSIST_CASE(208) LUMI_PERSIST_CASE(192) LUMI_PERSIST_CASE(160) LUMI_PERSIST_CASE(128)
         LUMI_PERSIST_CASE(96) LUMI_PERSIST_CASE(64)
 #undef LUMI_PERSIST_CASE

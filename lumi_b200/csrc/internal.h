@@ -170,6 +170,8 @@ struct lumi_session {
     __nv_bfloat16 *act_hi = nullptr, *act_lo = nullptr;
     uint32_t *tok_cur = nullptr;       // [max_batch] tokens the next step consumes
     int32_t *finished = nullptr, *out_len = nullptr;   // [max_batch]
+    int32_t* gemm_counters = nullptr;  // [2][kGemmCounters] zeroed ints for the split-K GEMM (second half: second lane)
+    float* gemm_scratch = nullptr;     // [2][kGemmScratchFloats] partial tiles of the split-K GEMM
     lumi::StepCtl* ctl = nullptr;      // device
     lumi::StepCtl* ctl_host = nullptr; // pinned mirror
     uint32_t* pin_tokens = nullptr;    // pinned staging [max_batch]
@@ -185,6 +187,8 @@ struct lumi_session {
 namespace lumi {
 
 constexpr int kPageTokens = 64;
+constexpr int kGemmCounters = 4096;
+constexpr size_t kGemmScratchFloats = (size_t)4 << 20;      // 16 MiB per lane
 
 // ---- kernel launchers (kernels.cu) --------------------------------------------------------------
 // All take the stream to enqueue on and return a cudaError_t from the launch.
@@ -258,6 +262,10 @@ struct GemmArgs {
     int M, N, K;
     int accumulate;
     int32_t* status_word;               // may be null
+    int32_t* tile_counters = nullptr;   // zeroed device ints for split-K (the kernel leaves them zero); null: no split-K
+    int n_counters = 0;
+    float* scratch = nullptr;           // partial tiles of the splits
+    size_t scratch_floats = 0;
 };
 int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st);   // returns LUMI_* status
 int32_t gemm_tcgen05_init();                                        // resolves the driver entry point

@@ -50,7 +50,8 @@ def test_gemv_matches_fp64(wdt, M, N, K):
 
 @pytest.mark.parametrize("split", [True, False])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (64, 7360, 1024), (200, 259, 1024), (300, 1024, 2048), (2048, 512, 128),
-                                   (2048, 7360, 1024), (1000, 5000, 512), (2300, 4100, 64)])   # the last three: more tiles than SMs
+                                   (2048, 7360, 1024), (1000, 5000, 512), (2300, 4100, 64),    # more tiles than SMs: persistent CTAs
+                                   (64, 1024, 2048), (512, 1024, 2048), (100, 1024, 2816), (300, 512, 4096)])   # few tiles: K split over CTAs
 def test_tcgen05_gemm_matches_torch(split, M, N, K):
     torch = _torch()
     g = torch.Generator(device="cpu").manual_seed(M + N + K)
@@ -81,3 +82,28 @@ def test_tcgen05_gemm_rejects_bad_k():
     d = torch.zeros((8, 8), dtype=torch.float32, device="cuda")
     st = lumi_b200.lib().lumi_k_gemm_bf16_tcgen05(a.data_ptr(), 0, w.data_ptr(), d.data_ptr(), 8, 8, 100, 8, 0, 0)
     assert st == -10
+
+
+def test_tcgen05_gemm_k_split_variant_in_child_process():
+    """LUMI_GEMM_SPLITK is latched at first use: run the few-tile shapes with K split 8 ways in a child process."""
+    import os, subprocess, sys
+    code = (
+        "import torch, lumi_b200\n"
+        "L = lumi_b200.lib()\n"
+        "for (M, N, K) in [(64, 1024, 2048), (512, 1024, 2048), (100, 1024, 2816)]:\n"
+        "    g = torch.Generator().manual_seed(M + N + K)\n"
+        "    a = torch.randn((M, K), generator=g); w = (torch.randn((N, K), generator=g) * 0.05).to(torch.bfloat16)\n"
+        "    hi = a.to(torch.bfloat16); lo = (a - hi.float()).to(torch.bfloat16); prev = torch.randn((M, N), generator=g)\n"
+        "    ref = (hi.double() + lo.double()) @ w.double().T + prev.double()\n"
+        "    outs = []\n"
+        "    for rep in range(2):\n"
+        "        d = prev.clone().cuda(); hid, lod, wd = hi.cuda(), lo.cuda(), w.cuda(); torch.cuda.synchronize()\n"
+        "        assert L.lumi_k_gemm_bf16_tcgen05(hid.data_ptr(), lod.data_ptr(), wd.data_ptr(), d.data_ptr(), M, N, K, N, 1, 0) == 0\n"
+        "        torch.cuda.synchronize(); outs.append(d.cpu())\n"
+        "    err = (outs[0].double() - ref).abs().max().item() / ref.abs().max().item()\n"
+        "    assert err < 2e-5, (M, N, K, err)\n"
+        "    assert torch.equal(outs[0], outs[1])\n"
+        "print('ok')\n")
+    env = dict(os.environ, LUMI_GEMM_SPLITK="8", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-2000:]
