@@ -95,27 +95,71 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     }
     __syncthreads();
 
-    // scores: one cached token per thread
+    // scores: a cached K row is HD * sizeof(KT) bytes = LPR lanes x 16 bytes, so one warp-wide 16-byte load
+    // covers RPI rows; UNR such loads are in flight per lane.  Lane (rg, sub) multiplies its EPL elements of
+    // row rg with the same elements of the HPK query heads (kept in registers) and the LPR partial sums of a
+    // row are added by a xor tree.
+    constexpr int EPL = 16 / (int)sizeof(KT);          // elements per lane per row
+    constexpr int LPR = HD / EPL;                      // lanes per row
+    constexpr int RPI = 32 / LPR;                      // rows per warp-wide load
+    constexpr int UNR = 4;
+    static_assert(LPR >= 1 && LPR <= 32 && (32 % LPR) == 0, "a row must be 16 to 512 bytes");
+    const int rg = lane / LPR, sub = lane % LPR;
+    __shared__ int32_t pages[64];
+    const bool pages_ok = a.pages_per_seq <= 64;
+    if (pages_ok) for (int i = tid; i < a.pages_per_seq; i += 128) pages[i] = pt[i];
+    __syncthreads();
+    auto row_ptr = [&](int t, int sel) -> const KT* {
+        const int page = pages_ok ? pages[t / kPageTokens] : pt[t / kPageTokens];
+        return pool + (((size_t)page * 2 + sel) * kPageTokens + (t % kPageTokens)) * KV + kvh * HD + sub * EPL;
+    };
+    auto unpack = [](const uint4& raw, float (&f)[EPL]) {
+        if constexpr (sizeof(KT) == 4) {
+            f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+        } else {
+            const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(u[i] << 16); f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
+        }
+    };
+    float qr[HPK][EPL];
+#pragma unroll
+    for (int hq = 0; hq < HPK; ++hq)
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) qr[hq][e] = qs[(sub * EPL + e) * HPK + hq];
     const float scale = (float)(1.0 / sqrt((double)HD));            // model.rs:530
     float lmax[HPK];
 #pragma unroll
     for (int hq = 0; hq < HPK; ++hq) lmax[hq] = -INFINITY;
-    for (int t = tid; t < T; t += 128) {
-        const KT* kr = kv_ptr(pool, pt, t, 0, KV) + kvh * HD;
-        float acc[HPK];
+    for (int t0 = warp * RPI; t0 < T; t0 += 4 * RPI * UNR) {
+        uint4 raw[UNR];
 #pragma unroll
-        for (int hq = 0; hq < HPK; ++hq) acc[hq] = 0.f;
-#pragma unroll 8
-        for (int d = 0; d < HD; ++d) {
-            const float kv = KvIo<KT>::ld(kr + d);
-#pragma unroll
-            for (int hq = 0; hq < HPK; ++hq) acc[hq] = fmaf(qs[d * HPK + hq], kv, acc[hq]);
+        for (int u = 0; u < UNR; ++u) {
+            const int t = t0 + u * 4 * RPI + rg;
+            raw[u] = t < T ? *reinterpret_cast<const uint4*>(row_ptr(t, 0)) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
-        for (int hq = 0; hq < HPK; ++hq) {
-            float s = __fmul_rn(acc[hq], scale);                    // model.rs:532
-            sc[hq * T + t] = s;
-            lmax[hq] = fmaxf(lmax[hq], s);
+        for (int u = 0; u < UNR; ++u) {
+            const int t = t0 + u * 4 * RPI + rg;
+            float kf[EPL];
+            unpack(raw[u], kf);
+            float acc[HPK];
+#pragma unroll
+            for (int hq = 0; hq < HPK; ++hq) {
+                acc[hq] = 0.f;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) acc[hq] = fmaf(qr[hq][e], kf[e], acc[hq]);
+#pragma unroll
+                for (int o = LPR / 2; o > 0; o >>= 1) acc[hq] += __shfl_xor_sync(0xffffffffu, acc[hq], o);
+            }
+            if (sub == 0 && t < T) {
+#pragma unroll
+                for (int hq = 0; hq < HPK; ++hq) {
+                    const float sv = __fmul_rn(acc[hq], scale);     // model.rs:532
+                    sc[hq * T + t] = sv;
+                    lmax[hq] = fmaxf(lmax[hq], sv);
+                }
+            }
         }
     }
     // block max per head
@@ -150,31 +194,48 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     if (tid < HPK) hsum[tid] = (red[tid] + red[HPK + tid]) + (red[2 * HPK + tid] + red[3 * HPK + tid]);
     __syncthreads();
 
-    // context: warp w takes tokens t = w (mod 4); lane owns dims lane, lane + 32, ...
-    constexpr int DPL = (HD + 31) / 32;
-    float ctx[HPK][DPL];
+    // context: same lane mapping over the V rows; a lane accumulates its EPL dims over the rows of its row
+    // group, then the RPI row groups are added by a xor tree and the four warps through shared memory
+    float ctx[HPK][EPL];
 #pragma unroll
     for (int hq = 0; hq < HPK; ++hq)
 #pragma unroll
-        for (int j = 0; j < DPL; ++j) ctx[hq][j] = 0.f;
-    for (int t = warp; t < T; t += 4) {
-        const KT* vr = kv_ptr(pool, pt, t, 1, KV) + kvh * HD;
-        float vv[DPL];
+        for (int e = 0; e < EPL; ++e) ctx[hq][e] = 0.f;
+    for (int t0 = warp * RPI; t0 < T; t0 += 4 * RPI * UNR) {
+        uint4 raw[UNR];
 #pragma unroll
-        for (int j = 0; j < DPL; ++j) vv[j] = (lane + 32 * j < HD) ? KvIo<KT>::ld(vr + lane + 32 * j) : 0.f;
+        for (int u = 0; u < UNR; ++u) {
+            const int t = t0 + u * 4 * RPI + rg;
+            raw[u] = t < T ? *reinterpret_cast<const uint4*>(row_ptr(t, 1)) : make_uint4(0u, 0u, 0u, 0u);
+        }
 #pragma unroll
-        for (int hq = 0; hq < HPK; ++hq) {
-            const float p = __fdiv_rn(sc[hq * T + t], hsum[hq]);
+        for (int u = 0; u < UNR; ++u) {
+            const int t = t0 + u * 4 * RPI + rg;
+            if (t < T) {
+                float vf[EPL];
+                unpack(raw[u], vf);
 #pragma unroll
-            for (int j = 0; j < DPL; ++j) ctx[hq][j] = fmaf(p, vv[j], ctx[hq][j]);
+                for (int hq = 0; hq < HPK; ++hq) {
+                    const float p = __fdiv_rn(sc[hq * T + t], hsum[hq]);
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) ctx[hq][e] = fmaf(p, vf[e], ctx[hq][e]);
+                }
+            }
         }
     }
-    __syncthreads();
 #pragma unroll
     for (int hq = 0; hq < HPK; ++hq)
 #pragma unroll
-        for (int j = 0; j < DPL; ++j)
-            if (lane + 32 * j < HD) red[warp * HPK * HD + hq * HD + lane + 32 * j] = ctx[hq][j];
+        for (int e = 0; e < EPL; ++e)
+#pragma unroll
+            for (int o = LPR; o < 32; o <<= 1) ctx[hq][e] += __shfl_xor_sync(0xffffffffu, ctx[hq][e], o);
+    __syncthreads();
+    if (rg == 0) {
+#pragma unroll
+        for (int hq = 0; hq < HPK; ++hq)
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) red[warp * HPK * HD + hq * HD + sub * EPL + e] = ctx[hq][e];
+    }
     __syncthreads();
     for (int i = tid; i < HPK * HD; i += 128) {
         float v = (red[i] + red[HPK * HD + i]) + (red[2 * HPK * HD + i] + red[3 * HPK * HD + i]);
