@@ -958,7 +958,32 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* logits, int V
         int k = ctl->top_k;
         if (k > kMaxTopK) k = kMaxTopK;
         if (k > 0 && k < V) {
-            // k rounds of block-wide argmax over the not-yet-taken entries
+            // k rounds of block-wide argmax over the not-yet-taken entries.  When the row fits (up to 32 entries
+            // per thread) each thread keeps its entries in registers with a taken-mask and a cached local best,
+            // so a round costs one block reduction and a rescan by the single thread that owned the winner.
+            constexpr int kRegVals = 32;
+            if (V <= nt * kRegVals) {
+                float vals[kRegVals];
+#pragma unroll
+                for (int j = 0; j < kRegVals; ++j) { const int i = tid + j * nt; vals[j] = i < V ? lg[i] : -INFINITY; }
+                uint32_t taken = 0u;
+                float lbv; int lbi;
+                auto rescan = [&]() {
+                    lbv = -INFINITY; lbi = 0x7fffffff;
+#pragma unroll
+                    for (int j = 0; j < kRegVals; ++j) {
+                        const int i = tid + j * nt;
+                        if (i < V && !((taken >> j) & 1u) && better(vals[j], i, lbv, lbi)) { lbv = vals[j]; lbi = i; }
+                    }
+                };
+                rescan();
+                for (int round = 0; round < k; ++round) {
+                    BestPair rr = block_argmax(lbv, lbi, red);
+                    if (tid == 0) { top_v[round] = rr.v; top_i[round] = rr.i; }
+                    if (rr.i < V && rr.i % nt == tid) { taken |= 1u << (rr.i / nt); rescan(); }
+                }
+                __syncthreads();
+            } else
             for (int round = 0; round < k; ++round) {
                 float bv = -INFINITY; int bi = 0x7fffffff;
                 for (int i = tid; i < V; i += nt) {
