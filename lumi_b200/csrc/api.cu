@@ -670,6 +670,14 @@ int32_t attention_block(StepPlan& p, const Layer& L) {
 }
 
 // embedding -> blocks -> (final norm -> logits -> sample) -> advance
+// Largest batch of the tensor-core path whose CUDA-core kernels are launched with programmatic dependent launch
+// (LUMI_PDL_TC; 0 = never): the state step then becomes resident under the in_proj GEMM and requests its tiles early.
+static int pdl_tc_max() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("LUMI_PDL_TC"); v = e ? atoi(e) : 128; }     // measured: +6 % at 64 rows, -3..5 % at 512-2048
+    return v;
+}
+
 int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches,
                      std::vector<std::pair<int, cudaEvent_t>>* prof = nullptr) {
     const Config& c = s->m->cfg;
@@ -677,7 +685,7 @@ int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches,
     p.prof = prof;
     // dependent launch overlaps each kernel's prologue (weight prefetch) with its predecessor; it is
     // used on the weight-streaming path, where launch gaps are the same order as the kernels
-    struct PdlScope { PdlScope(bool on) { set_launch_pdl(on); } ~PdlScope() { set_launch_pdl(false); } } pdl_scope(s->opt_pdl && !p.tc && prof == nullptr);
+    struct PdlScope { PdlScope(bool on) { set_launch_pdl(on); } ~PdlScope() { set_launch_pdl(false); } } pdl_scope(s->opt_pdl && prof == nullptr && (!p.tc || (pdl_tc_max() > 0 && B <= pdl_tc_max())));
     p.st_hi = p.st_lo = s->stream;
     mark(p);
     LUMI_CUDA(launch_embed(s->m->embedding.p, s->m->embedding.dtype, s->tok_cur, s->x, B, c.d_model, c.vocab, s->ctl, s->stream));

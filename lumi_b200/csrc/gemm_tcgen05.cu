@@ -279,6 +279,9 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = K / BK;
 
+    // A successor launched with programmatic dependent launch may become resident now and run the part of its
+    // prologue that does not depend on this kernel (the state step requests its state tiles there).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (status != nullptr && (*reinterpret_cast<volatile int32_t*>(status) & STATUS_TIMEOUT)) return;
 
     if (threadIdx.x == 0) {
