@@ -876,8 +876,16 @@ int32_t sample_after_b1(lumi_session* s) {
 }
 
 bool use_chunked_prefill(const lumi_session* s, int batch, int T) {
-    return s->opt_chunked_prefill > 0 && T >= s->opt_chunked_prefill && s->m->n_attn == 0 && s->m->wdtype == LUMI_DTYPE_BF16 &&
-           s->opt_gemm != 1 && prefill_ssd_supported(s->m->cfg) && (s->m->cfg.d_model % 64) == 0 && (s->m->cfg.d_inner() % 64) == 0;
+    if (!(s->opt_chunked_prefill > 0 && T >= s->opt_chunked_prefill && s->m->wdtype == LUMI_DTYPE_BF16 && s->opt_gemm != 1 &&
+          prefill_ssd_supported(s->m->cfg) && (s->m->cfg.d_model % 64) == 0 && (s->m->cfg.d_inner() % 64) == 0))
+        return false;
+    if (s->m->n_attn > 0) {
+        // attention layers: every row of a slice is appended before any row attends, which a sliding-window ring
+        // cannot take (later rows of the slice would overwrite slots that earlier rows still need)
+        if ((s->m->cfg.mlp_dim() % 64) != 0) return false;
+        for (const Layer& L : s->m->layers) if (L.is_attn && L.window > 0) return false;
+    }
+    return true;
 }
 
 // Prompt of T tokens for sequences 0..batch-1 through the chunked SSD scan; tokens come from
@@ -886,6 +894,10 @@ bool use_chunked_prefill(const lumi_session* s, int batch, int T) {
 int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head) {
     const Config& c = s->m->cfg;
     const int D = c.d_model, DI = c.d_inner(), R = c.in_proj_out();
+    const bool hybrid = s->m->n_attn > 0;
+    const int KVD = hybrid ? c.kv_dim() : 0, Q = D + 2 * KVD, MLP = hybrid ? c.mlp_dim() : 0;
+    const size_t wproj = std::max<size_t>({(size_t)R, (size_t)Q, (size_t)2 * MLP});       // widest fp32 row of a projection
+    const size_t wact = std::max<size_t>({(size_t)DI, (size_t)D, (size_t)MLP});           // widest bf16 operand row
     const int nb_max = std::min(batch, 2048);
     int TS = std::max(64, (std::max(64, s->opt_prefill_rows) / nb_max) / 64 * 64);
     if (TS > T) TS = T;
@@ -896,11 +908,11 @@ int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head) {
         s->pf_x = s->pf_proj = s->pf_rb = s->pf_rc = nullptr; s->pf_hi = s->pf_lo = nullptr; s->pf_rows = 0;
         const size_t rp = (rows_max + 127) / 128 * 128;
         LUMI_CUDA(cudaMalloc(&s->pf_x, sizeof(float) * rp * D));
-        LUMI_CUDA(cudaMalloc(&s->pf_proj, sizeof(float) * rp * R));
+        LUMI_CUDA(cudaMalloc(&s->pf_proj, sizeof(float) * rp * wproj));
         LUMI_CUDA(cudaMalloc(&s->pf_rb, sizeof(float) * rp));
         LUMI_CUDA(cudaMalloc(&s->pf_rc, sizeof(float) * rp));
-        LUMI_CUDA(cudaMalloc(&s->pf_hi, sizeof(__nv_bfloat16) * rp * DI));
-        LUMI_CUDA(cudaMalloc(&s->pf_lo, sizeof(__nv_bfloat16) * rp * DI));
+        LUMI_CUDA(cudaMalloc(&s->pf_hi, sizeof(__nv_bfloat16) * rp * wact));
+        LUMI_CUDA(cudaMalloc(&s->pf_lo, sizeof(__nv_bfloat16) * rp * wact));
         s->pf_rows = rows_max;
     }
     const size_t B = s->max_batch;
@@ -915,6 +927,42 @@ int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head) {
             s->launches += 1;
             for (const Layer& L : s->m->layers) {
                 const size_t l = L.kind_idx;
+                if (L.is_attn) {
+                    // AttentionBlock over all rows of the slice (model.rs:562-611 in forward_window's terms): q|k|v for every
+                    // row, the slice's K/V appended to the cache, then every row attends to the cache up to its own position
+                    LUMI_CUDA(launch_norm_split(s->pf_x, L.a.attn_norm_g, s->pf_hi, lo, M, D, c.eps, s->stream));
+                    GemmArgs gq{s->pf_hi, lo, (const __nv_bfloat16*)L.a.qkv.p, s->pf_proj, Q, M, Q, D, 0, &s->ctl->status};
+                    LUMI_TRY(launch_gemm_tcgen05(gq, s->stream));
+                    AttnArgs a{};
+                    a.qkv = s->pf_proj; a.ldq = Q;
+                    a.pool = (char*)s->kv_pool + l * s->kv_layer_bytes;
+                    a.kv_is_f32 = 0;
+                    a.page_table = s->page_table; a.pages_per_seq = s->pages_per_seq;
+                    a.pos = s->kv_pos;
+                    a.ctx32 = nullptr; a.chi = s->pf_hi; a.clo = lo;
+                    a.B = M; a.n_heads = c.attn_n_heads; a.kv_heads = c.attn_kv_heads; a.head_dim = c.attn_head_dim();
+                    a.window = 0; a.max_tokens = std::min(s->pages_per_seq * kPageTokens, s->max_tokens_kv);
+                    a.rope_base = c.attn_rope_base;
+                    a.ctl = s->ctl;
+                    a.rows_per_seq = ts; a.b0 = b0;
+                    for (int phase = 1; phase <= 2; ++phase) {
+                        a.phase = phase;
+                        cudaError_t e = launch_attention_decode(a, s->stream);
+                        if (e == cudaErrorInvalidValue) return fail(LUMI_E_UNSUPPORTED, "attention head_dim %d with %d query heads per kv head is not built", a.head_dim, a.n_heads / a.kv_heads);
+                        LUMI_CUDA(e);
+                    }
+                    GemmArgs go{s->pf_hi, lo, (const __nv_bfloat16*)L.a.o.p, s->pf_x, D, M, D, D, 1, &s->ctl->status};
+                    LUMI_TRY(launch_gemm_tcgen05(go, s->stream));
+                    // sigmoid-gated MLP (model.rs:546-555)
+                    LUMI_CUDA(launch_norm_split(s->pf_x, L.a.mlp_norm_g, s->pf_hi, lo, M, D, c.eps, s->stream));
+                    GemmArgs gu{s->pf_hi, lo, (const __nv_bfloat16*)L.a.gate_up.p, s->pf_proj, 2 * MLP, M, 2 * MLP, D, 0, &s->ctl->status};
+                    LUMI_TRY(launch_gemm_tcgen05(gu, s->stream));
+                    LUMI_CUDA(launch_gate_mul(s->pf_proj, 2 * MLP, nullptr, s->pf_hi, lo, M, MLP, s->stream));
+                    GemmArgs gd{s->pf_hi, lo, (const __nv_bfloat16*)L.a.down.p, s->pf_x, D, M, D, MLP, 1, &s->ctl->status};
+                    LUMI_TRY(launch_gemm_tcgen05(gd, s->stream));
+                    s->launches += 10;
+                    continue;
+                }
                 LUMI_CUDA(launch_norm_split(s->pf_x, L.m.norm_g, s->pf_hi, lo, M, D, c.eps, s->stream));
                 GemmArgs g1{s->pf_hi, lo, (const __nv_bfloat16*)L.m.in_proj.p, s->pf_proj, R, M, R, D, 0, &s->ctl->status};
                 LUMI_TRY(launch_gemm_tcgen05(g1, s->stream));
@@ -933,6 +981,10 @@ int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head) {
                 LUMI_TRY(launch_gemm_tcgen05(g2, s->stream));
                 s->launches += 5;
             }
+            if (hybrid) {
+                LUMI_CUDA(launch_kv_advance(s->kv_pos, b0, nb, ts, s->stream));
+                s->launches += 1;
+            }
             if (t0 + ts >= T) {
                 LUMI_CUDA(launch_gather_last(s->pf_x, s->x, D, ts, nb, b0, s->stream));
                 s->launches += 1;
@@ -946,7 +998,7 @@ int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head) {
         p.fam = FAM_HEAD;
         LUMI_TRY(linear(p, s->m->embedding, s->x, D, s->logits, c.vocab, nullptr, s->m->final_norm_g, 0, c.vocab));
         LUMI_CUDA(launch_sample(s->logits, batch, c.vocab, s->ctl, s->tok_cur, s->finished, s->out_len, s->stream));
-        LUMI_CUDA(launch_advance_step(s->ctl, nullptr, batch, 1, s->stream));
+        LUMI_CUDA(launch_advance_step(s->ctl, nullptr, batch, 1, s->stream));      // positions were advanced slice by slice
         s->launches += 3 + p.n;
     }
     return LUMI_OK;

@@ -41,13 +41,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     float* sc = red + 4 * HPK * HD;        // [HPK][T]
     __shared__ float hmax[HPK], hsum[HPK];
 
-    const int b = blockIdx.y, kvh = blockIdx.x;
+    const int r = blockIdx.y, kvh = blockIdx.x;          // r: token row (decode: the sequence)
+    const int b = a.b0 + r / a.rows_per_seq;             // sequence slot
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int D = a.n_heads * HD, KV = a.kv_heads * HD;
-    const float* q = a.qkv + (size_t)b * a.ldq + (size_t)kvh * HPK * HD;
-    const float* kn = a.qkv + (size_t)b * a.ldq + D + kvh * HD;
+    const float* q = a.qkv + (size_t)r * a.ldq + (size_t)kvh * HPK * HD;
+    const float* kn = a.qkv + (size_t)r * a.ldq + D + kvh * HD;
     const float* vn = kn + KV;
-    const int pos = a.pos[b];
+    const int pos = a.pos[b] + r % a.rows_per_seq;
     const int32_t* pt = a.page_table + (size_t)b * a.pages_per_seq;
     const int cap = a.window > 0 ? min(a.window, a.max_tokens) : a.max_tokens;
     int T, slot_new;
@@ -75,7 +76,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
         qs[(2 * pr) * HPK + hq] = q0;
         qs[(2 * pr + 1) * HPK + hq] = q1;
     }
-    for (int pr = tid; pr < HD / 2; pr += 128) {
+    for (int pr = tid; pr < HD / 2 && a.phase != 2; pr += 128) {
         float k0 = kn[2 * pr], k1 = kn[2 * pr + 1];
         if (a.rope_base > 0.f) {
             float inv = powf(a.rope_base, -(float)(2 * pr) / (float)HD);
@@ -93,6 +94,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
         KvIo<KT>::st(vd + 2 * pr, vn[2 * pr]);
         KvIo<KT>::st(vd + 2 * pr + 1, vn[2 * pr + 1]);
     }
+    if (a.phase == 1) return;                            // append only
     __syncthreads();
 
     // scores: a cached K row is HD * sizeof(KT) bytes = LPR lanes x 16 bytes, so one warp-wide 16-byte load
@@ -239,7 +241,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     __syncthreads();
     for (int i = tid; i < HPK * HD; i += 128) {
         float v = (red[i] + red[HPK * HD + i]) + (red[2 * HPK * HD + i] + red[3 * HPK * HD + i]);
-        const size_t o = (size_t)b * D + (size_t)kvh * HPK * HD + i;
+        const size_t o = (size_t)r * D + (size_t)kvh * HPK * HD + i;
         if (a.ctx32) a.ctx32[o] = v;
         if (a.chi) {
             __nv_bfloat16 hh, ll;
@@ -275,7 +277,17 @@ cudaError_t launch_kt(const AttnArgs& a, cudaStream_t st) {
     return cudaErrorInvalidValue;
 }
 
+__global__ void kv_advance_kernel(int32_t* kv_pos, int b0, int nb, int by) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < nb) kv_pos[b0 + i] += by;
+}
+
 }  // namespace
+
+cudaError_t launch_kv_advance(int32_t* kv_pos, int b0, int nb, int by, cudaStream_t st) {
+    kv_advance_kernel<<<(nb + 127) / 128, 128, 0, st>>>(kv_pos, b0, nb, by);
+    return cudaGetLastError();
+}
 
 // The cache element type follows the weights: fp32 weights keep an fp32 cache (so fp32 parity is
 // not limited by cache rounding), bf16 weights a bf16 cache.  `pool` carries the type by flag.

@@ -247,8 +247,13 @@ struct AttnArgs {
     int B, n_heads, kv_heads, head_dim, window, max_tokens;
     float rope_base;
     StepCtl* ctl;
+    // Batched prefill: B counts token rows, row r = sequence (b0 + r / rows_per_seq), position pos[sequence] + r % rows_per_seq;
+    // the rows of a slice are appended to the cache by one launch (phase 1) and attend to it in a second one (phase 2).
+    // Decode: rows_per_seq = 1, phase 0 (append, then attend, in one launch).
+    int rows_per_seq = 1, b0 = 0, phase = 0;
 };
 cudaError_t launch_attention_decode(const AttnArgs& a, cudaStream_t st);
+cudaError_t launch_kv_advance(int32_t* kv_pos, int b0, int nb, int by, cudaStream_t st);
 
 
 // ---- tcgen05 GEMM (gemm_tcgen05.cu) ---------------------------------------------------------------

@@ -365,3 +365,42 @@ def test_score_matches_oracle_log_softmax(case):
     s2.prefill(toks, want_logits=False)
     _, nxt2 = s2.forward_step(toks[:, -1] * 0 + 5, want_logits=False)
     assert np.array_equal(nxt, nxt2)
+
+
+@pytest.mark.parametrize("rows", [32768, 256])
+def test_chunked_prefill_with_attention_layers(rows):
+    """bf16 hybrid model (Mamba, attention, Mamba, attention), 150-token prompts: the batched prefill — chunked
+    scan for the Mamba layers, all rows of a slice through the attention layers at once — against the
+    token-by-token prefill and the oracle: last-position logits, Mamba state, and the greedy continuation
+    (which reads the K/V cache the prefill left behind).  rows = 256 forces slices of 64 tokens."""
+    cfg = synth.base_config(n_layers=4, vocab_size=1000, attention_layers=[1, 3], attn_mlp_dim=512, attn_rope_base=10000.0)
+    tens = list(synth.iter_tensors(cfg, seed=16, weights_dtype="bf16", perturb_ones=0.05))
+    B, T, n_new = 4, 150, 8
+    prompts = synth.random_prompts(B, T, cfg.vocab_size, seed=19)
+    model = lumi_b200.NmModel.from_tensors(cfg, tens)
+    step = model.init_states(B, 256)
+    step.set_option("chunked_prefill", 0)
+    lg_step = step.prefill(prompts)
+    chk = model.init_states(B, 256)
+    chk.set_option("chunked_prefill", 64)
+    chk.set_option("prefill_rows", rows)
+    lg_chk = chk.prefill(prompts)
+    for b in range(B):
+        assert rel_err(lg_chk[b], lg_step[b]) < 2e-4, (b, rel_err(lg_chk[b], lg_step[b]))
+        for layer in (0, 2):
+            h1, xp1, bp1, cu1 = chk.read_state(b, layer)
+            h0, xp0, bp0, cu0 = step.read_state(b, layer)
+            assert np.abs(h1 - h0).max() <= 2e-4 * max(1.0, np.abs(h0).max()), (b, layer)
+    # continuation: both sessions decode the same tokens from their caches
+    nxt = prompts[:, -1] * 0 + 7
+    for i in range(4):
+        _, a = step.forward_step(nxt, want_logits=False)
+        _, c = chk.forward_step(nxt, want_logits=False)
+        assert np.array_equal(a, c), (i, a, c)
+        nxt = a
+    ost = cpu_oracle.OracleModel(cfg, tens).init_states()
+    ref_toks, ref_logits = ost.generate(prompts[2], n_new, ignore_eos=True, dump_logits=True)
+    chk.reset()
+    toks, lens, dump, st = chk.generate(prompts, n_new, ignore_eos=True, dump_logits=True)
+    assert max(rel_err(dump[i, 2], ref_logits[i]) for i in range(n_new)) < TOL_BF16
+    _compare_tokens(toks[2], ref_toks, ref_logits, "hybrid chunked prefill, sequence 2")
