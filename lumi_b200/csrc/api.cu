@@ -336,7 +336,7 @@ extern "C" void lumi_session_free(lumi_session* s) {
     cudaSetDevice(s->m->device);
     if (s->stream) cudaStreamSynchronize(s->stream);
     for (auto& g : s->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
-    void* dev[] = {s->gemm_counters, s->gemm_scratch, s->h, s->xprev, s->bprev, s->cum, s->kv_pool, s->page_table, s->kv_pos, s->x, s->proj, s->y32, s->logits,
+    void* dev[] = {s->score_logits, s->gemm_counters, s->gemm_scratch, s->h, s->xprev, s->bprev, s->cum, s->kv_pool, s->page_table, s->kv_pos, s->x, s->proj, s->y32, s->logits,
                    s->act_hi, s->act_lo, s->tok_cur, s->finished, s->out_len, s->ctl, s->gen_out, s->prompt_dev, s->gen_dump,
                    s->pf_x, s->pf_proj, s->pf_rb, s->pf_rc, s->pf_hi, s->pf_lo,
                    s->b1_layers, s->b1_grid_ctl, s->b1_amax_val, s->b1_amax_idx, s->b1_timing, s->b1_tagged};
@@ -875,6 +875,16 @@ int32_t sample_after_b1(lumi_session* s) {
     return LUMI_OK;
 }
 
+template <typename T>
+int32_t grow(T*& p, size_t& cap, size_t need_elems) {
+    if (need_elems <= cap) return LUMI_OK;
+    if (p) LUMI_CUDA(cudaFree(p));
+    p = nullptr; cap = 0;
+    LUMI_CUDA(cudaMalloc(&p, need_elems * sizeof(T)));
+    cap = need_elems;
+    return LUMI_OK;
+}
+
 bool use_chunked_prefill(const lumi_session* s, int batch, int T) {
     if (!(s->opt_chunked_prefill > 0 && T >= s->opt_chunked_prefill && s->m->wdtype == LUMI_DTYPE_BF16 && s->opt_gemm != 1 &&
           prefill_ssd_supported(s->m->cfg) && (s->m->cfg.d_model % 64) == 0 && (s->m->cfg.d_inner() % 64) == 0))
@@ -891,7 +901,8 @@ bool use_chunked_prefill(const lumi_session* s, int batch, int T) {
 // Prompt of T tokens for sequences 0..batch-1 through the chunked SSD scan; tokens come from
 // prompt_dev[T][batch].  Leaves the decode state of every layer as the step-by-step path would, the
 // last position's residual in x, and (with_head) its logits plus the sampled first token.
-int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head) {
+// score_out (device, [batch][T-1]) != null: log p(next prompt token) at every position, from the head over all rows.
+int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head, float* score_out = nullptr) {
     const Config& c = s->m->cfg;
     const int D = c.d_model, DI = c.d_inner(), R = c.in_proj_out();
     const bool hybrid = s->m->n_attn > 0;
@@ -985,6 +996,22 @@ int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head) {
                 LUMI_CUDA(launch_kv_advance(s->kv_pos, b0, nb, ts, s->stream));
                 s->launches += 1;
             }
+            if (score_out != nullptr) {
+                // final norm + tied head over the rows of the slice, a block of rows at a time, then log-softmax at the target
+                const int V = c.vocab;
+                const int SR = (int)std::min<size_t>(4096, std::max<size_t>(128, ((size_t)256 << 20) / ((size_t)V * sizeof(float)) / 128 * 128));
+                LUMI_TRY(grow(s->score_logits, s->score_logits_cap, (size_t)SR * V));
+                LUMI_CUDA(launch_norm_split(s->pf_x, s->m->final_norm_g, s->pf_hi, lo, M, D, c.eps, s->stream));
+                for (int r0 = 0; r0 < M; r0 += SR) {
+                    const int nr = std::min(SR, M - r0);
+                    GemmArgs gh{s->pf_hi + (size_t)r0 * D, lo ? lo + (size_t)r0 * D : nullptr, (const __nv_bfloat16*)s->m->embedding.p,
+                                s->score_logits, V, nr, V, D, 0, &s->ctl->status};
+                    LUMI_TRY(launch_gemm_tcgen05(gh, s->stream));
+                    LUMI_CUDA(launch_logprob_rows(s->score_logits, nr, V, s->prompt_dev, batch, T, ts, t0, b0, r0, score_out, s->stream));
+                    s->launches += 2;
+                }
+                s->launches += 1;
+            }
             if (t0 + ts >= T) {
                 LUMI_CUDA(launch_gather_last(s->pf_x, s->x, D, ts, nb, b0, s->stream));
                 s->launches += 1;
@@ -1046,16 +1073,6 @@ int32_t pull_ctl(lumi_session* s) {
     return LUMI_OK;
 }
 
-template <typename T>
-int32_t grow(T*& p, size_t& cap, size_t need_elems) {
-    if (need_elems <= cap) return LUMI_OK;
-    if (p) LUMI_CUDA(cudaFree(p));
-    p = nullptr; cap = 0;
-    LUMI_CUDA(cudaMalloc(&p, need_elems * sizeof(T)));
-    cap = need_elems;
-    return LUMI_OK;
-}
-
 // prompt[batch][T] (host) -> prompt_dev[T][batch]
 int32_t upload_prompt(lumi_session* s, const uint32_t* tokens, int batch, int T) {
     LUMI_TRY(grow(s->prompt_dev, s->prompt_cap, (size_t)batch * T));
@@ -1107,7 +1124,16 @@ extern "C" int32_t lumi_score(lumi_session* s, const uint32_t* tokens, int32_t b
     s->ctl_host->prompt = s->prompt_dev;
     s->ctl_host->prompt_len = T;
     s->ctl_host->ignore_eos = 1;
+    const bool chunked = use_chunked_prefill(s, batch, T);
+    if (chunked) s->ctl_host->prompt_pos = T;          // the batched path consumes the whole prompt itself
     LUMI_TRY(push_ctl(s));
+    if (chunked) {
+        LUMI_TRY(prefill_chunked(s, batch, T, false, s->gen_dump));
+        LUMI_CUDA(cudaMemcpyAsync(logprobs_out, s->gen_dump, sizeof(float) * (size_t)batch * (T - 1), cudaMemcpyDeviceToHost, s->stream));
+        LUMI_TRY(pull_ctl(s));
+        LUMI_CUDA(cudaStreamSynchronize(s->stream));
+        return check_status(s);
+    }
     const bool mega = s->opt_mega;
     s->opt_mega = 0;                                    // the persistent kernel has no per-position head
     int32_t rc = LUMI_OK;

@@ -179,6 +179,7 @@ struct lumi_session {
     uint32_t* gen_out = nullptr; size_t gen_out_cap = 0;
     uint32_t* prompt_dev = nullptr; size_t prompt_cap = 0;
     float* gen_dump = nullptr; size_t gen_dump_cap = 0;
+    float* score_logits = nullptr; size_t score_logits_cap = 0;    // logits of a block of prefill rows (scoring)
     std::map<int64_t, lumi::GraphEntry> graphs;
     int64_t launches = 0;              // kernels enqueued outside graphs since last reset of the counter
     int64_t launches_per_step = 0;
@@ -206,6 +207,8 @@ struct GemvArgs {
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);
 cudaError_t launch_logprob(const float* logits, int B, int V, const uint32_t* targets, float* out, int out_stride, int out_col,
                            cudaStream_t st);
+cudaError_t launch_logprob_rows(const float* logits, int rows, int V, const uint32_t* prompt, int batch_total, int T, int ts, int t0,
+                                int b0, int row0, float* out, cudaStream_t st);
 // Kernels of kernels.cu launched by the calling thread from now on carry (or not) the
 // programmatic-dependent-launch attribute.
 void set_launch_pdl(bool on);

@@ -1367,6 +1367,45 @@ __global__ void __launch_bounds__(256) logprob_kernel(const float* logits, int V
     }
 }
 
+// The same for the token rows of a prefill slice: logits row i belongs to workspace row r = row0 + i = (sequence b0 + r / ts,
+// position t0 + r % ts); the target is the prompt's next token, rows at the last position have none.
+__global__ void __launch_bounds__(256) logprob_rows_kernel(const float* logits, int V, const uint32_t* prompt, int batch_total,
+                                                           int T, int ts, int t0, int b0, int row0, float* out) {
+    __shared__ float red[8];
+    const int r = row0 + blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = b0 + r / ts, t = t0 + r % ts;
+    if (t >= T - 1) return;
+    const float* l = logits + (size_t)blockIdx.x * V;
+    float m = -FLT_MAX;
+    for (int i = threadIdx.x; i < V; i += 256) m = fmaxf(m, l[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+    __syncthreads();
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < V; i += 256) sum += expf(l[i] - m);
+    sum = warp_sum(sum);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) tot += red[w];
+        const uint32_t tg = prompt[(size_t)(t + 1) * batch_total + b];
+        out[(size_t)b * (T - 1) + t] = tg < (uint32_t)V ? (l[tg] - m) - logf(tot) : -INFINITY;
+    }
+}
+
+cudaError_t launch_logprob_rows(const float* logits, int rows, int V, const uint32_t* prompt, int batch_total, int T, int ts, int t0,
+                                int b0, int row0, float* out, cudaStream_t st) {
+    logprob_rows_kernel<<<rows, 256, 0, st>>>(logits, V, prompt, batch_total, T, ts, t0, b0, row0, out);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_logprob(const float* logits, int B, int V, const uint32_t* targets, float* out, int out_stride, int out_col,
                            cudaStream_t st) {
     logprob_kernel<<<B, 256, 0, st>>>(logits, V, targets, B, out, out_stride, out_col);

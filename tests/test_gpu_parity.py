@@ -335,7 +335,7 @@ def test_sequence_snapshot_resumes_in_another_slot(kind):
         m2.init_states(1, 32).load_state(0, snap)
 
 
-@pytest.mark.parametrize("case", ["tiny_hybrid_f32", "base_bf16_batch12"])
+@pytest.mark.parametrize("case", ["tiny_hybrid_f32", "base_bf16_batch12", "base_bf16_long", "hybrid_bf16_long"])
 def test_score_matches_oracle_log_softmax(case):
     """Teacher-forced log-probabilities at every position (what `evaluate` sums, inference/src/eval.rs:39-139)
     against log-softmax of the oracle's per-position logits; the state afterwards continues like a prefill."""
@@ -343,13 +343,19 @@ def test_score_matches_oracle_log_softmax(case):
         cfg = synth.tiny_config(n_layers=4, attention_layers=[2])
         tens = list(synth.iter_tensors(cfg, seed=6, perturb_ones=0.1))
         B, T, tol = 3, 11, 2e-4
-    else:
+    elif case == "base_bf16_batch12":
         cfg = synth.base_config(n_layers=2, vocab_size=777)
         tens = list(synth.iter_tensors(cfg, seed=6, weights_dtype="bf16"))
         B, T, tol = 12, 6, 2e-3
+    else:
+        # long windows go through the batched prefill (chunked scan, head as one GEMM over all rows)
+        kw = dict(attention_layers=[1], attn_mlp_dim=512) if case == "hybrid_bf16_long" else {}
+        cfg = synth.base_config(n_layers=2, vocab_size=777, **kw)
+        tens = list(synth.iter_tensors(cfg, seed=6, weights_dtype="bf16"))
+        B, T, tol = 3, 140, 2e-3
     toks = synth.random_prompts(B, T, cfg.vocab_size, seed=12)
     model = lumi_b200.NmModel.from_tensors(cfg, tens)
-    sess = model.init_states(B, 64)
+    sess = model.init_states(B, 256)
     got = sess.score(toks)
     assert got.shape == (B, T - 1)
     om = cpu_oracle.OracleModel(cfg, tens)
@@ -361,7 +367,7 @@ def test_score_matches_oracle_log_softmax(case):
             assert abs(got[b, t] - ref) < tol * max(1.0, abs(ref)), (b, t, got[b, t], ref)
     # the state is that of a prefill of all T tokens: the same next tokens as prefill + decode
     _, nxt = sess.forward_step(toks[:, -1] * 0 + 5, want_logits=False)
-    s2 = model.init_states(B, 64)
+    s2 = model.init_states(B, 256)
     s2.prefill(toks, want_logits=False)
     _, nxt2 = s2.forward_step(toks[:, -1] * 0 + 5, want_logits=False)
     assert np.array_equal(nxt, nxt2)
