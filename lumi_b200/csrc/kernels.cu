@@ -917,9 +917,19 @@ __device__ BestPair block_argmax(float v, int i, BestPair* red) {
     __syncthreads();                       // red may still be read from a previous round
     if (lane == 0) { red[warp].v = v; red[warp].i = i; }
     __syncthreads();
-    BestPair r = red[0];
-    for (int w = 1; w < nw; ++w) if (better(red[w].v, red[w].i, r.v, r.i)) r = red[w];
-    return r;
+    if (warp == 0) {                       // the per-warp winners (at most 32) by one more xor tree
+        float wv = lane < nw ? red[lane].v : -INFINITY;
+        int wi = lane < nw ? red[lane].i : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, wv, o);
+            int oi = __shfl_xor_sync(0xffffffffu, wi, o);
+            if (better(ov, oi, wv, wi)) { wv = ov; wi = oi; }
+        }
+        if (lane == 0) { red[32].v = wv; red[32].i = wi; }
+    }
+    __syncthreads();
+    return red[32];
 }
 
 constexpr int kMaxTopK = 256;
@@ -929,7 +939,7 @@ constexpr int kMaxTopK = 256;
 // distribution in vocabulary order.
 __global__ void __launch_bounds__(1024) sample_kernel(const float* logits, int V, StepCtl* ctl,
                                                       uint32_t* tok_cur, int32_t* finished, int32_t* out_len) {
-    __shared__ BestPair red[32];
+    __shared__ BestPair red[33];           // 32 warp winners + the block winner
     __shared__ float top_v[kMaxTopK];
     __shared__ int top_i[kMaxTopK];
     __shared__ float chunk_sum[1024];
@@ -1000,13 +1010,18 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* logits, int V
                 if (tid == 0) { top_v[round] = rr.v; top_i[round] = rr.i; }
                 __syncthreads();
             }
-            if (tid == 0) {
-                // survivors into vocabulary order (insertion sort, k <= 256)
-                for (int a1 = 1; a1 < k; ++a1) {
-                    float v = top_v[a1]; int i = top_i[a1]; int j = a1 - 1;
-                    while (j >= 0 && top_i[j] > i) { top_v[j + 1] = top_v[j]; top_i[j + 1] = top_i[j]; --j; }
-                    top_v[j + 1] = v; top_i[j + 1] = i;
+            // survivors into vocabulary order: entry j goes to the position given by the number of smaller ids
+            {
+                float sv = 0.f; int si = 0, rank = 0;
+                if (tid < k) {
+                    sv = top_v[tid]; si = top_i[tid];
+                    for (int j = 0; j < k; ++j) rank += top_i[j] < si ? 1 : 0;
                 }
+                __syncthreads();
+                if (tid < k) { top_v[rank] = sv; top_i[rank] = si; }
+                __syncthreads();
+            }
+            if (tid == 0) {
                 float mx = -INFINITY;
                 for (int j = 0; j < k; ++j) { top_v[j] = __fmul_rn(top_v[j], inv_t); mx = fmaxf(mx, top_v[j]); }
                 float sum = 0.f;
