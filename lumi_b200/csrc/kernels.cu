@@ -310,13 +310,13 @@ __global__ void __launch_bounds__(256) gemv_kernel(const float* A, int lda, cons
 // For the smallest batches the chain of a token is latency-bound: each kernel waits for its predecessor,
 // then for HBM.  Here a CTA owns N / gridDim.x consecutive output rows and asks for ALL of their weights
 // the moment it becomes resident — the first 8 * RPW rows straight into registers (RPW rows per warp), the
-// rest by bulk copies into shared memory (one mbarrier per row) — and only then executes the dependency
-// wait.  Launched with programmatic dependent launch, the CTAs become resident while the predecessors
+// rest by bulk copies into shared memory (one mbarrier per warp, armed with the bytes of that warp's rows) —
+// and only then executes the dependency wait.  Launched with programmatic dependent launch, the CTAs become resident while the predecessors
 // still run, so the HBM stream of this kernel overlaps them; after the wait only the activation staging,
 // the RMSNorm and the dot products from on-chip memory remain.  One wave, at most one CTA per SM; the
 // register / shared-memory split is chosen so that the three kernels of a block fit on an SM together.
-// Summation order of a row: per-lane partials over chunks lane, lane + 32, ... in ascending k, then the
-// 5-step xor tree.
+// Summation order of a row: lane l owns chunks l, l + 32, ...; two per-lane partial sums (even and odd
+// chunks, each in ascending k) are added, then the 5-step xor tree.
 constexpr int kPreMaxSmemRows = 64;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
