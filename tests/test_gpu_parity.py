@@ -410,3 +410,36 @@ def test_chunked_prefill_with_attention_layers(rows):
     toks, lens, dump, st = chk.generate(prompts, n_new, ignore_eos=True, dump_logits=True)
     assert max(rel_err(dump[i, 2], ref_logits[i]) for i in range(n_new)) < TOL_BF16
     _compare_tokens(toks[2], ref_toks, ref_logits, "hybrid chunked prefill, sequence 2")
+
+
+def test_slot_reuse_by_transplanting_a_prefilled_sequence():
+    """Continuous batching with the snapshot calls: while a batch of three sequences decodes, sequence 1 ends; a new
+    prompt is prefilled in a one-slot side session, its snapshot is loaded into slot 1, and decoding goes on.
+    The newcomer's tokens are the oracle's for its prompt; the neighbours never notice."""
+    cfg = synth.tiny_config(n_layers=4, attention_layers=[2])
+    tens = list(synth.iter_tensors(cfg, seed=21, perturb_ones=0.1))
+    om = cpu_oracle.OracleModel(cfg, tens)
+    prompts = synth.random_prompts(3, 6, cfg.vocab_size, seed=22)
+    newcomer = synth.random_prompts(1, 9, cfg.vocab_size, seed=23)[0]
+    refs = [om.init_states().generate(prompts[b], 10, ignore_eos=True) for b in range(3)]
+    ref_new = om.init_states().generate(newcomer, 6, ignore_eos=True)
+    model = lumi_b200.NmModel.from_tensors(cfg, tens)
+    main = model.init_states(3, 64)
+    main.prefill(prompts[:, :-1], want_logits=False)
+    cur = prompts[:, -1].copy()
+    got = [[], [], []]
+    for i in range(4):
+        _, cur = main.forward_step(cur, want_logits=False)
+        for b in range(3): got[b].append(int(cur[b]))
+    # sequence 1 is done: bring the newcomer in
+    side = model.init_states(1, 64)
+    side.prefill(newcomer[None, :-1], want_logits=False)
+    main.load_state(1, side.save_state(0))
+    cur = cur.copy(); cur[1] = newcomer[-1]
+    new_tokens = []
+    for i in range(6):
+        _, cur = main.forward_step(cur, want_logits=False)
+        got[0].append(int(cur[0])); got[2].append(int(cur[2])); new_tokens.append(int(cur[1]))
+    assert got[0] == [int(t) for t in refs[0]] and got[2] == [int(t) for t in refs[2]]
+    assert got[1] == [int(t) for t in refs[1][:4]]
+    assert new_tokens == [int(t) for t in ref_new]
