@@ -275,18 +275,56 @@ class Session:
         return x
 
 
+class TextCodec:
+    """The text boundary of `lumi-infer generate` (inference/src/main.rs:100-113, 154-165): byte-level models map
+    byte b to id b + 3 with eos 2 and print single bytes that are valid UTF-8 on their own; other models use a
+    HuggingFace `tokenizer.json` (byte-level BPE as the trainer builds it, training/src/tokenizer.rs:19-76) through
+    the `tokenizers` package, eos = id of "<eos>" or 2, pieces decoded token by token with special tokens skipped."""
+
+    def __init__(self, byte_level: bool, tokenizer_path: Optional[str] = None):
+        self.byte_level = byte_level
+        self._tok = None
+        if not byte_level:
+            if tokenizer_path is None:
+                raise ValueError("a model that is not byte-level needs a tokenizer.json (main.rs:105-107 loads one)")
+            try:
+                from tokenizers import Tokenizer
+            except ImportError as e:      # the package is the same library the reference links as a crate
+                raise RuntimeError("the `tokenizers` package is needed for tokenizer.json models") from e
+            self._tok = Tokenizer.from_file(tokenizer_path)
+
+    @property
+    def eos_id(self) -> int:
+        if self.byte_level:
+            return 2
+        eos = self._tok.token_to_id("<eos>")
+        return 2 if eos is None else int(eos)
+
+    def encode(self, text: str) -> np.ndarray:
+        if self.byte_level:
+            return np.frombuffer(text.encode(), dtype=np.uint8).astype(np.uint32) + 3
+        return np.asarray(self._tok.encode(text, add_special_tokens=False).ids, dtype=np.uint32)
+
+    def piece(self, token: int) -> str:
+        """What the loop prints for one generated token (main.rs:154-165)."""
+        if self.byte_level:
+            return chr(token - 3) if 3 <= token < 131 else ""
+        return self._tok.decode([int(token)], skip_special_tokens=True)
+
+    def decode(self, tokens) -> str:
+        return "".join(self.piece(int(t)) for t in tokens)
+
+
 def generate(model_path: str, config_path: str, prompt: str, max_tokens: int = 200, temperature: float = 0.8,
-             top_k: int = 0, seed: int = 0, device: int = 0) -> Tuple[str, np.ndarray]:
-    """`lumi-infer generate` for byte-level models (inference/src/main.rs:96-177): ids = byte + 3,
-    eos = 2, bytes 3..258 decoded back to text.  (BPE models need a tokenizer.json, which lies
-    outside this package; feed token ids to Session.generate instead.)"""
+             top_k: int = 0, seed: int = 0, device: int = 0, tokenizer_path: Optional[str] = None) -> Tuple[str, np.ndarray]:
+    """`lumi-infer generate` (inference/src/main.rs:96-177): encode the prompt, run the token loop on the GPU until
+    eos or `max_tokens`, return prompt + generated text and the generated ids."""
     model = NmModel.load(model_path, config_path, device)
-    if not model.config.byte_level:
-        raise ValueError("generate(): only byte_level models carry their own tokenizer; pass token ids to Session.generate")
-    ids = np.frombuffer(prompt.encode(), dtype=np.uint8).astype(np.uint32) + 3
-    sess = model.init_states(1)
-    out, lens, _, _ = sess.generate(ids[None, :], max_tokens, temperature=temperature, top_k=top_k, seed=seed, eos_id=2)
+    codec = TextCodec(bool(model.config.byte_level), tokenizer_path)
+    ids = codec.encode(prompt)
+    if len(ids) == 0:
+        raise ValueError("empty prompt")
+    sess = model.init_states(1, len(ids) + max_tokens + 1)
+    out, lens, _, _ = sess.generate(ids[None, :], max_tokens, temperature=temperature, top_k=top_k, seed=seed, eos_id=codec.eos_id)
     toks = out[0, :lens[0]]
-    # main.rs:154-160 prints a byte only when it is valid UTF-8 on its own, i.e. ASCII
-    text = bytes(int(t) - 3 for t in toks if 3 <= t < 131).decode("ascii")
-    return prompt + text, toks
+    return prompt + codec.decode(toks), toks
