@@ -105,6 +105,11 @@ __global__ void __launch_bounds__(256, 2) ssd_prefill_kernel(PrefillArgs a) {
     if (tid < HN) sm.cum[tid] = a.cum[bh * HN + tid];
     __syncthreads();
 
+    // BCNorm weights of this thread's angle pair (the same for every token)
+    const int kk0 = g * N + 2 * (tid & 31);
+    const float kbg0 = a.bg[kk0], kbg1 = a.bg[kk0 + 1], kbb0 = a.bb[kk0], kbb1 = a.bb[kk0 + 1];
+    const float kcg0 = a.cg[kk0], kcg1 = a.cg[kk0 + 1], kcb0 = a.cb[kk0], kcb1 = a.cb[kk0 + 1];
+
     int last_valid = 0;
     for (int t0 = 0; t0 < ts; t0 += LCH) {
         const int nv = min(LCH, ts - t0);                  // valid tokens in this chunk
@@ -156,28 +161,52 @@ __global__ void __launch_bounds__(256, 2) ssd_prefill_kernel(PrefillArgs a) {
             }
         }
         // ---- 2. x, gate, normalised B / C, angles, rotation
-        for (int e = tid; e < LCH * P; e += 256) {
-            const int i = e / P, p = e % P;
-            float xv = 0.f, gv = 0.f;
-            if (i < nv) {
-                const float* pr = prow0 + (size_t)(t0 + i) * R;
-                xv = silu_ref(pr[h * P + p]);              // model.rs:310
-                gv = silu_ref(pr[DI + h * P + p]);         // model.rs:370
+        {
+            // all loads of the chunk's x and z first (8 tokens per thread), then the activations: the projection rows
+            // come from DRAM and a load-use-load chain per token was the largest stall of this kernel
+            constexpr int NE = LCH * P / 256;
+            float xr[NE], zr[NE];
+#pragma unroll
+            for (int q = 0; q < NE; ++q) {
+                const int e = tid + 256 * q, i = e / P, p = e % P;
+                xr[q] = 0.f; zr[q] = 0.f;
+                if (i < nv) {
+                    const float* pr = prow0 + (size_t)(t0 + i) * R;
+                    xr[q] = pr[h * P + p];
+                    zr[q] = pr[DI + h * P + p];
+                }
             }
-            sm.Xt[p][i] = xv;
-            sm.Gt[i][p] = gv;
+#pragma unroll
+            for (int q = 0; q < NE; ++q) {
+                const int e = tid + 256 * q, i = e / P, p = e % P;
+                sm.Xt[p][i] = i < nv ? silu_ref(xr[q]) : 0.f;      // model.rs:310
+                sm.Gt[i][p] = i < nv ? silu_ref(zr[q]) : 0.f;      // model.rs:370
+            }
         }
         {
             const int k = tid & 31, sg = tid >> 5;         // angle pair k, token segment sg (8 tokens)
             float loc[8], run = 0.f;
+            // this thread's 8 tokens: theta and the raw B / C pairs are requested together, ahead of any arithmetic
+            float thv[8], rb8[8], rc8[8], pb0[8], pb1[8], pc0[8], pc1[8];
+            const int i0k = g * N + 2 * k;
+#pragma unroll
+            for (int ii = 0; ii < 8; ++ii) {
+                const int i = sg * 8 + ii;
+                thv[ii] = 0.f; rb8[ii] = rc8[ii] = 0.f; pb0[ii] = pb1[ii] = pc0[ii] = pc1[ii] = 0.f;
+                if (i < nv) {
+                    const float* pr = prow0 + (size_t)(t0 + i) * R;
+                    const size_t row = (size_t)b * ts + t0 + i;
+                    thv[ii] = pr[off_dt + 3 * H + h * HN + k];
+                    rb8[ii] = a.rb[row]; rc8[ii] = a.rc[row];
+                    pb0[ii] = pr[off_b + i0k]; pb1[ii] = pr[off_b + i0k + 1];
+                    pc0[ii] = pr[off_c + i0k]; pc1[ii] = pr[off_c + i0k + 1];
+                }
+            }
 #pragma unroll
             for (int ii = 0; ii < 8; ++ii) {
                 const int i = sg * 8 + ii;
                 float d = 0.f;
-                if (i < nv) {
-                    const float th = prow0[(size_t)(t0 + i) * R + off_dt + 3 * H + h * HN + k];
-                    d = __fmul_rn(sm.dtp[i], __fmul_rn(tanhf(th), PI_F));     // model.rs:341-342
-                }
+                if (i < nv) d = __fmul_rn(sm.dtp[i], __fmul_rn(tanhf(thv[ii]), PI_F));     // model.rs:341-342
                 run += d;
                 loc[ii] = run;
             }
@@ -197,14 +226,11 @@ __global__ void __launch_bounds__(256, 2) ssd_prefill_kernel(PrefillArgs a) {
                 const int i = sg * 8 + ii;
                 float b0 = 0.f, b1 = 0.f, c0 = 0.f, c1 = 0.f;
                 if (i < nv) {
-                    const size_t row = (size_t)b * ts + t0 + i;
-                    const float* pr = prow0 + (size_t)(t0 + i) * R;
-                    const float rb = a.rb[row], rc = a.rc[row];
-                    const int i0 = g * N + 2 * k;
-                    const float nb0 = __fadd_rn(__fmul_rn(__fmul_rn(pr[off_b + i0], rb), a.bg[i0]), a.bb[i0]);
-                    const float nb1 = __fadd_rn(__fmul_rn(__fmul_rn(pr[off_b + i0 + 1], rb), a.bg[i0 + 1]), a.bb[i0 + 1]);
-                    const float nc0 = __fadd_rn(__fmul_rn(__fmul_rn(pr[off_c + i0], rc), a.cg[i0]), a.cb[i0]);
-                    const float nc1 = __fadd_rn(__fmul_rn(__fmul_rn(pr[off_c + i0 + 1], rc), a.cg[i0 + 1]), a.cb[i0 + 1]);
+                    const float rb = rb8[ii], rc = rc8[ii];
+                    const float nb0 = __fadd_rn(__fmul_rn(__fmul_rn(pb0[ii], rb), kbg0), kbb0);
+                    const float nb1 = __fadd_rn(__fmul_rn(__fmul_rn(pb1[ii], rb), kbg1), kbb1);
+                    const float nc0 = __fadd_rn(__fmul_rn(__fmul_rn(pc0[ii], rc), kcg0), kcb0);
+                    const float nc1 = __fadd_rn(__fmul_rn(__fmul_rn(pc1[ii], rc), kcg1), kcb1);
                     float sa, ca;
                     sincosf(fmodf(base + loc[ii], TWO_PI), &sa, &ca);
                     b0 = __fsub_rn(__fmul_rn(ca, nb0), __fmul_rn(sa, nb1));   // model.rs:345-348
