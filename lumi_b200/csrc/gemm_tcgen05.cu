@@ -573,7 +573,7 @@ int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st) {
         // K can be split over CTAs as well (LUMI_GEMM_SPLITK=2, 4 or 8; at least four k-blocks per split) when the
         // tiles do not fill the SMs.  Off by default: measured slower at 64-512 rows, because the fix-up (the last
         // warp to arrive adds the parked partial tiles in split order) is a chain of L2 round trips in few warps.
-        static const int widths[] = {256, 224, 208, 192, 160, 128, 96, 64};
+        static const int widths[] = {256, 224, 208, 192, 160, 128, 96, 64, 32};
         static const int max_splits = getenv("LUMI_GEMM_SPLITK") ? atoi(getenv("LUMI_GEMM_SPLITK")) : 1;
         const long tiles_m = (a.M + BM - 1) / BM;
         const int num_kb = a.K / BK;
@@ -592,7 +592,7 @@ int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st) {
         }
 #define LUMI_PERSIST_CASE(W) if (best == W) return split ? launch_persistent<W, true>(a, best_splits, st) : launch_persistent<W, false>(a, best_splits, st);
         LUMI_PERSIST_CASE(256) LUMI_PERSIST_CASE(224) LUMI_PERSIST_CASE(208) LUMI_PERSIST_CASE(192) LUMI_PERSIST_CASE(160) LUMI_PERSIST_CASE(128)
-        LUMI_PERSIST_CASE(96) LUMI_PERSIST_CASE(64)
+        LUMI_PERSIST_CASE(96) LUMI_PERSIST_CASE(64) LUMI_PERSIST_CASE(32)
 #undef LUMI_PERSIST_CASE
     }
     if (tiles256 >= 148) return split ? launch_t<256, true, 1>(a, st) : launch_t<256, false, 1>(a, st);
