@@ -79,3 +79,27 @@ def test_bad_token_and_batch_and_kv_capacity():
     sess.reset()                                                    # the session stays usable
     logits = sess.prefill(np.full((1, 4), 5, dtype=np.uint32))
     assert np.isfinite(logits).all()
+
+
+def test_score_and_snapshot_argument_errors():
+    """Bad arguments to the scoring and snapshot calls come back as status codes, never as aborts."""
+    import ctypes as C
+    cfg = synth.tiny_config(n_layers=2)
+    model = lumi_b200.NmModel.from_tensors(cfg, list(synth.iter_tensors(cfg, seed=1)))
+    sess = model.init_states(2, 32)
+    with pytest.raises(lumi_b200.LumiError):
+        sess.score(np.array([[5], [6]], dtype=np.uint32))                 # a window of one token has nothing to score
+    with pytest.raises(lumi_b200.LumiError):
+        sess.score(np.array([[5, cfg.vocab_size + 7, 3]], dtype=np.uint32))   # token id out of range
+    with pytest.raises(lumi_b200.LumiError):
+        sess.save_state(2)                                                # slot out of range
+    snap = sess.save_state(1)
+    with pytest.raises(lumi_b200.LumiError):
+        sess.load_state(0, snap[: len(snap) // 2])                        # truncated
+    bad = snap.copy()
+    bad[0] ^= 0xFF
+    with pytest.raises(lumi_b200.LumiError):
+        sess.load_state(0, bad)                                           # not a snapshot
+    sess.load_state(0, snap)                                              # the intact one still loads
+    n = C.c_int64()
+    assert lumi_b200.lib().lumi_session_state_bytes(sess._h, C.byref(n)) == 0 and n.value == len(snap)
