@@ -15,7 +15,9 @@
  *   - returns LUMI_OK (0) or a negative LUMI_E_* code; never aborts, never throws;
  *   - after a failure, lumi_last_error() (calling thread) holds a message;
  *   - host buffers passed in are borrowed for the duration of the call only;
- *   - the library owns all device memory; nothing is allocated after lumi_session_create();
+ *   - the library owns all device memory; the decode step allocates nothing after lumi_session_create()
+ *     (grow-only work areas exist for lumi_generate's outputs, the batched prefill and lumi_score: they are
+ *     sized by the first call that needs them and reused afterwards);
  *   - one handle is driven by one host thread at a time; handles on different devices are
  *     independent (one host thread or process per GPU; the path needs no collective);
  *   - there is no CPU fallback: without a CUDA device every call that needs one fails.
@@ -105,8 +107,8 @@ int32_t lumi_model_info(const lumi_model* m, int64_t* out12);
  *      731-763) for `max_batch` independent sequences ----------------------------------------- */
 
 /* Allocates SSM state (fp32, rank-1 factors for prev_bx), the attention cache for max_tokens_kv
- * tokens per sequence (bf16, ignored for models without attention layers) and all scratch, then
- * resets every slot. */
+ * tokens per sequence (element type of the weights: bf16 or fp32; ignored for models without attention
+ * layers) and the decode step's scratch, then resets every slot. */
 int32_t lumi_session_create(lumi_model* m, int32_t max_batch, int32_t max_tokens_kv, lumi_session** out);
 
 /* h <- h_init broadcast over head_dim, prev_bx <- 0, cum_angle <- 0, cache emptied.
@@ -119,25 +121,27 @@ void    lumi_session_free(lumi_session* s);
  *                         "split_activations" = 1 (default) feeds tensor-core GEMMs with bf16 hi+lo
  *                         halves of each fp32 activation, 0 rounds activations to bf16 once;
  *                         "graph" = 1 (default) replays the decode step as a CUDA graph;
- *                         "pdl" = 1 (default) launches the weight-streaming kernels with programmatic
- *                         dependent launch so each one prefetches its weights while its predecessor runs;
+ *                         "pdl" = 1 (default) launches the kernels of small batches with programmatic dependent
+ *                         launch so each one requests its weights / state while its predecessors still run;
  *                         "chunked_prefill" = minimum prompt length (default 128, 0 = never) from which bf16
- *                         Mamba-only models prefill with the chunked SSD scan (chunk 64) and tensor-core GEMMs over
- *                         all prompt tokens instead of token by token (same state to rounding); "prefill_rows" =
+ *                         models (attention layers included, unless one has a sliding window) prefill with the
+ *                         chunked SSD scan (chunk 64), attention over all rows of a slice and tensor-core GEMMs
+ *                         over all prompt tokens instead of token by token (same state to rounding); "prefill_rows" =
  *                         token rows per pass of that path (default 32768; sets its workspace size);
  *                         "overlap" = minimum batch (default 0 = never) from which the tensor-core path runs two
  *                         lanes of sequences side by side on prioritised streams (measured neutral: the state
  *                         step needs its L1 and cannot share an SM with the 198 KB GEMM);
  *                         "megakernel" = 1 runs batch-1 calls on Mamba-only models (head_dim 32, d_state 64) as
- *                         one persistent cooperative kernel per call (default 0: measured on par with the
- *                         graph-replayed kernel chain, which needs no device-side waits). */
+ *                         one persistent cooperative kernel per call (default 0: measured slower than the
+ *                         graph-replayed chain of dependent-launched kernels). */
 int32_t lumi_session_set_option(lumi_session* s, const char* name, int64_t value);
 
 /* ---- token loop: replaces NmModel::forward_step (inference/src/model.rs:766-801) and the
  *      generate loop (inference/src/main.rs:118-170) ------------------------------------------ */
 
-/* Feeds tokens[batch][T] (row-major) through the model position by position, exactly as the
- * reference prefills (main.rs:121-125).  last_logits (may be NULL): [batch][vocab] fp32 of the final
+/* Feeds tokens[batch][T] (row-major) through the model: position by position, exactly as the
+ * reference prefills (main.rs:121-125), or by the batched path the "chunked_prefill" option describes
+ * (same resulting state to rounding).  last_logits (may be NULL): [batch][vocab] fp32 of the final
  * position.  Sequences occupy slots 0..batch-1. */
 int32_t lumi_prefill(lumi_session* s, const uint32_t* tokens, int32_t batch, int32_t T, float* last_logits);
 
