@@ -197,14 +197,8 @@ def batch1_line(args, peak_gbs):
             "value": toks, "unit": UNIT, "bytes_per_step": per_step, "achieved_gbs": ach, "peak_gbs": peak_gbs, "frac": ach / peak_gbs}
 
 
-CONFIGS = {
-    # name: (config kwargs, weights dtype, batch, prompt length, decode tokens, sampling)
-    "config1": (dict(), "f32", 1, 32, 256, dict()),
-    "config2": (dict(), "bf16", 64, 128, 512, dict()),
-    "config3": (dict(n_layers=96), "bf16", 256, 2048, 256, dict()),
-    "config4": (dict(attention_interval=6, attn_mlp_dim=2816, attn_rope_base=10000.0), "bf16", 128, 1024, 1024,
-                dict(temperature=0.8, top_k=50, seed=1234)),
-}
+# name: (config kwargs, weights dtype, batch, prompt length, decode tokens, sampling, prompt seed)
+CONFIGS = {k: v for k, v in synth.BENCH_CONFIGS.items() if k != "config5"}      # config 5 is the default sweep
 
 
 def run_named_config(args, rank, local_rank, world):
@@ -213,7 +207,7 @@ def run_named_config(args, rank, local_rank, world):
     if rank != 0:
         return
     import lumi_b200
-    kw, wdt, batch, T, n_new, samp = CONFIGS[args.workload]
+    kw, wdt, batch, T, n_new, samp, pseed = CONFIGS[args.workload]
     if args.steps_override:
         n_new = args.steps_override
     cfg = synth.base_config(max_seq_len=4096, **kw)
@@ -221,7 +215,7 @@ def run_named_config(args, rank, local_rank, world):
     model = lumi_b200.NmModel.from_tensors(cfg, synth.iter_tensors(cfg, seed=0, weights_dtype=wdt), device=local_rank)
     info = model.info()
     sess = model.init_states(batch, T + n_new + 1)
-    prompts = synth.random_prompts(batch, T, cfg.vocab_size, seed=0)
+    prompts = synth.random_prompts(batch, T, cfg.vocab_size, seed=pseed)
     sess.generate(prompts[:, :min(T, 128)], 4, ignore_eos=True, **samp)        # warm-up (graphs, attributes)
     sess.reset()
     sampler = ClockSampler(local_rank)

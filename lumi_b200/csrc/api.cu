@@ -338,7 +338,7 @@ extern "C" void lumi_session_free(lumi_session* s) {
     for (auto& g : s->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
     void* dev[] = {s->score_logits, s->gemm_counters, s->gemm_scratch, s->h, s->xprev, s->bprev, s->cum, s->kv_pool, s->page_table, s->kv_pos, s->x, s->proj, s->y32, s->logits,
                    s->act_hi, s->act_lo, s->tok_cur, s->finished, s->out_len, s->ctl, s->gen_out, s->prompt_dev, s->gen_dump,
-                   s->pf_x, s->pf_proj, s->pf_rb, s->pf_rc, s->pf_hi, s->pf_lo,
+                   s->pf_x, s->pf_proj, s->pf_rb, s->pf_rc, s->pf_hi, s->pf_lo, s->slot_buf,
                    s->b1_layers, s->b1_grid_ctl, s->b1_amax_val, s->b1_amax_idx, s->b1_timing, s->b1_tagged};
     for (void* p : dev) if (p) cudaFree(p);
     if (s->ctl_host) cudaFreeHost(s->ctl_host);
@@ -386,6 +386,22 @@ static int32_t session_alloc(lumi_session* s) {
     }
     if (na > 0) {
         if (s->max_tokens_kv <= 0) return fail(LUMI_E_INVALID, "max_tokens_kv must be > 0 for a model with attention layers");
+        // the attention kernel keeps one score per cached token and query head of a group in shared memory
+        // (227 KB per CTA): the longest context a layer can attend to is bounded by that
+        {
+            const int hd = c.attn_head_dim(), hpk = c.attn_n_heads / std::max(1, c.attn_kv_heads);
+            const long fixed = (long)5 * hd * hpk * 4 + 1024;
+            const long max_ctx = (227 * 1024 - fixed) / (4L * hpk);
+            int ai = 0;
+            for (const Layer& L : s->m->layers) {
+                if (!L.is_attn) continue;
+                const int ctx = L.window > 0 ? std::min(L.window, s->max_tokens_kv) : s->max_tokens_kv;
+                if (ctx > max_ctx)
+                    return fail(LUMI_E_UNSUPPORTED, "attention layer %d would attend to %d cached tokens; with %d query heads per kv head the kernel holds at most %ld "
+                                "(give the layer a sliding window or a smaller max_tokens_kv)", ai, ctx, hpk, max_ctx);
+                ++ai;
+            }
+        }
         s->pages_per_seq = (s->max_tokens_kv + kPageTokens - 1) / kPageTokens;
         const size_t esz = s->m->wdtype == LUMI_DTYPE_BF16 ? 2 : 4;
         s->kv_layer_bytes = B * s->pages_per_seq * 2 * kPageTokens * (size_t)c.kv_dim() * esz;
@@ -396,6 +412,7 @@ static int32_t session_alloc(lumi_session* s) {
         LUMI_CUDA(cudaMemcpy(s->page_table, pt.data(), pt.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
     }
     LUMI_CUDA(cudaMalloc(&s->kv_pos, sizeof(int32_t) * B));
+    LUMI_CUDA(cudaMalloc(&s->slot_buf, sizeof(int32_t) * B));
     LUMI_CUDA(cudaMalloc(&s->gemm_counters, sizeof(int32_t) * 2 * kGemmCounters));
     LUMI_CUDA(cudaMemset(s->gemm_counters, 0, sizeof(int32_t) * 2 * kGemmCounters));
     LUMI_CUDA(cudaMalloc(&s->gemm_scratch, sizeof(float) * 2 * kGemmScratchFloats));
@@ -486,7 +503,8 @@ extern "C" int32_t lumi_session_reset(lumi_session* s, const int32_t* slots, int
         if (n_slots <= 0) return LUMI_OK;
         for (int i = 0; i < n_slots; ++i)
             if (slots[i] < 0 || slots[i] >= s->max_batch) return fail(LUMI_E_INVALID, "slot %d out of range [0,%d)", slots[i], s->max_batch);
-        LUMI_CUDA(cudaMalloc(&dslots, sizeof(int32_t) * n_slots));
+        if (n_slots > s->max_batch) return fail(LUMI_E_INVALID, "%d slots given, the session has %d", n_slots, s->max_batch);
+        dslots = s->slot_buf;                        // allocated with the session: a reset allocates nothing
         LUMI_CUDA(cudaMemcpyAsync(dslots, slots, sizeof(int32_t) * n_slots, cudaMemcpyHostToDevice, s->stream));
         n = n_slots;
     }
@@ -500,11 +518,9 @@ extern "C" int32_t lumi_session_reset(lumi_session* s, const int32_t* slots, int
     if (!slots) {
         LUMI_CUDA(cudaMemsetAsync(s->kv_pos, 0, sizeof(int32_t) * B, s->stream));
     } else {
-        std::vector<int32_t> z(1, 0);
         for (int i = 0; i < n_slots; ++i) LUMI_CUDA(cudaMemsetAsync(s->kv_pos + slots[i], 0, sizeof(int32_t), s->stream));
     }
     LUMI_CUDA(cudaStreamSynchronize(s->stream));
-    if (dslots) LUMI_CUDA(cudaFree(dslots));
     return LUMI_OK;
 }
 
@@ -1397,6 +1413,15 @@ extern "C" int32_t lumi_session_load_state(lumi_session* s, int32_t slot, const 
         return fail(LUMI_E_TENSOR, "snapshot of another model or cache size (%u Mamba + %u attention layers, %llu bytes; this session: %d + %d, %zu)",
                     hd.n_mamba, hd.n_attn, (unsigned long long)hd.payload_bytes, s->m->n_mamba, s->m->n_attn, L.payload);
     if (nbytes < (int64_t)(sizeof(hd) + L.payload)) return fail(LUMI_E_INVALID, "snapshot truncated");
+    // the position indexes the page table and the cache: a value outside what this session can hold is refused here
+    // (with a sliding window on every attention layer positions may run past the capacity: the ring wraps)
+    if (hd.kv_pos < 0) return fail(LUMI_E_INVALID, "snapshot with a negative position (%d)", hd.kv_pos);
+    if (s->m->n_attn > 0) {
+        bool all_windowed = true;
+        for (const Layer& Ly : s->m->layers) if (Ly.is_attn && !(Ly.window > 0 && Ly.window <= s->max_tokens_kv)) all_windowed = false;
+        if (!all_windowed && hd.kv_pos > s->max_tokens_kv)
+            return fail(LUMI_E_INVALID, "snapshot at position %d, this session's cache holds %d tokens", hd.kv_pos, s->max_tokens_kv);
+    }
     LUMI_CUDA(cudaSetDevice(s->m->device));
     LUMI_CUDA(cudaMemcpyAsync(s->kv_pos + slot, &hd.kv_pos, sizeof(int32_t), cudaMemcpyHostToDevice, s->stream));
     LUMI_TRY(snap_copy(s, slot, (char*)const_cast<void*>(host_buf) + sizeof(SnapHeader), false));

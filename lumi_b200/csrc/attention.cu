@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     int T, slot_new;
     if (a.window > 0 && a.window <= a.max_tokens) { slot_new = pos % a.window; T = min(pos + 1, a.window); }
     else { slot_new = pos; T = pos + 1; }
-    if (slot_new >= cap || T > cap) {      // cache capacity exceeded: report, write nothing
+    if (pos < 0 || slot_new >= cap || T > cap) {      // position outside the cache (full, or a corrupt position): report, write nothing
         if (tid == 0) atomicOr(&a.ctl->status, STATUS_KV_FULL);
         return;
     }

@@ -164,6 +164,7 @@ struct lumi_session {
     size_t kv_layer_bytes = 0;
     int32_t* page_table = nullptr;     // [max_batch][pages_per_seq]
     int32_t* kv_pos = nullptr;         // [max_batch] tokens consumed so far (absolute position)
+    int32_t* slot_buf = nullptr;       // [max_batch] slot list of a partial reset
     int pages_per_seq = 0;
     // activations
     float *x = nullptr, *proj = nullptr, *y32 = nullptr, *logits = nullptr;

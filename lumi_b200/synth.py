@@ -225,10 +225,28 @@ def write_model_dir(dirpath: str, cfg: ModelConfig, seed: int = 0, weights_dtype
     return cpath, mpath
 
 
+def random_prompt_row(b: int, length: int, vocab: int, seed: int = 0) -> np.ndarray:
+    """Row `b` of random_prompts(): uniform ids in [3, vocab) from the Philox stream keyed by (seed, b)."""
+    g = np.random.Generator(np.random.Philox(key=[seed, 0x70726F6D + b]))
+    return g.integers(3, vocab, size=length, dtype=np.uint32)
+
+
 def random_prompts(batch: int, length: int, vocab: int, seed: int = 0) -> np.ndarray:
     """Uniform ids in [3, vocab): one Philox stream keyed by (seed, sequence index)."""
     out = np.empty((batch, length), dtype=np.uint32)
     for b in range(batch):
-        g = np.random.Generator(np.random.Philox(key=[seed, 0x70726F6D + b]))
-        out[b] = g.integers(3, vocab, size=length, dtype=np.uint32)
+        out[b] = random_prompt_row(b, length, vocab, seed)
     return out
+
+
+# The benchmark configurations 1-5: (config kwargs, weights dtype, batch per GPU, prompt length, decode tokens,
+# sampling, prompt seed).  Weights always come from seed 0.  Configuration 5 is the throughput sweep; its batch
+# here is one resident wave of a GPU (the first 2048 of the 4096 sequences, whose prompts use seed 1000).
+BENCH_CONFIGS = {
+    "config1": (dict(), "f32", 1, 32, 256, dict(), 0),
+    "config2": (dict(), "bf16", 64, 128, 512, dict(), 0),
+    "config3": (dict(n_layers=96), "bf16", 256, 2048, 256, dict(), 0),
+    "config4": (dict(attention_interval=6, attn_mlp_dim=2816, attn_rope_base=10000.0), "bf16", 128, 1024, 1024,
+                dict(temperature=0.8, top_k=50, seed=1234), 0),
+    "config5": (dict(n_layers=96, byte_level=True), "bf16", 2048, 512, 256, dict(), 1000),
+}
