@@ -92,7 +92,7 @@ def test_attention_block_against_reference_kernel_chain(tmp_path, window):
     cfg = synth.base_config(n_layers=1, vocab_size=512, attention_layers=[0], attn_window_sizes=[window] if window else [])
     tens = list(synth.iter_tensors(cfg, seed=13, perturb_ones=0.1))
     # the reference's softmax kernel reduces over min(seq, 256) threads with a halving loop
-    # (training/csrc/elementwise_ops.cu:1017-1021, 1043-1047), which is only complete for a power-of-two count
+    # (training/csrc/elementwise_ops.cu:1021-1024, 1043-1046), which is only complete for a power-of-two count
     B, T = 2, 32
     g = np.random.default_rng(4)
     x = g.standard_normal((B, T, cfg.d_model)).astype(np.float32)
