@@ -6,8 +6,8 @@
 
 Workload (the benchmark definition's throughput sweep): the 96-layer Mamba-3 LM in byte-level
 mode (vocab 259), bf16 weights, fp32 state; 4096 independent sequences sharded contiguously over
-the N ranks with no collective; seeded uniform-random prompts prefilled token by token as the
-reference does; then greedy decode.  One "step" is one decode step of every resident sequence.
+the N ranks with no collective; seeded uniform-random prompts prefilled (untimed) by the batched path
+(chunked SSD scan); then greedy decode.  One "step" is one decode step of every resident sequence.
 Per-rank state for more than `--capacity` sequences does not fit one GPU (fp32 state is
 53.5 MB per sequence), so a rank runs its shard in waves; a step of the job is then one step of
 each wave and the times add.
@@ -201,6 +201,84 @@ def batch1_line(args, peak_gbs):
 CONFIGS = {k: v for k, v in synth.BENCH_CONFIGS.items() if k != "config5"}      # config 5 is the default sweep
 
 
+def scan_compare(nb=64, T=2048, reps=3):
+    """The chunked prefill scan of this library (lumi_k_ssd_prefill) and the reference's own sequential CUDA scan
+    (training/csrc/ssm_scan.cu, built into oracle/_ref/ from the reference's sources) on the same random in_proj
+    rows: nb sequences x T tokens at the base dimensions, CUDA events, best of `reps`.  Returns microseconds per
+    (sequence, head, 64-token chunk) for both and their ratio; the reference entry is None when its library was
+    not built (no reference checkout at build time)."""
+    import ctypes as C
+    import torch
+    import lumi_b200
+    H, P, N, G = 64, 32, 64, 8
+    DI, BC = H * P, G * N
+    R = 2 * DI + 2 * BC + 3 * H + H * N // 2
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    proj = torch.randn((nb * T, R), generator=gen, device="cuda", dtype=torch.float32)
+    one = lambda n: 1 + 0.1 * torch.randn(n, generator=gen, device="cuda")
+    bg, cg, bb, cb, dsk = one(BC), one(BC), one(BC), one(BC), one(H)
+    dtb = -4 + 3 * torch.rand(H, generator=gen, device="cuda")
+    h_init = 0.01 * torch.randn((H, N), generator=gen, device="cuda")
+    units = nb * H * ((T + 63) // 64)
+
+    def fresh_state():
+        return (h_init[None, :, None, :].expand(nb, H, P, N).contiguous(), torch.zeros((nb, H, P), device="cuda"),
+                torch.zeros((nb, H, N), device="cuda"), torch.zeros((nb, H, N // 2), device="cuda"))
+    yhi = torch.empty((nb * T, DI), dtype=torch.bfloat16, device="cuda")
+    ylo = torch.empty_like(yhi)
+    scratch = torch.empty(2 * nb * T, dtype=torch.float32, device="cuda")
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ours = None
+    for _ in range(reps + 1):
+        h, xp, bp, cum = fresh_state()
+        torch.cuda.synchronize()
+        ev0.record()
+        lumi_b200.api.check(lumi_b200.lib().lumi_k_ssd_prefill(
+            proj.data_ptr(), R, bg.data_ptr(), cg.data_ptr(), bb.data_ptr(), cb.data_ptr(), dsk.data_ptr(), dtb.data_ptr(),
+            h.data_ptr(), xp.data_ptr(), bp.data_ptr(), cum.data_ptr(), yhi.data_ptr(), ylo.data_ptr(), scratch.data_ptr(),
+            nb, T, H, G, torch.cuda.current_stream().cuda_stream))
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1)
+        ours = ms if ours is None else min(ours, ms)
+    out = {"sequences": nb, "tokens": T, "units": units, "ours_ms": ours, "ours_us_per_unit": ours * 1e3 / units}
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "libref_ssm_scan.so")
+    if not os.path.exists(ref_path):
+        out["reference_us_per_unit"] = None
+        return out
+    ref = C.CDLL(ref_path)
+    ref.ssm_scan_fwd_gpu.argtypes = [C.c_void_p] * 13 + [C.c_int] * 6
+    # the reference kernel's inputs, prepared as its trainer does before the scan (native_trainer.rs:222-259); untimed
+    pr = proj.view(nb, T, R)
+    x_in = torch.nn.functional.silu(pr[..., :DI]).contiguous()
+    z_in = pr[..., DI:2 * DI].contiguous()
+    bproj, cproj = pr[..., 2 * DI:2 * DI + BC], pr[..., 2 * DI + BC:2 * DI + 2 * BC]
+    bn = (bproj * torch.rsqrt((bproj ** 2).mean(-1, keepdim=True) + 1e-5) * bg + bb).contiguous()
+    cn = (cproj * torch.rsqrt((cproj ** 2).mean(-1, keepdim=True) + 1e-5) * cg + cb).contiguous()
+    o = 2 * DI + 2 * BC
+    dt_raw = pr[..., o:o + H].contiguous()
+    lam = torch.sigmoid(pr[..., o + H:o + 2 * H]).contiguous()
+    a_vals = torch.clamp(-torch.nn.functional.softplus(pr[..., o + 2 * H:o + 3 * H]), -1e6, -1e-4).contiguous()
+    theta = pr[..., o + 3 * H:].contiguous()
+    y = torch.empty((nb, T, DI), device="cuda")
+    yg = torch.empty_like(y)
+    theirs = None
+    for _ in range(2):
+        torch.cuda.synchronize()
+        ev0.record()
+        ref.ssm_scan_fwd_gpu(x_in.data_ptr(), dt_raw.data_ptr(), bn.data_ptr(), cn.data_ptr(), dsk.data_ptr(), dtb.data_ptr(),
+                             h_init.data_ptr(), lam.data_ptr(), theta.data_ptr(), a_vals.data_ptr(), z_in.data_ptr(), y.data_ptr(),
+                             yg.data_ptr(), nb, T, H, P, N, G)       # launches on the legacy default stream, as the reference does
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1)
+        theirs = ms if theirs is None else min(theirs, ms)
+    got = (yhi.float() + ylo.float()).view(nb, T, DI)
+    out.update({"reference_ms": theirs, "reference_us_per_unit": theirs * 1e3 / units, "speedup": theirs / ours,
+                "max_rel_diff": float((got - yg).abs().max() / yg.abs().max())})
+    return out
+
+
 def run_named_config(args, rank, local_rank, world):
     """The other benchmark configurations, one GPU, through Session.generate (prefill + decode timed
     by CUDA events inside the library).  Sequences would shard over ranks exactly as in the sweep."""
@@ -224,6 +302,12 @@ def run_named_config(args, rank, local_rank, world):
     toks, lens, _, st = sess.generate(prompts, n_new + 1, ignore_eos=True, **samp)
     wall = time.perf_counter() - t0
     clocks = sampler.stop()
+    sess.close(); model.close()
+    scan = None
+    if args.workload == "config3":           # the chunked scan alone, beside the reference's sequential CUDA scan
+        import torch
+        torch.cuda.set_device(local_rank)
+        scan = scan_compare()
     S = state_bytes_per_seq_step(cfg)
     kv = 0
     if info["n_attention"]:
@@ -245,6 +329,7 @@ def run_named_config(args, rank, local_rank, world):
         "roofline": {"bound": "hbm", "kernel": "whole decode step", "achieved": gbs, "peak": peak_gbs, "unit": "GB/s", "frac": gbs / peak_gbs,
                      "traffic": None, "peak_source": peak_src, "bytes_per_step": step_bytes},
         "clocks": clocks,
+        "prefill_scan": scan if scan is not None else None,
     }), flush=True)
 
 
@@ -352,7 +437,7 @@ def run_ours(args, rank, local_rank, world):
                        "resident_sequences": cap, "weights": "bf16", "state": "fp32",
                        "activations_into_gemm": "bf16 hi+lo split" if args.split else "bf16",
                        "l2": "inputs larger than L2: each step streams %.1f GB of state" % (cap * info["n_mamba"] * S / 1e9),
-                       "prefill": "token by token through the decode step (untimed)"},
+                       "prefill": "untimed; 512-token bf16 prompts take the batched path (chunked SSD scan + tensor-core GEMMs over all prompt tokens)"},
             "gpu_launches": int(lsum),
             "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "roofline": {"bound": "hbm", "kernel": "ssm_step_kernel<32,64>", "achieved": ssm_gbs, "peak": peak_gbs, "unit": "GB/s",
@@ -398,13 +483,20 @@ def main():
     ap.add_argument("--no-batch1", action="store_true")
     ap.add_argument("--only-batch1", action="store_true", help="run just the batch-1 figure (profiling)")
     ap.add_argument("--b1-layers", type=int, default=48)
-    ap.add_argument("--workload", default="sweep", choices=["sweep"] + sorted(CONFIGS))
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "scan"] + sorted(CONFIGS))
+    ap.add_argument("--scan-seqs", type=int, default=64, help="--workload scan: sequences")
+    ap.add_argument("--scan-tokens", type=int, default=2048, help="--workload scan: tokens per sequence")
     ap.add_argument("--steps-override", type=int, default=0, help="decode tokens for --workload configN (0 = the configuration's own)")
     args = ap.parse_args()
     rank, local_rank, world = shard.env_rank_world()
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE {world}")
-    if args.workload != "sweep":
+    if args.workload == "scan":       # the chunked prefill scan alone beside the reference's CUDA scan (profiling, small cases)
+        if rank == 0:
+            import torch
+            torch.cuda.set_device(local_rank)
+            print(json.dumps({"prefill_scan": scan_compare(args.scan_seqs, args.scan_tokens)}), flush=True)
+    elif args.workload != "sweep":
         run_named_config(args, rank, local_rank, world)
     elif args.only_batch1:
         print(json.dumps({"batch1": batch1_line(args, measured_peak_gbs()[0])}), flush=True)

@@ -206,6 +206,15 @@ int32_t lumi_session_load_state(lumi_session* s, int32_t slot, const void* host_
 int32_t lumi_k_gemm_bf16_tcgen05(uint64_t a_hi, uint64_t a_lo, uint64_t w, uint64_t d, int32_t M, int32_t N,
                                  int32_t K, int32_t ldd, int32_t accumulate, uint64_t stream);
 
+/* Failure-path test hook for the bounded device-side waits (no counterpart in the reference, whose kernels never wait
+ * on one another): runs the same GEMM with activations a_hi only, every device-side wait limited to wait_limit_ns, and
+ * the producer stopping before work unit `skip_unit` (units are 128-row x tile-width output tiles in launch order;
+ * -1 = none), so that the waits of the consumers run out.  status_word: a zeroed device int32.  Returns LUMI_E_TIMEOUT
+ * when a wait gave up — the kernel has then returned cleanly (copies drained, tensor memory freed) and further calls
+ * work — or LUMI_OK when nothing was skipped.  Synchronises the default stream. */
+int32_t lumi_debug_gemm_wait_timeout(uint64_t a_hi, uint64_t w, uint64_t d, int32_t M, int32_t N, int32_t K,
+                                     uint64_t wait_limit_ns, int32_t skip_unit, uint64_t status_word);
+
 /* Same contraction on CUDA cores with fp32 activations: D[M][N] = A[M][K] * W[N][K]^T (+ residual R).
  * w_dtype LUMI_DTYPE_*.  norm_gamma != 0 applies RMSNorm(gamma) to each row of A first. */
 int32_t lumi_k_gemv(uint64_t a_f32, uint64_t w, int32_t w_dtype, uint64_t d, uint64_t residual,
@@ -217,6 +226,17 @@ int32_t lumi_k_gemv(uint64_t a_f32, uint64_t w, int32_t w_dtype, uint64_t d, uin
 int32_t lumi_k_ssm_step(uint64_t proj, int32_t ldp, uint64_t b_gamma, uint64_t c_gamma, uint64_t b_bias, uint64_t c_bias,
                         uint64_t d_skip, uint64_t dt_bias, uint64_t h, uint64_t x_prev, uint64_t b_prev, uint64_t cum_angle,
                         uint64_t y, int32_t B, int32_t H, int32_t P, int32_t N, int32_t G, uint64_t stream);
+
+/* The chunked prefill scan alone (chunk length 64; head_dim 32, d_state 64): the same recurrence as lumi_k_ssm_step
+ * over `ts` consecutive tokens of each of `nb` sequences at once — what replaces `ts` sequential forward_step calls
+ * (inference/src/main.rs:121-125) and what the reference's sequential CUDA scan computes for its trainer
+ * (training/csrc/ssm_scan.cu:71-229, host entry :773).  proj[nb * ts][ldp]: in_proj output rows, row = sequence * ts +
+ * token.  State arrays as for lumi_k_ssm_step (slot = sequence), updated in place to the state after the last token.
+ * y_hi / y_lo [nb * ts][H * 32]: the gated output as bf16 hi + lo halves (y_lo may be 0).  scratch: 2 * nb * ts floats. */
+int32_t lumi_k_ssd_prefill(uint64_t proj, int32_t ldp, uint64_t b_gamma, uint64_t c_gamma, uint64_t b_bias, uint64_t c_bias,
+                           uint64_t d_skip, uint64_t dt_bias, uint64_t h, uint64_t x_prev, uint64_t b_prev, uint64_t cum_angle,
+                           uint64_t y_hi, uint64_t y_lo, uint64_t scratch, int32_t nb, int32_t ts, int32_t H, int32_t G,
+                           uint64_t stream);
 
 /* One Mamba block (RMSNorm -> in_proj -> state step -> out_proj + residual, inference/src/model.rs:296-375
  * in arithmetic) WITHOUT any allocation.  This entry point has no counterpart in the reference.

@@ -1003,6 +1003,7 @@ int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head, float
                 a.rb = s->pf_rb; a.rc = s->pf_rc;
                 a.yhi = s->pf_hi; a.ylo = lo;
                 a.H = c.n_heads; a.G = c.n_groups; a.ts = ts; a.nb = nb; a.b0 = b0; a.eps = c.eps;
+                a.status = &s->ctl->status;
                 LUMI_CUDA(launch_prefill_scan(a, s->stream));
                 GemmArgs g2{s->pf_hi, lo, (const __nv_bfloat16*)L.m.out_proj.p, s->pf_x, D, M, D, DI, 1, &s->ctl->status};
                 LUMI_TRY(launch_gemm_tcgen05(g2, s->stream));
@@ -1477,6 +1478,24 @@ extern "C" int32_t lumi_k_gemm_bf16_tcgen05(uint64_t a_hi, uint64_t a_lo, uint64
     return launch_gemm_tcgen05(g, (cudaStream_t)stream);
 }
 
+// Failure-path test hook: the persistent tcgen05 GEMM with a caller-chosen wait limit and a work unit whose operands
+// the producer never requests.  The consumers' bounded waits run out, the kernel records STATUS_TIMEOUT in
+// *status_word (device int32, zeroed by the caller), drains what it issued, frees its TMEM and returns; the call
+// then answers LUMI_E_TIMEOUT.  Nothing faults and the context stays usable.
+extern "C" int32_t lumi_debug_gemm_wait_timeout(uint64_t a_hi, uint64_t w, uint64_t d, int32_t M, int32_t N, int32_t K, uint64_t wait_limit_ns,
+                                                int32_t skip_unit, uint64_t status_word) {
+    if (!a_hi || !w || !d || !status_word) return fail(LUMI_E_INVALID, "null device pointer");
+    GemmArgs g{(const __nv_bfloat16*)a_hi, nullptr, (const __nv_bfloat16*)w, (float*)d, N, M, N, K, 0, (int32_t*)status_word};
+    g.wait_limit_ns = wait_limit_ns;
+    g.debug_skip_unit = skip_unit;
+    LUMI_TRY(launch_gemm_tcgen05(g, nullptr));
+    LUMI_CUDA(cudaStreamSynchronize(nullptr));
+    int32_t st = 0;
+    LUMI_CUDA(cudaMemcpy(&st, (const void*)status_word, sizeof(st), cudaMemcpyDeviceToHost));
+    if (st & STATUS_TIMEOUT) return fail(LUMI_E_TIMEOUT, "a bounded device-side wait expired in the tensor-core GEMM (limit %llu ns)", (unsigned long long)wait_limit_ns);
+    return LUMI_OK;
+}
+
 extern "C" int32_t lumi_k_gemv(uint64_t a_f32, uint64_t w, int32_t w_dtype, uint64_t d, uint64_t residual, uint64_t norm_gamma,
                                int32_t M, int32_t N, int32_t K, uint64_t stream) {
     if (!a_f32 || !w || !d || M <= 0 || N <= 0 || K <= 0) return fail(LUMI_E_INVALID, "bad argument to lumi_k_gemv");
@@ -1500,5 +1519,25 @@ extern "C" int32_t lumi_k_ssm_step(uint64_t proj, int32_t ldp, uint64_t b_gamma,
     a.y32 = (float*)y;
     a.B = B; a.H = H; a.P = P; a.N = N; a.G = G; a.eps = 1e-5f;
     LUMI_CUDA(launch_ssm_step(a, (cudaStream_t)stream));
+    return LUMI_OK;
+}
+
+extern "C" int32_t lumi_k_ssd_prefill(uint64_t proj, int32_t ldp, uint64_t b_gamma, uint64_t c_gamma, uint64_t b_bias, uint64_t c_bias,
+                                      uint64_t d_skip, uint64_t dt_bias, uint64_t h, uint64_t x_prev, uint64_t b_prev, uint64_t cum_angle,
+                                      uint64_t y_hi, uint64_t y_lo, uint64_t scratch, int32_t nb, int32_t ts, int32_t H, int32_t G,
+                                      uint64_t stream) {
+    if (!proj || !b_gamma || !c_gamma || !b_bias || !c_bias || !d_skip || !dt_bias || !h || !x_prev || !b_prev || !cum_angle || !y_hi || !scratch)
+        return fail(LUMI_E_INVALID, "null device pointer to lumi_k_ssd_prefill");
+    if (nb <= 0 || ts <= 0 || H <= 0 || G <= 0 || (H % G) || (H % 4) || (ldp % 4) || ldp < 2 * H * 32 + 2 * G * 64 + 3 * H + H * 32)
+        return fail(LUMI_E_UNSUPPORTED, "unsupported shape for lumi_k_ssd_prefill (head_dim 32, d_state 64, n_heads %% 4 == 0)");
+    PrefillArgs a{};
+    a.proj = (const float*)proj; a.ldp = ldp;
+    a.bg = (const float*)b_gamma; a.cg = (const float*)c_gamma; a.bb = (const float*)b_bias; a.cb = (const float*)c_bias;
+    a.dskip = (const float*)d_skip; a.dtb = (const float*)dt_bias;
+    a.h = (float*)h; a.xprev = (float*)x_prev; a.bprev = (float*)b_prev; a.cum = (float*)cum_angle;
+    a.rb = (float*)scratch; a.rc = (float*)scratch + (size_t)nb * ts;
+    a.yhi = (__nv_bfloat16*)y_hi; a.ylo = (__nv_bfloat16*)y_lo;
+    a.H = H; a.G = G; a.ts = ts; a.nb = nb; a.b0 = 0; a.eps = 1e-5f;
+    LUMI_CUDA(launch_prefill_scan(a, (cudaStream_t)stream));
     return LUMI_OK;
 }

@@ -20,6 +20,8 @@
 
 namespace lumi {
 
+int32_t gemm_tcgen05_init();
+
 namespace {
 
 constexpr int BM = 128;
@@ -53,12 +55,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: false when the limit expired.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+        if (globaltimer_ns() - t0 > limit_ns) return false;
     }
 }
 
@@ -264,7 +266,8 @@ template <int BN, bool SPLIT>
 __global__ void __launch_bounds__(192, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
                        const __grid_constant__ CUtensorMap map_w, float* D, int ldd, int M, int N, int K,
-                       int accumulate, int tiles_m, int ntiles, int splits, int32_t* tile_counters, float* scratch, int32_t* status) {
+                       int accumulate, int tiles_m, int ntiles, int splits, int32_t* tile_counters, float* scratch, int32_t* status,
+                       uint64_t wait_ns, int skip_unit) {
     using T = Tile<BN, SPLIT, 1>;
     constexpr int S = T::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -306,13 +309,14 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
         if (lane == 0) {
             uint32_t kbg = 0;                    // k-blocks issued so far, over all tiles of this CTA
             for (int u = blockIdx.x; u < ntiles * splits && !timed_out; u += gridDim.x) {
+                if (u == skip_unit) break;       // test hook: this unit's operands never arrive, so the waits below it run out
                 const int t = u / splits, sp = u - t * splits;
                 const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
                 const int kb0 = sp * num_kb / splits, kb1 = (sp + 1) * num_kb / splits;
                 for (int kb = kb0; kb < kb1; ++kb, ++kbg) {
                     const int s = kbg % S;
                     const uint32_t ph = (kbg / S) & 1u;
-                    if (!mbar_wait(&empty_bar[s], ph ^ 1u)) { timed_out = true; break; }
+                    if (!mbar_wait(&empty_bar[s], ph ^ 1u, wait_ns)) { timed_out = true; break; }
                     uint8_t* st = base + s * T::STAGE;
                     mbar_expect_tx(&full_bar[s], (uint32_t)T::STAGE);
                     tma_load_2d(st, &map_ahi, &full_bar[s], kb * BK, m0);
@@ -322,7 +326,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
             }
             if (timed_out) {
                 // drain: wait (bounded) for the copies this thread issued and nobody may consume
-                for (uint32_t k = kbg > (uint32_t)S ? kbg - S : 0; k < kbg; ++k) mbar_wait(&full_bar[k % S], (k / S) & 1u);
+                for (uint32_t k = kbg > (uint32_t)S ? kbg - S : 0; k < kbg; ++k) mbar_wait(&full_bar[k % S], (k / S) & 1u, wait_ns);
             }
         }
     } else if (warp == 1) {
@@ -331,7 +335,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
             uint32_t kbg = 0, it = 0;
             for (int u = blockIdx.x; u < ntiles * splits && !timed_out; u += gridDim.x, ++it) {
                 const uint32_t as = it & 1u, aph = (it >> 1) & 1u;
-                if (!mbar_wait(&tmem_empty[as], aph ^ 1u)) { timed_out = true; break; }     // the epilogue has drained this accumulator
+                if (!mbar_wait(&tmem_empty[as], aph ^ 1u, wait_ns)) { timed_out = true; break; }     // the epilogue has drained this accumulator
                 tc_fence_after();
                 const uint32_t acc = tmem_base + as * ACC_COLS;
                 const int sp = u % splits;
@@ -339,7 +343,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
                 for (int kb = kb0; kb < kb1; ++kb, ++kbg) {
                     const int s = kbg % S;
                     const uint32_t ph = (kbg / S) & 1u;
-                    if (!mbar_wait(&full_bar[s], ph)) { timed_out = true; break; }
+                    if (!mbar_wait(&full_bar[s], ph, wait_ns)) { timed_out = true; break; }
                     tc_fence_after();
                     const uint32_t a_hi = smem_u32(base + s * T::STAGE);
                     const uint32_t b_addr = a_hi + T::A_BYTES * (SPLIT ? 2 : 1);
@@ -358,7 +362,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
             }
             if (timed_out) {                     // let every MMA issued so far finish before TMEM is freed
                 umma_commit(drain_bar);
-                mbar_wait(drain_bar, 0);         // bounded
+                mbar_wait(drain_bar, 0, wait_ns);         // bounded
             }
         }
     } else {
@@ -369,7 +373,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
             const uint32_t as = it & 1u, aph = (it >> 1) & 1u;
             const int t = u / splits, sp = u - t * splits;
             const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
-            if (!mbar_wait(&tmem_full[as], aph)) timed_out = true;
+            if (!mbar_wait(&tmem_full[as], aph, wait_ns)) timed_out = true;
             timed_out = __any_sync(0xffffffffu, timed_out);     // tcgen05.ld below is warp-collective
             if (timed_out) break;
             tc_fence_after();
@@ -532,12 +536,29 @@ int32_t launch_persistent(const GemmArgs& a, int splits, cudaStream_t st) {
     const int units = ntiles * splits;
     const int grid = units < sm_count_gemm() ? units : sm_count_gemm();
     kern<<<grid, 192, T::SMEM, st>>>(mh, ml, mw, a.d, a.ldd, a.M, a.N, a.K, a.accumulate, tiles_m, ntiles, splits, a.tile_counters,
-                                     a.scratch, a.status_word);
+                                     a.scratch, a.status_word, a.wait_limit_ns ? a.wait_limit_ns : kWaitLimitNs, a.debug_skip_unit);
     LUMI_CUDA(cudaGetLastError());
     return LUMI_OK;
 }
 
 }  // namespace
+
+// Row-major fp32 matrix [rows][cols] (row pitch in bytes) as a 2-D tensor map with a dense box_rows x box_cols box,
+// no swizzle, zeros for out-of-range elements.  Used by the chunked prefill scan to stage projection rows.
+int32_t make_f32_map_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
+                        uint32_t box_rows) {
+    LUMI_TRY(gemm_tcgen05_init());
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(LUMI_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (fp32 %llu x %llu)", (int)r, (unsigned long long)rows, (unsigned long long)cols);
+    return LUMI_OK;
+}
 
 int32_t gemm_tcgen05_init() {
     if (g_encode != nullptr) return LUMI_OK;

@@ -275,6 +275,8 @@ struct GemmArgs {
     int n_counters = 0;
     float* scratch = nullptr;           // partial tiles of the splits
     size_t scratch_floats = 0;
+    uint64_t wait_limit_ns = 0;         // limit of every device-side wait (0 = the default, 0.5 s)
+    int debug_skip_unit = -1;           // test hook: the producer stops before this work unit, so the consumers' waits run out
 };
 int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st);   // returns LUMI_* status
 int32_t gemm_tcgen05_init();                                        // resolves the driver entry point
@@ -315,6 +317,7 @@ struct PrefillArgs {
     __nv_bfloat16 *yhi, *ylo;                // [nb * ts][d_inner] gated output halves
     int H, G, ts, nb, b0;                    // heads, groups, tokens per sequence in this launch, sequences, first slot
     float eps;
+    int32_t* status = nullptr;               // device word that receives STATUS_TIMEOUT if the bounded wait gives up
 };
 bool prefill_ssd_supported(const Config& c);
 cudaError_t launch_prefill_embed(const void* emb, int dtype, const uint32_t* prompt, float* x, int D, int vocab, int rows, int ts,

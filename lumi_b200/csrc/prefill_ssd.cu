@@ -1,4 +1,5 @@
-// Chunked (SSD-style) prefill of the Mamba-3 trapezoidal recurrence, chunk length 64.
+// Chunked (SSD-style) prefill of the Mamba-3 trapezoidal recurrence, chunk length 64, with the chunk's
+// projection rows staged by TMA one chunk ahead and the chunk products on tensor cores.
 //
 // The reference prefills token by token (inference/src/main.rs:121-125) and its only NVIDIA scan
 // is sequential in time (training/csrc/ssm_scan.cu:137-227; SSD_FWD_CHUNK there is dead code).
@@ -9,43 +10,143 @@
 // an ordinary decayed linear recurrence, so inside a chunk starting at t0 (l_i = sum of log a up to i)
 //     y_i = e^{l_i} (S^_in C~_i) + sum_{j<i} e^{l_i - l_j} kap_j (C~_i . B~_j) x_j + lam_i (C~_i . B~_i) x_i + D x_i
 //     S^_out = e^{l_last} S^_in + sum_j e^{l_last - l_j} kap_j x_j (x) B~_j
-// — three small matrix products per (sequence, head, chunk).  The last token of a launch uses
-// kap = lam, which makes S^ equal the true S: every launch ends with exactly the state the decode
-// kernel expects (h, x_prev, B~_prev, cum_angle), and the next launch rebuilds S^ from it.
-// DD-RoPE angles are a prefix sum over the chunk taken mod 2 pi at the end (the reference reduces
-// mod 2 pi every step: same angle, rounding-level differences; the stored angle may differ from the
-// sequential one by a multiple of 2 pi).
+// — four small matrix products per (sequence, head, chunk):
+//     G = C~ B~^T (64x64x64),  Y1 = W X with W = mask/decay(G) (64x64x32),  Y2 = C~ S^_in^T (64x64x32),
+//     S^_out += (w x)^T B~ (32x64x64).
+// The last token of a launch uses kap = lam, which makes S^ equal the true S: every launch ends with exactly
+// the state the decode kernel expects (h, x_prev, B~_prev, cum_angle), and the next launch rebuilds S^ from it.
+// DD-RoPE angles are a prefix sum over the chunk taken mod 2 pi (the reference reduces mod 2 pi every step:
+// same angle, rounding-level differences; the stored angle may differ from the sequential one by a multiple
+// of 2 pi).
 //
-// One CTA per (head, sequence); fp32 arithmetic on CUDA cores with shared-memory tiles.
+// One CTA of four warps per (head, sequence), two CTAs per SM.
+//   * Staging: the chunk's x, z, theta (64 x 32 fp32 each) and the group's raw B, C (64 x 64 fp32 each) arrive by
+//     five cp.async.bulk.tensor copies on one mbarrier (bounded wait); the copies for chunk c+1 are issued as
+//     soon as chunk c's raw values have been consumed, i.e. before chunk c's matrix products, and the per-token
+//     scalars (dt, lambda, A, BCNorm scales) of chunk c+1 are requested into registers at the same point.
+//   * Arithmetic: every operand is an fp32 value split into bf16 hi + lo; a product is three
+//     mma.sync.m16n8k16 (hi*hi + hi*lo + lo*hi, fp32 accumulate), which keeps ~16 mantissa bits per factor.
+//     Warp w owns tokens 16w..16w+15: its C~ rows stay in registers as A fragments, G's accumulators are masked,
+//     decayed and re-used in place as the A fragments of W X (no trip through shared memory), and the state S^
+//     lives in accumulator registers across the chunks of a launch (warp w: 16 rows of P x 32 columns of N).
+//   * The pointwise part (softplus / sigmoid / tanh / SiLU / sin / cos) uses the fast hardware forms here: their
+//     error (~1e-6) is far below the operand split's (1.5e-5) — the decode step keeps the exact forms.
 #include "internal.h"
 
+#include <cuda.h>
+
 namespace lumi {
+
+// defined in gemm_tcgen05.cu: cuTensorMapEncodeTiled for a row-major fp32 matrix [rows][cols], no swizzle
+int32_t make_f32_map_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
+                        uint32_t box_rows);
 
 namespace {
 
 constexpr int LCH = 64;          // chunk length
-constexpr int LDS_ = 68;         // row stride of the shared tiles (floats): 16-byte aligned, conflict-free row walks
+constexpr int TSB = 72;          // row stride (bf16 elements) of the operand tiles: 144 bytes, conflict-free fragment loads
+constexpr uint64_t kScanWaitLimitNs = 500ull * 1000 * 1000;
 
 __device__ __forceinline__ float sigmoid_ref(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
 __device__ __forceinline__ float softplus_ref(float x) { return logf(__fadd_rn(expf(x), 1.0f)); }
-__device__ __forceinline__ float silu_ref(float x) { return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))); }
-__device__ __forceinline__ float dot4(const float4& a, const float4& b) { return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, a.w * b.w))); }
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float tanh_fast(float x) {
+    // 1 - 2 / (e^{2x} + 1): absolute error ~1e-7; the argument is clamped so e^{2x} stays finite
+    const float xc = fminf(fmaxf(x, -15.f), 15.f);
+    return 1.0f - __fdividef(2.0f, __expf(2.0f * xc) + 1.0f);
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit expired.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (globaltimer_ns() - t0 > limit_ns) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// D (16x8, fp32) += A (16x16, bf16, row) * B (16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// (a_hi + a_lo)(b_hi + b_lo) without the lo*lo term
+__device__ __forceinline__ void mma3(float (&d)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4], uint32_t bh0, uint32_t bh1,
+                                     uint32_t bl0, uint32_t bl1) {
+    mma_bf16(d, ah, bh0, bh1);
+    mma_bf16(d, ah, bl0, bl1);
+    mma_bf16(d, al, bh0, bh1);
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+// two fp32 values -> bf16x2 hi word and bf16x2 lo word (first value in the low half)
+__device__ __forceinline__ void split2(float v0, float v1, uint32_t& hi, uint32_t& lo) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+    const float2 hf = __bfloat1622float2(h);
+    __nv_bfloat162 l = __floats2bfloat162_rn(v0 - hf.x, v1 - hf.y);
+    hi = *reinterpret_cast<uint32_t*>(&h);
+    lo = *reinterpret_cast<uint32_t*>(&l);
+}
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
 __device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
     hi = __float2bfloat16_rn(v);
     lo = __float2bfloat16_rn(v - __bfloat162float(hi));
 }
 
 struct PfSmem {
-    float Bt[LCH][LDS_];       // rotated B~ of the chunk              [token][n]
-    float Ct[LCH][LDS_];       // rotated C~                           [token][n]
-    float Wm[LCH][LDS_];       // masked, decayed (C~ B~^T)            [i][j]
-    float Xt[32][LDS_];        // silu(x) transposed                   [p][token]
-    float Sh[32][LDS_];        // augmented state S^                   [p][n]
-    float Gt[LCH][33];         // silu(z) gate                         [token][p]
-    float seg[9][32];          // angle prefix sums of the 8 token segments
-    float ell[LCH], lam[LCH + 1], kap[LCH], dtp[LCH], wj[LCH];
+    // destinations of the bulk tensor copies (dense boxes); theta becomes the angle and z the gate in place
+    float rx[LCH][32];
+    float rth[LCH][32];
+    float rB[LCH][64];
+    float rC[LCH][64];
+    float rz[2][LCH][32];
+    // bf16 operand tiles, hi and lo planes
+    __nv_bfloat16 Bt[2][LCH][TSB];     // rotated B~            [token][n]
+    __nv_bfloat16 Xt[2][32][TSB];      // silu(x) transposed    [p][token]
+    __nv_bfloat16 St[2][32][TSB];      // augmented state S^    [p][n]
+    float ell[LCH], eli[LCH], lam[LCH + 4], kap[LCH], wj[LCH], dtp[LCH], rbs[LCH], rcs[LCH];
+    float seg[5][32];                  // angle prefix sums at the boundaries of the four 16-token segments
     float cum[32];
+    float gam[4][64];                  // this group's BCNorm weights: b gamma, b bias, c gamma, c bias
+    unsigned long long bar;
+    int ok;
 };
+
+constexpr uint32_t kChunkTxBytes = 3 * LCH * 32 * 4 + 2 * LCH * 64 * 4;
 
 // row r = b * ts + t  of the super-chunk; token ids come from prompt[(t_abs) * batch_total + b_abs]
 template <typename WT>
@@ -86,52 +187,102 @@ __global__ void gather_last_kernel(const float* __restrict__ xr, float* __restri
     for (int k = threadIdx.x; k < D; k += blockDim.x) x[(size_t)(b0 + b) * D + k] = xr[((size_t)b * ts + ts - 1) * D + k];
 }
 
-__global__ void __launch_bounds__(256, 2) ssd_prefill_kernel(PrefillArgs a) {
+__global__ void __launch_bounds__(128, 2)
+ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_constant__ CUtensorMap map64, PrefillArgs a) {
     constexpr int P = 32, N = 64, HN = 32;
     extern __shared__ uint8_t pf_raw[];
-    PfSmem& sm = *reinterpret_cast<PfSmem*>((reinterpret_cast<uintptr_t>(pf_raw) + 15) & ~(uintptr_t)15);
-    const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
+    PfSmem& sm = *reinterpret_cast<PfSmem*>((reinterpret_cast<uintptr_t>(pf_raw) + 1023) & ~(uintptr_t)1023);
+    const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g4 = lane >> 2, t4 = lane & 3;               // mma fragment coordinates: row group, column pair
     const int H = a.H, DI = H * P, BC = a.G * N, ts = a.ts, R = a.ldp;
-    const int g = h / (H / a.G);
+    const int grp = h / (H / a.G);
     const size_t bh = (size_t)(a.b0 + b) * H + h;
     const float* prow0 = a.proj + (size_t)b * ts * R;      // first token row of this sequence
     const int off_b = 2 * DI, off_c = off_b + BC, off_dt = off_c + BC;
     const float PI_F = 3.14159265358979323846f;
-    const float TWO_PI = __fmul_rn(2.0f, PI_F);
+    const float TWO_PI = 6.28318530717958647692f;
+    const float INV_TWO_PI = 0.15915494309189533577f;
     const float dskip = a.dskip[h], dtb = a.dtb[h];
+    uint64_t* bar = reinterpret_cast<uint64_t*>(&sm.bar);
 
-    // incoming state: S (true state of the decode representation); S^ is formed once lam of the first token is known
-    for (int i = tid; i < P * N; i += 256) sm.Sh[i / N][i % N] = a.h[bh * (size_t)(P * N) + i];
+    // a wait that expired in an earlier CTA of this launch: do not start new work
+    if (a.status != nullptr && (*reinterpret_cast<volatile int32_t*>(a.status) & STATUS_TIMEOUT)) return;
+
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     if (tid < HN) sm.cum[tid] = a.cum[bh * HN + tid];
+    if (tid < 64) {
+        const int c = grp * N + tid;
+        sm.gam[0][tid] = a.bg[c]; sm.gam[1][tid] = a.bb[c]; sm.gam[2][tid] = a.cg[c]; sm.gam[3][tid] = a.cb[c];
+    }
     __syncthreads();
 
-    // BCNorm weights of this thread's angle pair (the same for every token)
-    const int kk0 = g * N + 2 * (tid & 31);
-    const float kbg0 = a.bg[kk0], kbg1 = a.bg[kk0 + 1], kbb0 = a.bb[kk0], kbb1 = a.bb[kk0 + 1];
-    const float kcg0 = a.cg[kk0], kcg1 = a.cg[kk0 + 1], kcb0 = a.cb[kk0], kcb1 = a.cb[kk0 + 1];
+    auto issue_chunk = [&](int t0, int zb) {       // one thread: the five box copies of the chunk starting at token t0
+        const int row0 = b * ts + t0;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(kChunkTxBytes) : "memory");
+        tma_load_2d(&sm.rx[0][0], &map32, bar, h * P, row0);
+        tma_load_2d(&sm.rz[zb][0][0], &map32, bar, DI + h * P, row0);
+        tma_load_2d(&sm.rth[0][0], &map32, bar, off_dt + 3 * H + h * HN, row0);
+        tma_load_2d(&sm.rB[0][0], &map64, bar, off_b + grp * N, row0);
+        tma_load_2d(&sm.rC[0][0], &map64, bar, off_c + grp * N, row0);
+    };
+    // per-token scalars of a chunk, requested into registers one chunk ahead (threads 0..63: own token; thread 64:
+    // lambda of the token after the chunk)
+    float n_dt = 0.f, n_lam = 0.f, n_a = 0.f, n_rb = 0.f, n_rc = 0.f;
+    auto request_scalars = [&](int t0) {
+        if (tid < LCH && t0 + tid < ts) {
+            const float* pr = prow0 + (size_t)(t0 + tid) * R;
+            const size_t row = (size_t)b * ts + t0 + tid;
+            n_dt = pr[off_dt + h]; n_lam = pr[off_dt + H + h]; n_a = pr[off_dt + 2 * H + h];
+            n_rb = a.rb[row]; n_rc = a.rc[row];
+        } else if (tid == LCH && t0 + LCH < ts) {
+            n_lam = prow0[(size_t)(t0 + LCH) * R + off_dt + H + h];
+        }
+    };
+    if (tid == 0) issue_chunk(0, 0);
+    request_scalars(0);
 
-    int last_valid = 0;
-    for (int t0 = 0; t0 < ts; t0 += LCH) {
+    // state S^ of this warp: rows p0 + {g4, g4 + 8}, columns n0 + 8 nt + 2 t4 + {0, 1}
+    const int p0 = 16 * (warp & 1), n0 = 32 * (warp >> 1);
+    float S[4][4];
+    {
+        const float* hp = a.h + bh * (size_t)(P * N);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const float2 v0 = *reinterpret_cast<const float2*>(hp + (p0 + g4) * N + n0 + 8 * nt + 2 * t4);
+            const float2 v1 = *reinterpret_cast<const float2*>(hp + (p0 + g4 + 8) * N + n0 + 8 * nt + 2 * t4);
+            S[nt][0] = v0.x; S[nt][1] = v0.y; S[nt][2] = v1.x; S[nt][3] = v1.y;
+        }
+    }
+
+    uint32_t phase = 0;
+    bool failed = false;
+    int chunk = 0;
+    for (int t0 = 0; t0 < ts; t0 += LCH, ++chunk) {
         const int nv = min(LCH, ts - t0);                  // valid tokens in this chunk
-        last_valid = nv - 1;
-        // ---- 1. per-token scalars (model.rs:307, 314-317)
+        const int zb = chunk & 1;
+        const bool last_chunk = t0 + LCH >= ts;
+        // ---- 0. the chunk's raw rows have landed (one thread waits, bounded; everyone follows its verdict)
+        if (tid == 0) sm.ok = mbar_wait(bar, phase, kScanWaitLimitNs) ? 1 : 0;
+        // ---- 1. per-token scalars (model.rs:307, 314-317) from the registers requested a chunk earlier
         if (tid < LCH) {
             float dtpv = 0.f, gl = 0.f, lm = 0.f;
             if (tid < nv) {
-                const float* pr = prow0 + (size_t)(t0 + tid) * R;
-                dtpv = softplus_ref(__fadd_rn(pr[off_dt + h], dtb));
-                float av = -softplus_ref(pr[off_dt + 2 * H + h]);
+                dtpv = softplus_ref(__fadd_rn(n_dt, dtb));
+                float av = -softplus_ref(n_a);
                 av = fminf(fmaxf(av, -1e6f), -1e-4f);
                 gl = __fmul_rn(av, dtpv);                 // log a_t
-                lm = sigmoid_ref(pr[off_dt + H + h]);
+                lm = sigmoid_ref(n_lam);
             }
             sm.dtp[tid] = dtpv; sm.ell[tid] = gl; sm.lam[tid] = lm;
+            sm.rbs[tid] = n_rb; sm.rcs[tid] = n_rc;
         }
-        if (tid == LCH) {
-            // lam of the token after this chunk; < 0 marks "none in this launch"
-            sm.lam[LCH] = (t0 + LCH < ts) ? sigmoid_ref(prow0[(size_t)(t0 + LCH) * R + off_dt + H + h]) : -1.0f;
-        }
+        if (tid == LCH) sm.lam[LCH] = (t0 + LCH < ts) ? sigmoid_ref(n_lam) : -1.0f;      // < 0: no next token in this launch
         __syncthreads();
+        if (!sm.ok) { failed = true; break; }
+        phase ^= 1;
         if (tid < 32) {                                    // inclusive prefix of log a over the chunk
             float v0 = sm.ell[2 * lane], v1 = sm.ell[2 * lane + 1];
             float s = v0 + v1, incl = s;
@@ -150,208 +301,294 @@ __global__ void __launch_bounds__(256, 2) ssd_prefill_kernel(PrefillArgs a) {
                 k = (ln < 0.f) ? sm.lam[i] : __fadd_rn(sm.lam[i], __fsub_rn(1.0f, ln));
             }
             sm.kap[i] = k;
-            sm.wj[i] = expf(sm.ell[LCH - 1] - sm.ell[i]) * k;
+            sm.wj[i] = __expf(sm.ell[LCH - 1] - sm.ell[i]) * k;
+            sm.eli[i] = __expf(sm.ell[i]);
         }
-        if (t0 == 0) {
+        if (chunk == 0) {
             // S^_in = S + (1 - lam_first) x_prev (x) B~_prev   (prev_bx of the decode state, model.rs:359)
             const float oml = __fadd_rn(__fmul_rn(sm.lam[0], -1.0f), 1.0f);
-            for (int i = tid; i < P * N; i += 256) {
-                const int p = i / N, n = i % N;
-                sm.Sh[p][n] += oml * (a.xprev[bh * P + p] * a.bprev[bh * N + n]);
+            const float xp0 = a.xprev[bh * P + p0 + g4] * oml, xp1 = a.xprev[bh * P + p0 + g4 + 8] * oml;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const float2 bp = *reinterpret_cast<const float2*>(a.bprev + bh * N + n0 + 8 * nt + 2 * t4);
+                S[nt][0] = fmaf(xp0, bp.x, S[nt][0]); S[nt][1] = fmaf(xp0, bp.y, S[nt][1]);
+                S[nt][2] = fmaf(xp1, bp.x, S[nt][2]); S[nt][3] = fmaf(xp1, bp.y, S[nt][3]);
+            }
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                uint32_t hi, lo;
+                split2(S[nt][0], S[nt][1], hi, lo);
+                *reinterpret_cast<uint32_t*>(&sm.St[0][p0 + g4][n0 + 8 * nt + 2 * t4]) = hi;
+                *reinterpret_cast<uint32_t*>(&sm.St[1][p0 + g4][n0 + 8 * nt + 2 * t4]) = lo;
+                split2(S[nt][2], S[nt][3], hi, lo);
+                *reinterpret_cast<uint32_t*>(&sm.St[0][p0 + g4 + 8][n0 + 8 * nt + 2 * t4]) = hi;
+                *reinterpret_cast<uint32_t*>(&sm.St[1][p0 + g4 + 8][n0 + 8 * nt + 2 * t4]) = lo;
             }
         }
-        // ---- 2. x, gate, normalised B / C, angles, rotation
+        // ---- 2. thread (lane, warp) takes column `lane` (angle pair k, head dim p) of the warp's 16 tokens:
+        //         angles, rotated B~, silu(x) transposed, gate
         {
-            // all loads of the chunk's x and z first (8 tokens per thread), then the activations: the projection rows
-            // come from DRAM and a load-use-load chain per token was the largest stall of this kernel
-            constexpr int NE = LCH * P / 256;
-            float xr[NE], zr[NE];
+            const int k = lane, i0 = 16 * warp;
+            float loc[16], run = 0.f;
 #pragma unroll
-            for (int q = 0; q < NE; ++q) {
-                const int e = tid + 256 * q, i = e / P, p = e % P;
-                xr[q] = 0.f; zr[q] = 0.f;
-                if (i < nv) {
-                    const float* pr = prow0 + (size_t)(t0 + i) * R;
-                    xr[q] = pr[h * P + p];
-                    zr[q] = pr[DI + h * P + p];
-                }
-            }
-#pragma unroll
-            for (int q = 0; q < NE; ++q) {
-                const int e = tid + 256 * q, i = e / P, p = e % P;
-                sm.Xt[p][i] = i < nv ? silu_ref(xr[q]) : 0.f;      // model.rs:310
-                sm.Gt[i][p] = i < nv ? silu_ref(zr[q]) : 0.f;      // model.rs:370
-            }
-        }
-        {
-            const int k = tid & 31, sg = tid >> 5;         // angle pair k, token segment sg (8 tokens)
-            float loc[8], run = 0.f;
-            // this thread's 8 tokens: theta and the raw B / C pairs are requested together, ahead of any arithmetic
-            float thv[8], rb8[8], rc8[8], pb0[8], pb1[8], pc0[8], pc1[8];
-            const int i0k = g * N + 2 * k;
-#pragma unroll
-            for (int ii = 0; ii < 8; ++ii) {
-                const int i = sg * 8 + ii;
-                thv[ii] = 0.f; rb8[ii] = rc8[ii] = 0.f; pb0[ii] = pb1[ii] = pc0[ii] = pc1[ii] = 0.f;
-                if (i < nv) {
-                    const float* pr = prow0 + (size_t)(t0 + i) * R;
-                    const size_t row = (size_t)b * ts + t0 + i;
-                    thv[ii] = pr[off_dt + 3 * H + h * HN + k];
-                    rb8[ii] = a.rb[row]; rc8[ii] = a.rc[row];
-                    pb0[ii] = pr[off_b + i0k]; pb1[ii] = pr[off_b + i0k + 1];
-                    pc0[ii] = pr[off_c + i0k]; pc1[ii] = pr[off_c + i0k + 1];
-                }
-            }
-#pragma unroll
-            for (int ii = 0; ii < 8; ++ii) {
-                const int i = sg * 8 + ii;
-                float d = 0.f;
-                if (i < nv) d = __fmul_rn(sm.dtp[i], __fmul_rn(tanhf(thv[ii]), PI_F));     // model.rs:341-342
+            for (int ii = 0; ii < 16; ++ii) {
+                const float d = sm.dtp[i0 + ii] * (tanh_fast(sm.rth[i0 + ii][k]) * PI_F);      // model.rs:341-342; dtp = 0 past the end
                 run += d;
                 loc[ii] = run;
             }
-            sm.seg[sg + 1][k] = run;
+            sm.seg[warp + 1][k] = run;
             __syncthreads();
             if (tid < 32) {
                 float off = sm.cum[tid];
                 sm.seg[0][tid] = off;
                 // reduced mod 2 pi at every segment boundary, so sums stay small and keep their low bits
-                for (int s2 = 1; s2 <= 8; ++s2) { off = fmodf(off + sm.seg[s2][tid], TWO_PI); sm.seg[s2][tid] = off; }
+                for (int s2 = 1; s2 <= 4; ++s2) { off = fmodf(off + sm.seg[s2][tid], TWO_PI); sm.seg[s2][tid] = off; }
                 sm.cum[tid] = off;                         // angle after the chunk's last valid token
             }
             __syncthreads();
-            const float base = sm.seg[sg][k];
+            const float base = sm.seg[warp][k];
+            const float bgm0 = sm.gam[0][2 * k], bgm1 = sm.gam[0][2 * k + 1], bbs0 = sm.gam[1][2 * k], bbs1 = sm.gam[1][2 * k + 1];
 #pragma unroll
-            for (int ii = 0; ii < 8; ++ii) {
-                const int i = sg * 8 + ii;
-                float b0 = 0.f, b1 = 0.f, c0 = 0.f, c1 = 0.f;
+            for (int ii = 0; ii < 16; ++ii) {
+                const int i = i0 + ii;
+                float ang = base + loc[ii];
+                ang -= TWO_PI * rintf(ang * INV_TWO_PI);                     // into [-pi, pi] for the fast sin / cos
+                sm.rth[i][k] = ang;
+                float b0 = 0.f, b1 = 0.f;
                 if (i < nv) {
-                    const float rb = rb8[ii], rc = rc8[ii];
-                    const float nb0 = __fadd_rn(__fmul_rn(__fmul_rn(pb0[ii], rb), kbg0), kbb0);
-                    const float nb1 = __fadd_rn(__fmul_rn(__fmul_rn(pb1[ii], rb), kbg1), kbb1);
-                    const float nc0 = __fadd_rn(__fmul_rn(__fmul_rn(pc0[ii], rc), kcg0), kcb0);
-                    const float nc1 = __fadd_rn(__fmul_rn(__fmul_rn(pc1[ii], rc), kcg1), kcb1);
+                    const float2 raw = *reinterpret_cast<const float2*>(&sm.rB[i][2 * k]);
+                    const float rb = sm.rbs[i];
+                    const float nb0 = fmaf(raw.x * rb, bgm0, bbs0), nb1 = fmaf(raw.y * rb, bgm1, bbs1);      // model.rs:311-313
                     float sa, ca;
-                    sincosf(fmodf(base + loc[ii], TWO_PI), &sa, &ca);
-                    b0 = __fsub_rn(__fmul_rn(ca, nb0), __fmul_rn(sa, nb1));   // model.rs:345-348
-                    b1 = __fadd_rn(__fmul_rn(sa, nb0), __fmul_rn(ca, nb1));
-                    c0 = __fsub_rn(__fmul_rn(ca, nc0), __fmul_rn(sa, nc1));
-                    c1 = __fadd_rn(__fmul_rn(sa, nc0), __fmul_rn(ca, nc1));
-                }
-                sm.Bt[i][2 * k] = b0; sm.Bt[i][2 * k + 1] = b1;
-                sm.Ct[i][2 * k] = c0; sm.Ct[i][2 * k + 1] = c1;
-            }
-        }
-        __syncthreads();
-        // ---- 3. W[i][j] = (C~_i . B~_j) * decay * weight, lower triangle
-        {
-            const int ti = tid >> 4, tj = tid & 15;        // rows ti + 16a, cols tj + 16b
-            float acc[4][4];
-#pragma unroll
-            for (int x = 0; x < 4; ++x)
-#pragma unroll
-                for (int y = 0; y < 4; ++y) acc[x][y] = 0.f;
-#pragma unroll 4
-            for (int n4 = 0; n4 < N / 4; ++n4) {
-                float4 c4[4], b4[4];
-#pragma unroll
-                for (int x = 0; x < 4; ++x) c4[x] = *reinterpret_cast<const float4*>(&sm.Ct[ti + 16 * x][4 * n4]);
-#pragma unroll
-                for (int y = 0; y < 4; ++y) b4[y] = *reinterpret_cast<const float4*>(&sm.Bt[tj + 16 * y][4 * n4]);
-#pragma unroll
-                for (int x = 0; x < 4; ++x)
-#pragma unroll
-                    for (int y = 0; y < 4; ++y) acc[x][y] += dot4(c4[x], b4[y]);
-            }
-#pragma unroll
-            for (int x = 0; x < 4; ++x)
-#pragma unroll
-                for (int y = 0; y < 4; ++y) {
-                    const int i = ti + 16 * x, j = tj + 16 * y;
-                    float w = 0.f;
-                    if (j < i) w = acc[x][y] * expf(sm.ell[i] - sm.ell[j]) * sm.kap[j];
-                    else if (j == i) w = acc[x][y] * sm.lam[i];
-                    sm.Wm[i][j] = w;
-                }
-        }
-        __syncthreads();
-        // ---- 4. y = W X + e^{l_i} (C~ S^_in^T) + D x, gated                     (model.rs:365-370)
-        {
-            const int r = tid >> 3, c = tid & 7;           // rows r + 32a, cols c + 8b
-            float yi[2][4], ys[2][4];
-#pragma unroll
-            for (int x = 0; x < 2; ++x)
-#pragma unroll
-                for (int y = 0; y < 4; ++y) { yi[x][y] = 0.f; ys[x][y] = 0.f; }
-#pragma unroll 4
-            for (int q = 0; q < LCH / 4; ++q) {
-                float4 w4[2], x4[4], c4[2], s4[4];
-#pragma unroll
-                for (int x = 0; x < 2; ++x) { w4[x] = *reinterpret_cast<const float4*>(&sm.Wm[r + 32 * x][4 * q]); c4[x] = *reinterpret_cast<const float4*>(&sm.Ct[r + 32 * x][4 * q]); }
-#pragma unroll
-                for (int y = 0; y < 4; ++y) { x4[y] = *reinterpret_cast<const float4*>(&sm.Xt[c + 8 * y][4 * q]); s4[y] = *reinterpret_cast<const float4*>(&sm.Sh[c + 8 * y][4 * q]); }
-#pragma unroll
-                for (int x = 0; x < 2; ++x)
-#pragma unroll
-                    for (int y = 0; y < 4; ++y) { yi[x][y] += dot4(w4[x], x4[y]); ys[x][y] += dot4(c4[x], s4[y]); }
-            }
-#pragma unroll
-            for (int x = 0; x < 2; ++x) {
-                const int i = r + 32 * x;
-                if (i < nv) {
-                    const float el = expf(sm.ell[i]);
-                    const size_t row = (size_t)b * ts + t0 + i;
-#pragma unroll
-                    for (int y = 0; y < 4; ++y) {
-                        const int p = c + 8 * y;
-                        float yv = yi[x][y] + el * ys[x][y] + dskip * sm.Xt[p][i];
-                        yv *= sm.Gt[i][p];
-                        const size_t o = row * DI + h * P + p;
-                        __nv_bfloat16 hh, ll;
-                        split_bf16(yv, hh, ll);
-                        a.yhi[o] = hh;
-                        if (a.ylo) a.ylo[o] = ll;
+                    __sincosf(ang, &sa, &ca);
+                    b0 = ca * nb0 - sa * nb1;                                // model.rs:345-348
+                    b1 = sa * nb0 + ca * nb1;
+                    if (last_chunk && i == nv - 1) {                         // hand-over: B~ of the launch's last token, in fp32
+                        a.bprev[bh * N + 2 * k] = b0;
+                        a.bprev[bh * N + 2 * k + 1] = b1;
                     }
                 }
+                uint32_t hi, lo;
+                split2(b0, b1, hi, lo);
+                *reinterpret_cast<uint32_t*>(&sm.Bt[0][i][2 * k]) = hi;
+                *reinterpret_cast<uint32_t*>(&sm.Bt[1][i][2 * k]) = lo;
+            }
+            // x -> silu -> Xt[p][token] (two tokens per 32-bit word); z -> gate in place
+            const int p = lane;
+#pragma unroll
+            for (int ii = 0; ii < 16; ii += 2) {
+                const int i = i0 + ii;
+                const float x0 = i < nv ? silu_fast(sm.rx[i][p]) : 0.f;                        // model.rs:310
+                const float x1 = i + 1 < nv ? silu_fast(sm.rx[i + 1][p]) : 0.f;
+                uint32_t hi, lo;
+                split2(x0, x1, hi, lo);
+                *reinterpret_cast<uint32_t*>(&sm.Xt[0][p][i]) = hi;
+                *reinterpret_cast<uint32_t*>(&sm.Xt[1][p][i]) = lo;
+                if (last_chunk && (i == nv - 1 || i + 1 == nv - 1)) a.xprev[bh * P + p] = (i == nv - 1) ? x0 : x1;
+                sm.rz[zb][i][p] = i < nv ? silu_fast(sm.rz[zb][i][p]) : 0.f;                   // model.rs:370
+                sm.rz[zb][i + 1][p] = i + 1 < nv ? silu_fast(sm.rz[zb][i + 1][p]) : 0.f;
             }
         }
         __syncthreads();
-        // ---- 5. S^_out = e^{l_last} S^_in + sum_j wj[j] x_j (x) B~_j
+        // ---- 2b. this warp's C~ rows as A fragments (hi, lo), built straight from the raw C rows and the angles
+        uint32_t Ch[4][4], Cl[4][4];
         {
-            const int pr = tid >> 4, n4 = tid & 15;        // rows pr + 16a, columns 4 n4 .. 4 n4 + 3
-            const float el = expf(sm.ell[LCH - 1]);
-            float4 acc[2];
 #pragma unroll
-            for (int x = 0; x < 2; ++x) {
-                const float4 s = *reinterpret_cast<const float4*>(&sm.Sh[pr + 16 * x][4 * n4]);
-                acc[x] = make_float4(el * s.x, el * s.y, el * s.z, el * s.w);
-            }
-#pragma unroll 4
-            for (int j = 0; j < LCH; ++j) {
-                const float4 b4 = *reinterpret_cast<const float4*>(&sm.Bt[j][4 * n4]);
-                const float w = sm.wj[j];
+            for (int q = 0; q < 8; ++q) {
+                const int k = t4 + 4 * q, ks = q >> 1, odd = q & 1;
+                const float cg0 = sm.gam[2][2 * k], cg1 = sm.gam[2][2 * k + 1], cb0 = sm.gam[3][2 * k], cb1 = sm.gam[3][2 * k + 1];
 #pragma unroll
-                for (int x = 0; x < 2; ++x) {
-                    const float xw = sm.Xt[pr + 16 * x][j] * w;
-                    acc[x].x = fmaf(xw, b4.x, acc[x].x); acc[x].y = fmaf(xw, b4.y, acc[x].y);
-                    acc[x].z = fmaf(xw, b4.z, acc[x].z); acc[x].w = fmaf(xw, b4.w, acc[x].w);
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int i = 16 * warp + g4 + 8 * rr;
+                    float c0 = 0.f, c1 = 0.f;
+                    if (i < nv) {
+                        const float2 raw = *reinterpret_cast<const float2*>(&sm.rC[i][2 * k]);
+                        const float rc = sm.rcs[i];
+                        const float nc0 = fmaf(raw.x * rc, cg0, cb0), nc1 = fmaf(raw.y * rc, cg1, cb1);
+                        float sa, ca;
+                        __sincosf(sm.rth[i][k], &sa, &ca);
+                        c0 = ca * nc0 - sa * nc1;
+                        c1 = sa * nc0 + ca * nc1;
+                    }
+                    split2(c0, c1, Ch[ks][2 * odd + rr], Cl[ks][2 * odd + rr]);
                 }
             }
+        }
+        // every raw value of this chunk has been consumed: order these generic-proxy accesses before the next copies
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        if (!last_chunk) {
+            if (tid == 0) issue_chunk(t0 + LCH, zb ^ 1);
+            request_scalars(t0 + LCH);
+        }
+        // ---- 3. Y2 = C~ S^_in^T, G = C~ B~^T (causal part), W = mask / decay (G) (+ D on the diagonal), Y1 = W X
+        float y1[4][4], y2[4][4];
 #pragma unroll
-            for (int x = 0; x < 2; ++x) *reinterpret_cast<float4*>(&sm.Sh[pr + 16 * x][4 * n4]) = acc[x];
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { y1[nt][e] = 0.f; y2[nt][e] = 0.f; }
+        {
+            // ldmatrix row address of this lane inside a [rows][TSB] tile: matrix m = lane / 8, row r = lane % 8
+            const int lm = lane >> 3, lr = lane & 7;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+                for (int np = 0; np < 2; ++np) {           // p tiles 2 np, 2 np + 1
+                    uint32_t sh[4], sl[4];
+                    const int row = 8 * (2 * np + (lm >> 1)) + lr, col = 16 * ks + 8 * (lm & 1);
+                    ldsm_x4(sh, &sm.St[0][row][col]);
+                    ldsm_x4(sl, &sm.St[1][row][col]);
+                    mma3(y2[2 * np], Ch[ks], Cl[ks], sh[0], sh[1], sl[0], sl[1]);
+                    mma3(y2[2 * np + 1], Ch[ks], Cl[ks], sh[2], sh[3], sl[2], sl[3]);
+                }
+            }
+            const int ia = 16 * warp + g4, ib = ia + 8;
+            const float ella = sm.ell[ia], ellb = sm.ell[ib];
+            for (int jp = 0; jp <= warp; ++jp) {           // token columns 16 jp .. 16 jp + 15
+                float g0[4] = {0.f, 0.f, 0.f, 0.f}, g1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    uint32_t bh4[4], bl4[4];
+                    const int row = 16 * jp + 8 * (lm >> 1) + lr, col = 16 * ks + 8 * (lm & 1);
+                    ldsm_x4(bh4, &sm.Bt[0][row][col]);
+                    ldsm_x4(bl4, &sm.Bt[1][row][col]);
+                    mma3(g0, Ch[ks], Cl[ks], bh4[0], bh4[1], bl4[0], bl4[1]);
+                    mma3(g1, Ch[ks], Cl[ks], bh4[2], bh4[3], bl4[2], bl4[3]);
+                }
+                // element e of tile q: row (e < 2 ? ia : ib), column 16 jp + 8 q + 2 t4 + (e & 1)
+                float wv[2][4];
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = (e < 2) ? ia : ib, j = 16 * jp + 8 * q + 2 * t4 + (e & 1);
+                        const float gv = q == 0 ? g0[e] : g1[e];
+                        float w = 0.f;
+                        if (j < i) w = gv * __expf(((e < 2) ? ella : ellb) - sm.ell[j]) * sm.kap[j];
+                        else if (j == i) w = fmaf(gv, sm.lam[i], dskip);          // lam_i (C~_i . B~_i) x_i + D x_i
+                        wv[q][e] = w;
+                    }
+                uint32_t wh[4], wl[4];
+                split2(wv[0][0], wv[0][1], wh[0], wl[0]);
+                split2(wv[0][2], wv[0][3], wh[1], wl[1]);
+                split2(wv[1][0], wv[1][1], wh[2], wl[2]);
+                split2(wv[1][2], wv[1][3], wh[3], wl[3]);
+#pragma unroll
+                for (int np = 0; np < 2; ++np) {
+                    uint32_t xh[4], xl[4];
+                    const int row = 8 * (2 * np + (lm >> 1)) + lr, col = 16 * jp + 8 * (lm & 1);
+                    ldsm_x4(xh, &sm.Xt[0][row][col]);
+                    ldsm_x4(xl, &sm.Xt[1][row][col]);
+                    mma3(y1[2 * np], wh, wl, xh[0], xh[1], xl[0], xl[1]);
+                    mma3(y1[2 * np + 1], wh, wl, xh[2], xh[3], xl[2], xl[3]);
+                }
+            }
+            // y = Y1 + e^{l_i} Y2, gated; four lanes of a quad exchange words so that each stores 16 bytes of a row
+            const float ela = sm.eli[ia], elb = sm.eli[ib];
+            uint32_t oh[2][4], ol[2][4];                   // [row a / b][p tile]
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const float2 ga = *reinterpret_cast<const float2*>(&sm.rz[zb][ia][8 * nt + 2 * t4]);
+                const float2 gb = *reinterpret_cast<const float2*>(&sm.rz[zb][ib][8 * nt + 2 * t4]);
+                split2(fmaf(ela, y2[nt][0], y1[nt][0]) * ga.x, fmaf(ela, y2[nt][1], y1[nt][1]) * ga.y, oh[0][nt], ol[0][nt]);
+                split2(fmaf(elb, y2[nt][2], y1[nt][2]) * gb.x, fmaf(elb, y2[nt][3], y1[nt][3]) * gb.y, oh[1][nt], ol[1][nt]);
+            }
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int i = rr == 0 ? ia : ib;
+                uint32_t vh[4], vl[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    // step r: this lane hands over its word for p tile (t4 - r) & 3 and receives, from lane (t4 + r) & 3
+                    // of its quad, that lane's word for p tile t4
+                    const int give = (t4 - r) & 3, from = (lane & ~3) | ((t4 + r) & 3);
+                    const uint32_t sh_ = give == 0 ? oh[rr][0] : give == 1 ? oh[rr][1] : give == 2 ? oh[rr][2] : oh[rr][3];
+                    const uint32_t sl_ = give == 0 ? ol[rr][0] : give == 1 ? ol[rr][1] : give == 2 ? ol[rr][2] : ol[rr][3];
+                    const uint32_t rh = __shfl_sync(0xffffffffu, sh_, from);
+                    const uint32_t rl = __shfl_sync(0xffffffffu, sl_, from);
+                    const int slot = (t4 + r) & 3;
+                    if (slot == 0) { vh[0] = rh; vl[0] = rl; } else if (slot == 1) { vh[1] = rh; vl[1] = rl; }
+                    else if (slot == 2) { vh[2] = rh; vl[2] = rl; } else { vh[3] = rh; vl[3] = rl; }
+                }
+                if (i < nv) {
+                    const size_t o = ((size_t)b * ts + t0 + i) * DI + h * P + 8 * t4;
+                    *reinterpret_cast<uint4*>(a.yhi + o) = make_uint4(vh[0], vh[1], vh[2], vh[3]);
+                    if (a.ylo) *reinterpret_cast<uint4*>(a.ylo + o) = make_uint4(vl[0], vl[1], vl[2], vl[3]);
+                }
+            }
+        }
+        __syncthreads();                                   // every warp has read S^_in's tile
+        // ---- 4. S^_out = e^{l_last} S^_in + (w x)^T B~  for this warp's 16 x 32 block; new S^ tile for the next chunk
+        {
+            const float el = __expf(sm.ell[LCH - 1]);
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) S[nt][e] *= el;
+            const int lm = lane >> 3, lr = lane & 7;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {               // tokens 16 ks .. 16 ks + 15
+                uint32_t ah[4], al[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int p = p0 + g4 + 8 * (e & 1), j = 16 * ks + 2 * t4 + 8 * (e >> 1);
+                    const float2 xh = unpack2(*reinterpret_cast<const uint32_t*>(&sm.Xt[0][p][j]));
+                    const float2 xl = unpack2(*reinterpret_cast<const uint32_t*>(&sm.Xt[1][p][j]));
+                    split2((xh.x + xl.x) * sm.wj[j], (xh.y + xl.y) * sm.wj[j + 1], ah[e], al[e]);
+                }
+#pragma unroll
+                for (int np = 0; np < 2; ++np) {           // state columns n0 + 16 np .. + 15
+                    uint32_t bh4[4], bl4[4];
+                    const int row = 16 * ks + 8 * (lm & 1) + lr, col = n0 + 16 * np + 8 * (lm >> 1);
+                    ldsm_x4_trans(bh4, &sm.Bt[0][row][col]);
+                    ldsm_x4_trans(bl4, &sm.Bt[1][row][col]);
+                    mma3(S[2 * np], ah, al, bh4[0], bh4[1], bl4[0], bl4[1]);
+                    mma3(S[2 * np + 1], ah, al, bh4[2], bh4[3], bl4[2], bl4[3]);
+                }
+            }
+            if (!last_chunk) {
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    uint32_t hi, lo;
+                    split2(S[nt][0], S[nt][1], hi, lo);
+                    *reinterpret_cast<uint32_t*>(&sm.St[0][p0 + g4][n0 + 8 * nt + 2 * t4]) = hi;
+                    *reinterpret_cast<uint32_t*>(&sm.St[1][p0 + g4][n0 + 8 * nt + 2 * t4]) = lo;
+                    split2(S[nt][2], S[nt][3], hi, lo);
+                    *reinterpret_cast<uint32_t*>(&sm.St[0][p0 + g4 + 8][n0 + 8 * nt + 2 * t4]) = hi;
+                    *reinterpret_cast<uint32_t*>(&sm.St[1][p0 + g4 + 8][n0 + 8 * nt + 2 * t4]) = lo;
+                }
+            }
         }
         __syncthreads();
     }
-    // ---- hand-over: the exact decode state after the last token of this launch
-    for (int i = tid; i < P * N; i += 256) a.h[bh * (size_t)(P * N) + i] = sm.Sh[i / N][i % N];
-    if (tid < P) a.xprev[bh * P + tid] = sm.Xt[tid][last_valid];
-    if (tid < N) a.bprev[bh * N + tid] = sm.Bt[last_valid][tid];
+    if (failed) {
+        // the wait gave up: report, let this CTA's copies land (bounded) so nothing writes into shared memory after exit
+        if (tid == 0) {
+            if (a.status != nullptr) atomicOr(a.status, STATUS_TIMEOUT);
+            mbar_wait(bar, phase, kScanWaitLimitNs);
+        }
+        __syncthreads();
+        return;
+    }
+    // ---- hand-over: the exact decode state after the last token of this launch (kap = lam on it, so S^ = S)
+    {
+        float* hp = a.h + bh * (size_t)(P * N);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            *reinterpret_cast<float2*>(hp + (p0 + g4) * N + n0 + 8 * nt + 2 * t4) = make_float2(S[nt][0], S[nt][1]);
+            *reinterpret_cast<float2*>(hp + (p0 + g4 + 8) * N + n0 + 8 * nt + 2 * t4) = make_float2(S[nt][2], S[nt][3]);
+        }
+    }
     if (tid < HN) a.cum[bh * HN + tid] = sm.cum[tid];
 }
 
 }  // namespace
 
-bool prefill_ssd_supported(const Config& c) { return c.head_dim() == 32 && c.d_state == 64; }
+// head_dim 32 and d_state 64 are what the fragments are laid out for; n_heads % 4 keeps every box of the staged
+// projection rows on a 16-byte boundary (row pitch and the offsets of the theta columns)
+bool prefill_ssd_supported(const Config& c) {
+    return c.head_dim() == 32 && c.d_state == 64 && c.n_groups > 0 && c.n_heads % c.n_groups == 0 && c.n_heads % 4 == 0;
+}
 
 cudaError_t launch_prefill_embed(const void* emb, int dtype, const uint32_t* prompt, float* x, int D, int vocab, int rows, int ts,
                                  int t_abs0, int b_abs0, int batch_total, StepCtl* ctl, cudaStream_t st) {
@@ -363,7 +600,7 @@ cudaError_t launch_prefill_embed(const void* emb, int dtype, const uint32_t* pro
 }
 
 cudaError_t launch_prefill_scan(const PrefillArgs& a, cudaStream_t st) {
-    const size_t smem = sizeof(PfSmem) + 16;
+    const size_t smem = sizeof(PfSmem) + 1024;
     static bool set = false;
     if (!set) {
         cudaError_t e = cudaFuncSetAttribute(ssd_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -371,10 +608,15 @@ cudaError_t launch_prefill_scan(const PrefillArgs& a, cudaStream_t st) {
         set = true;
     }
     const int rows = a.nb * a.ts;
+    // the projection rows as a 2-D fp32 tensor [rows][ldp]; boxes of 64 tokens x 32 columns (x, z, theta) and x 64 (B, C)
+    CUtensorMap m32, m64;
+    if (make_f32_map_2d(&m32, a.proj, (uint64_t)rows, (uint64_t)a.ldp, (uint64_t)a.ldp * 4, 32, LCH) != LUMI_OK ||
+        make_f32_map_2d(&m64, a.proj, (uint64_t)rows, (uint64_t)a.ldp, (uint64_t)a.ldp * 4, 64, LCH) != LUMI_OK)
+        return cudaErrorInvalidValue;
     bc_stats_kernel<<<(rows * 32 + 255) / 256, 256, 0, st>>>(a.proj, a.ldp, 2 * a.H * 32, a.G * 64, a.eps, a.rb, a.rc, rows);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    ssd_prefill_kernel<<<dim3(a.H, a.nb), 256, smem, st>>>(a);
+    ssd_prefill_kernel<<<dim3(a.H, a.nb), 128, smem, st>>>(m32, m64, a);
     return cudaGetLastError();
 }
 

@@ -103,3 +103,34 @@ def test_score_and_snapshot_argument_errors():
     sess.load_state(0, snap)                                              # the intact one still loads
     n = C.c_int64()
     assert lumi_b200.lib().lumi_session_state_bytes(sess._h, C.byref(n)) == 0 and n.value == len(snap)
+
+
+def test_bounded_device_wait_runs_out_and_the_library_recovers():
+    """A device-side wait that can never be satisfied: the producer warp of the persistent tensor-core GEMM is told
+    to stop before one output tile, every wait is limited to 2 ms, and the consumers' waits run out.  The kernel must
+    return by itself (no trap, no unbounded spin), report STATUS_TIMEOUT -> LUMI_E_TIMEOUT, free its tensor memory,
+    and the same GEMM must work right afterwards."""
+    import torch
+    L = lumi_b200.lib()
+    M, N, K = 256, 512, 256
+    g = torch.Generator(device="cuda").manual_seed(1)
+    a = torch.randn((M, K), generator=g, device="cuda").to(torch.bfloat16).contiguous()
+    w = torch.randn((N, K), generator=g, device="cuda").to(torch.bfloat16).contiguous()
+    d = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    rc = L.lumi_debug_gemm_wait_timeout(a.data_ptr(), w.data_ptr(), d.data_ptr(), M, N, K, 2_000_000, 1, status.data_ptr())
+    assert rc == -7, L.lumi_last_error().decode()                  # LUMI_E_TIMEOUT
+    assert "wait expired" in L.lumi_last_error().decode()
+    assert int(status.item()) & 4                                  # STATUS_TIMEOUT
+    # nothing was skipped: the same entry point, then the ordinary one, give the product
+    status.zero_()
+    torch.cuda.synchronize()
+    rc = L.lumi_debug_gemm_wait_timeout(a.data_ptr(), w.data_ptr(), d.data_ptr(), M, N, K, 2_000_000, -1, status.data_ptr())
+    assert rc == 0, L.lumi_last_error().decode()
+    ref = a.float() @ w.float().t()
+    assert float((d - ref).abs().max() / ref.abs().max()) < 1e-5
+    d.zero_()
+    lumi_b200.api.check(L.lumi_k_gemm_bf16_tcgen05(a.data_ptr(), 0, w.data_ptr(), d.data_ptr(), M, N, K, N, 0, 0))
+    torch.cuda.synchronize()
+    assert float((d - ref).abs().max() / ref.abs().max()) < 1e-5
