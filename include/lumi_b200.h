@@ -127,7 +127,7 @@ void    lumi_session_free(lumi_session* s);
  *                         models (attention layers included, unless one has a sliding window) prefill with the
  *                         chunked SSD scan (chunk 64), attention over all rows of a slice and tensor-core GEMMs
  *                         over all prompt tokens instead of token by token (same state to rounding); "prefill_rows" =
- *                         token rows per pass of that path (default 32768; sets its workspace size);
+ *                         token rows per pass of that path (default 131072; sets its workspace size: 41 KB per row);
  *                         "overlap" = minimum batch (default 0 = never) from which the tensor-core path runs two
  *                         lanes of sequences side by side on prioritised streams (measured neutral: the state
  *                         step needs its L1 and cannot share an SM with the 198 KB GEMM);

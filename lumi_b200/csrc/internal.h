@@ -141,7 +141,7 @@ struct lumi_session {
     int opt_overlap = 0;              // minimum batch for two-lane execution (0 = never)
     size_t act_ld = 0;                // elements per row of the activation-half buffers
     int opt_chunked_prefill = 128;    // minimum prompt length for the chunked SSD prefill (0 = never)
-    int opt_prefill_rows = 32768;     // token rows processed per chunked-prefill pass (workspace size)
+    int opt_prefill_rows = 131072;    // token rows processed per chunked-prefill pass (workspace size)
     // chunked-prefill workspace (grow-only): residual rows, in_proj output, bf16 halves, BCNorm scales
     float *pf_x = nullptr, *pf_proj = nullptr, *pf_rb = nullptr, *pf_rc = nullptr;
     __nv_bfloat16 *pf_hi = nullptr, *pf_lo = nullptr;

@@ -35,6 +35,8 @@
 
 #include <cuda.h>
 
+#include <type_traits>
+
 namespace lumi {
 
 // defined in gemm_tcgen05.cu: cuTensorMapEncodeTiled for a row-major fp32 matrix [rows][cols], no swizzle
@@ -91,17 +93,29 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
 
 // D (16x8, fp32) += A (16x16, bf16, row) * B (16x8, bf16, col)
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// (a_hi + a_lo)(b_hi + b_lo) without the lo*lo term
-__device__ __forceinline__ void mma3(float (&d)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4], uint32_t bh0, uint32_t bh1,
-                                     uint32_t bl0, uint32_t bl1) {
-    mma_bf16(d, ah, bh0, bh1);
-    mma_bf16(d, ah, bl0, bl1);
-    mma_bf16(d, al, bh0, bh1);
+// (a_hi + a_lo)(b_hi + b_lo) without the lo*lo term, for the two 8-column tiles whose B fragments one ldmatrix.x4
+// delivers (bh / bl: {b0, b1} of the first tile, {b0, b1} of the second).  The six multiply-adds alternate between
+// the two accumulators so that no instruction waits for the one just before it.
+__device__ __forceinline__ void mma3x2(float (&d0)[4], float (&d1)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4],
+                                       const uint32_t (&bh)[4], const uint32_t (&bl)[4]) {
+    mma_bf16(d0, ah, bh[0], bh[1]);
+    mma_bf16(d1, ah, bh[2], bh[3]);
+    mma_bf16(d0, ah, bl[0], bl[1]);
+    mma_bf16(d1, ah, bl[2], bl[3]);
+    mma_bf16(d0, al, bh[0], bh[1]);
+    mma_bf16(d1, al, bh[2], bh[3]);
+}
+// the same for four tiles (two ldmatrix.x4 per plane): twelve multiply-adds round-robin over four accumulators
+__device__ __forceinline__ void mma3x4(float (&d0)[4], float (&d1)[4], float (&d2)[4], float (&d3)[4], const uint32_t (&ah)[4],
+                                       const uint32_t (&al)[4], const uint32_t (&bh0)[4], const uint32_t (&bl0)[4],
+                                       const uint32_t (&bh1)[4], const uint32_t (&bl1)[4]) {
+    mma_bf16(d0, ah, bh0[0], bh0[1]); mma_bf16(d1, ah, bh0[2], bh0[3]); mma_bf16(d2, ah, bh1[0], bh1[1]); mma_bf16(d3, ah, bh1[2], bh1[3]);
+    mma_bf16(d0, ah, bl0[0], bl0[1]); mma_bf16(d1, ah, bl0[2], bl0[3]); mma_bf16(d2, ah, bl1[0], bl1[1]); mma_bf16(d3, ah, bl1[2], bl1[3]);
+    mma_bf16(d0, al, bh0[0], bh0[1]); mma_bf16(d1, al, bh0[2], bh0[3]); mma_bf16(d2, al, bh1[0], bh1[1]); mma_bf16(d3, al, bh1[2], bh1[3]);
 }
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -258,10 +272,11 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
     }
 
     uint32_t phase = 0;
-    bool failed = false;
-    int chunk = 0;
-    for (int t0 = 0; t0 < ts; t0 += LCH, ++chunk) {
-        const int nv = min(LCH, ts - t0);                  // valid tokens in this chunk
+    // One chunk.  FULL: all 64 tokens are valid, so every "past the end of the sequence" test folds away.
+    auto do_chunk = [&](auto full_c, const int t0, const int chunk) -> bool {
+        constexpr bool FULL = decltype(full_c)::value;
+        const int nv = FULL ? LCH : min(LCH, ts - t0);     // valid tokens in this chunk
+        auto valid = [&](int i) { return FULL || i < nv; };
         const int zb = chunk & 1;
         const bool last_chunk = t0 + LCH >= ts;
         // ---- 0. the chunk's raw rows have landed (one thread waits, bounded; everyone follows its verdict)
@@ -269,7 +284,7 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
         // ---- 1. per-token scalars (model.rs:307, 314-317) from the registers requested a chunk earlier
         if (tid < LCH) {
             float dtpv = 0.f, gl = 0.f, lm = 0.f;
-            if (tid < nv) {
+            if (valid(tid)) {
                 dtpv = softplus_ref(__fadd_rn(n_dt, dtb));
                 float av = -softplus_ref(n_a);
                 av = fminf(fmaxf(av, -1e6f), -1e-4f);
@@ -281,7 +296,7 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
         }
         if (tid == LCH) sm.lam[LCH] = (t0 + LCH < ts) ? sigmoid_ref(n_lam) : -1.0f;      // < 0: no next token in this launch
         __syncthreads();
-        if (!sm.ok) { failed = true; break; }
+        if (!sm.ok) return false;
         phase ^= 1;
         if (tid < 32) {                                    // inclusive prefix of log a over the chunk
             float v0 = sm.ell[2 * lane], v1 = sm.ell[2 * lane + 1];
@@ -296,8 +311,8 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
         if (tid < LCH) {
             const int i = tid;
             float k = 0.f;
-            if (i < nv) {
-                const float ln = (i + 1 < nv) ? sm.lam[i + 1] : ((nv == LCH) ? sm.lam[LCH] : -1.0f);
+            if (valid(i)) {
+                const float ln = valid(i + 1) && i + 1 < LCH ? sm.lam[i + 1] : ((nv == LCH) ? sm.lam[LCH] : -1.0f);
                 k = (ln < 0.f) ? sm.lam[i] : __fadd_rn(sm.lam[i], __fsub_rn(1.0f, ln));
             }
             sm.kap[i] = k;
@@ -355,7 +370,7 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
                 ang -= TWO_PI * rintf(ang * INV_TWO_PI);                     // into [-pi, pi] for the fast sin / cos
                 sm.rth[i][k] = ang;
                 float b0 = 0.f, b1 = 0.f;
-                if (i < nv) {
+                if (valid(i)) {
                     const float2 raw = *reinterpret_cast<const float2*>(&sm.rB[i][2 * k]);
                     const float rb = sm.rbs[i];
                     const float nb0 = fmaf(raw.x * rb, bgm0, bbs0), nb1 = fmaf(raw.y * rb, bgm1, bbs1);      // model.rs:311-313
@@ -378,15 +393,15 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
 #pragma unroll
             for (int ii = 0; ii < 16; ii += 2) {
                 const int i = i0 + ii;
-                const float x0 = i < nv ? silu_fast(sm.rx[i][p]) : 0.f;                        // model.rs:310
-                const float x1 = i + 1 < nv ? silu_fast(sm.rx[i + 1][p]) : 0.f;
+                const float x0 = valid(i) ? silu_fast(sm.rx[i][p]) : 0.f;                        // model.rs:310
+                const float x1 = valid(i + 1) ? silu_fast(sm.rx[i + 1][p]) : 0.f;
                 uint32_t hi, lo;
                 split2(x0, x1, hi, lo);
                 *reinterpret_cast<uint32_t*>(&sm.Xt[0][p][i]) = hi;
                 *reinterpret_cast<uint32_t*>(&sm.Xt[1][p][i]) = lo;
                 if (last_chunk && (i == nv - 1 || i + 1 == nv - 1)) a.xprev[bh * P + p] = (i == nv - 1) ? x0 : x1;
-                sm.rz[zb][i][p] = i < nv ? silu_fast(sm.rz[zb][i][p]) : 0.f;                   // model.rs:370
-                sm.rz[zb][i + 1][p] = i + 1 < nv ? silu_fast(sm.rz[zb][i + 1][p]) : 0.f;
+                sm.rz[zb][i][p] = valid(i) ? silu_fast(sm.rz[zb][i][p]) : 0.f;                   // model.rs:370
+                sm.rz[zb][i + 1][p] = valid(i + 1) ? silu_fast(sm.rz[zb][i + 1][p]) : 0.f;
             }
         }
         __syncthreads();
@@ -401,7 +416,7 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
                 for (int rr = 0; rr < 2; ++rr) {
                     const int i = 16 * warp + g4 + 8 * rr;
                     float c0 = 0.f, c1 = 0.f;
-                    if (i < nv) {
+                    if (valid(i)) {
                         const float2 raw = *reinterpret_cast<const float2*>(&sm.rC[i][2 * k]);
                         const float rc = sm.rcs[i];
                         const float nc0 = fmaf(raw.x * rc, cg0, cb0), nc1 = fmaf(raw.y * rc, cg1, cb1);
@@ -432,29 +447,35 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
             const int lm = lane >> 3, lr = lane & 7;
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-#pragma unroll
-                for (int np = 0; np < 2; ++np) {           // p tiles 2 np, 2 np + 1
-                    uint32_t sh[4], sl[4];
-                    const int row = 8 * (2 * np + (lm >> 1)) + lr, col = 16 * ks + 8 * (lm & 1);
-                    ldsm_x4(sh, &sm.St[0][row][col]);
-                    ldsm_x4(sl, &sm.St[1][row][col]);
-                    mma3(y2[2 * np], Ch[ks], Cl[ks], sh[0], sh[1], sl[0], sl[1]);
-                    mma3(y2[2 * np + 1], Ch[ks], Cl[ks], sh[2], sh[3], sl[2], sl[3]);
-                }
+                uint32_t sh0[4], sl0[4], sh1[4], sl1[4];   // p tiles 0, 1 and 2, 3
+                const int row = 8 * (lm >> 1) + lr, col = 16 * ks + 8 * (lm & 1);
+                ldsm_x4(sh0, &sm.St[0][row][col]);
+                ldsm_x4(sl0, &sm.St[1][row][col]);
+                ldsm_x4(sh1, &sm.St[0][row + 16][col]);
+                ldsm_x4(sl1, &sm.St[1][row + 16][col]);
+                mma3x4(y2[0], y2[1], y2[2], y2[3], Ch[ks], Cl[ks], sh0, sl0, sh1, sl1);
             }
             const int ia = 16 * warp + g4, ib = ia + 8;
             const float ella = sm.ell[ia], ellb = sm.ell[ib];
             for (int jp = 0; jp <= warp; ++jp) {           // token columns 16 jp .. 16 jp + 15
+                // six independent accumulation chains (hi*hi, hi*lo, lo*hi of the two 8-column tiles), added at the end
                 float g0[4] = {0.f, 0.f, 0.f, 0.f}, g1[4] = {0.f, 0.f, 0.f, 0.f};
+                float g0b[4] = {0.f, 0.f, 0.f, 0.f}, g1b[4] = {0.f, 0.f, 0.f, 0.f}, g0c[4] = {0.f, 0.f, 0.f, 0.f}, g1c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
                     uint32_t bh4[4], bl4[4];
                     const int row = 16 * jp + 8 * (lm >> 1) + lr, col = 16 * ks + 8 * (lm & 1);
                     ldsm_x4(bh4, &sm.Bt[0][row][col]);
                     ldsm_x4(bl4, &sm.Bt[1][row][col]);
-                    mma3(g0, Ch[ks], Cl[ks], bh4[0], bh4[1], bl4[0], bl4[1]);
-                    mma3(g1, Ch[ks], Cl[ks], bh4[2], bh4[3], bl4[2], bl4[3]);
+                    mma_bf16(g0, Ch[ks], bh4[0], bh4[1]);
+                    mma_bf16(g1, Ch[ks], bh4[2], bh4[3]);
+                    mma_bf16(g0b, Ch[ks], bl4[0], bl4[1]);
+                    mma_bf16(g1b, Ch[ks], bl4[2], bl4[3]);
+                    mma_bf16(g0c, Cl[ks], bh4[0], bh4[1]);
+                    mma_bf16(g1c, Cl[ks], bh4[2], bh4[3]);
                 }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { g0[e] += g0b[e] + g0c[e]; g1[e] += g1b[e] + g1c[e]; }
                 // element e of tile q: row (e < 2 ? ia : ib), column 16 jp + 8 q + 2 t4 + (e & 1)
                 float wv[2][4];
 #pragma unroll
@@ -473,14 +494,14 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
                 split2(wv[0][2], wv[0][3], wh[1], wl[1]);
                 split2(wv[1][0], wv[1][1], wh[2], wl[2]);
                 split2(wv[1][2], wv[1][3], wh[3], wl[3]);
-#pragma unroll
-                for (int np = 0; np < 2; ++np) {
-                    uint32_t xh[4], xl[4];
-                    const int row = 8 * (2 * np + (lm >> 1)) + lr, col = 16 * jp + 8 * (lm & 1);
-                    ldsm_x4(xh, &sm.Xt[0][row][col]);
-                    ldsm_x4(xl, &sm.Xt[1][row][col]);
-                    mma3(y1[2 * np], wh, wl, xh[0], xh[1], xl[0], xl[1]);
-                    mma3(y1[2 * np + 1], wh, wl, xh[2], xh[3], xl[2], xl[3]);
+                {
+                    uint32_t xh0[4], xl0[4], xh1[4], xl1[4];
+                    const int row = 8 * (lm >> 1) + lr, col = 16 * jp + 8 * (lm & 1);
+                    ldsm_x4(xh0, &sm.Xt[0][row][col]);
+                    ldsm_x4(xl0, &sm.Xt[1][row][col]);
+                    ldsm_x4(xh1, &sm.Xt[0][row + 16][col]);
+                    ldsm_x4(xl1, &sm.Xt[1][row + 16][col]);
+                    mma3x4(y1[0], y1[1], y1[2], y1[3], wh, wl, xh0, xl0, xh1, xl1);
                 }
             }
             // y = Y1 + e^{l_i} Y2, gated; four lanes of a quad exchange words so that each stores 16 bytes of a row
@@ -510,7 +531,7 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
                     if (slot == 0) { vh[0] = rh; vl[0] = rl; } else if (slot == 1) { vh[1] = rh; vl[1] = rl; }
                     else if (slot == 2) { vh[2] = rh; vl[2] = rl; } else { vh[3] = rh; vl[3] = rl; }
                 }
-                if (i < nv) {
+                if (valid(i)) {
                     const size_t o = ((size_t)b * ts + t0 + i) * DI + h * P + 8 * t4;
                     *reinterpret_cast<uint4*>(a.yhi + o) = make_uint4(vh[0], vh[1], vh[2], vh[3]);
                     if (a.ylo) *reinterpret_cast<uint4*>(a.ylo + o) = make_uint4(vl[0], vl[1], vl[2], vl[3]);
@@ -536,14 +557,14 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
                     const float2 xl = unpack2(*reinterpret_cast<const uint32_t*>(&sm.Xt[1][p][j]));
                     split2((xh.x + xl.x) * sm.wj[j], (xh.y + xl.y) * sm.wj[j + 1], ah[e], al[e]);
                 }
-#pragma unroll
-                for (int np = 0; np < 2; ++np) {           // state columns n0 + 16 np .. + 15
-                    uint32_t bh4[4], bl4[4];
-                    const int row = 16 * ks + 8 * (lm & 1) + lr, col = n0 + 16 * np + 8 * (lm >> 1);
-                    ldsm_x4_trans(bh4, &sm.Bt[0][row][col]);
-                    ldsm_x4_trans(bl4, &sm.Bt[1][row][col]);
-                    mma3(S[2 * np], ah, al, bh4[0], bh4[1], bl4[0], bl4[1]);
-                    mma3(S[2 * np + 1], ah, al, bh4[2], bh4[3], bl4[2], bl4[3]);
+                {
+                    uint32_t bh0[4], bl0[4], bh1[4], bl1[4];   // state columns n0 .. n0 + 15 and n0 + 16 .. n0 + 31
+                    const int row = 16 * ks + 8 * (lm & 1) + lr, col = n0 + 8 * (lm >> 1);
+                    ldsm_x4_trans(bh0, &sm.Bt[0][row][col]);
+                    ldsm_x4_trans(bl0, &sm.Bt[1][row][col]);
+                    ldsm_x4_trans(bh1, &sm.Bt[0][row][col + 16]);
+                    ldsm_x4_trans(bl1, &sm.Bt[1][row][col + 16]);
+                    mma3x4(S[0], S[1], S[2], S[3], ah, al, bh0, bl0, bh1, bl1);
                 }
             }
             if (!last_chunk) {
@@ -560,6 +581,15 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
             }
         }
         __syncthreads();
+        return true;
+    };
+    bool failed = false;
+    {
+        int chunk = 0;
+        for (int t0 = 0; t0 < ts && !failed; t0 += LCH, ++chunk) {
+            const bool okc = (t0 + LCH <= ts) ? do_chunk(std::true_type{}, t0, chunk) : do_chunk(std::false_type{}, t0, chunk);
+            failed = !okc;
+        }
     }
     if (failed) {
         // the wait gave up: report, let this CTA's copies land (bounded) so nothing writes into shared memory after exit
