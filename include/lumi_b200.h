@@ -71,6 +71,9 @@ typedef struct lumi_stats {
     int64_t bytes_per_step;   /* algorithmic bytes of one decode step at this batch:
                                  weights once + per sequence (state read+write, KV)   */
     int64_t kernel_launches;  /* kernels of this library launched in the timed phases  */
+    float   achieved_gbps;    /* bytes_per_step * decode steps / ms_decode, in GB/s (0 without decode steps) */
+    int32_t waves;            /* resident batches the call ran through: always 1 here — a host that holds more
+                                 sequences than a session runs them as several calls (waves) and adds the times */
 } lumi_stats;
 
 /* Message for the last failure on the calling thread ("" if none). */
@@ -255,7 +258,12 @@ int32_t lumi_k_ssd_prefill(uint64_t proj, int32_t ldp, uint64_t b_gamma, uint64_
  * LUMI_E_UNSUPPORTED.  The weights come from `m` (loaded and finalized earlier).  No cudaMalloc,
  * cudaFree or other allocating call is made.  The first call on a device looks up the array's
  * device address (cudaGetSymbolAddress, with that device current) and keeps it: make that first
- * call before any stream capture begins.  All calls on a device share the one array, which keeps
+ * call before any stream capture begins — with the same batch size and the same model as the calls
+ * that follow, because the batch size (1, 2, 3-4 or 5-8) and the weight type select the kernels, and a
+ * kernel's code is loaded at its first launch.  The call makes the model's device current
+ * (cudaSetDevice) and leaves it so.  It enqueues three kernels on `stream` and returns without
+ * synchronising; none of them waits on anything on the device, so there is no device-side failure it
+ * would have to report later.  All calls on a device share the one array, which keeps
  * whatever the last call left in it; nothing in it needs clearing (every element is written
  * before it is read), but two calls whose kernels overlap on the GPU — different streams, or the same
  * stream from different threads — race on it: serialise them. */

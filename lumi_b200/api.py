@@ -43,7 +43,8 @@ class Sampling(C.Structure):
 
 class Stats(C.Structure):
     _fields_ = [("prompt_tokens", C.c_int64), ("decode_tokens", C.c_int64), ("ms_prefill", C.c_float),
-                ("ms_decode", C.c_float), ("bytes_per_step", C.c_int64), ("kernel_launches", C.c_int64)]
+                ("ms_decode", C.c_float), ("bytes_per_step", C.c_int64), ("kernel_launches", C.c_int64),
+                ("achieved_gbps", C.c_float), ("waves", C.c_int32)]
 
 
 def lib():

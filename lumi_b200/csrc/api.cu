@@ -338,7 +338,7 @@ extern "C" void lumi_session_free(lumi_session* s) {
     for (auto& g : s->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
     void* dev[] = {s->score_logits, s->gemm_counters, s->gemm_scratch, s->h, s->xprev, s->bprev, s->cum, s->kv_pool, s->page_table, s->kv_pos, s->x, s->proj, s->y32, s->logits,
                    s->act_hi, s->act_lo, s->tok_cur, s->finished, s->out_len, s->ctl, s->gen_out, s->prompt_dev, s->gen_dump,
-                   s->pf_x, s->pf_proj, s->pf_rb, s->pf_rc, s->pf_hi, s->pf_lo, s->slot_buf,
+                   s->pf_x, s->pf_proj, s->pf_rb, s->pf_rc, s->pf_hi, s->pf_lo, s->slot_buf, s->xn_hi, s->xn_lo, s->ssq, s->attn_part, s->attn_part_count,
                    s->b1_layers, s->b1_grid_ctl, s->b1_amax_val, s->b1_amax_idx, s->b1_timing, s->b1_tagged};
     for (void* p : dev) if (p) cudaFree(p);
     if (s->ctl_host) cudaFreeHost(s->ctl_host);
@@ -386,27 +386,19 @@ static int32_t session_alloc(lumi_session* s) {
     }
     if (na > 0) {
         if (s->max_tokens_kv <= 0) return fail(LUMI_E_INVALID, "max_tokens_kv must be > 0 for a model with attention layers");
-        // the attention kernel keeps one score per cached token and query head of a group in shared memory
-        // (227 KB per CTA): the longest context a layer can attend to is bounded by that
-        {
-            const int hd = c.attn_head_dim(), hpk = c.attn_n_heads / std::max(1, c.attn_kv_heads);
-            const long fixed = (long)5 * hd * hpk * 4 + 1024;
-            const long max_ctx = (227 * 1024 - fixed) / (4L * hpk);
-            int ai = 0;
-            for (const Layer& L : s->m->layers) {
-                if (!L.is_attn) continue;
-                const int ctx = L.window > 0 ? std::min(L.window, s->max_tokens_kv) : s->max_tokens_kv;
-                if (ctx > max_ctx)
-                    return fail(LUMI_E_UNSUPPORTED, "attention layer %d would attend to %d cached tokens; with %d query heads per kv head the kernel holds at most %ld "
-                                "(give the layer a sliding window or a smaller max_tokens_kv)", ai, ctx, hpk, max_ctx);
-                ++ai;
-            }
-        }
         s->pages_per_seq = (s->max_tokens_kv + kPageTokens - 1) / kPageTokens;
         const size_t esz = s->m->wdtype == LUMI_DTYPE_BF16 ? 2 : 4;
         s->kv_layer_bytes = B * s->pages_per_seq * 2 * kPageTokens * (size_t)c.kv_dim() * esz;
         LUMI_CUDA(cudaMalloc(&s->kv_pool, s->kv_layer_bytes * na));
         LUMI_CUDA(cudaMalloc(&s->page_table, sizeof(int32_t) * B * s->pages_per_seq));
+        // partial results of an attention context split over several CTAs: used only while batch x KV heads is below two
+        // CTAs per SM, so a fixed number of (row, KV head) units is enough
+        {
+            const size_t pw = (size_t)(c.attn_n_heads / std::max(1, c.attn_kv_heads)) * (c.attn_head_dim() + 2);
+            LUMI_CUDA(cudaMalloc(&s->attn_part, sizeof(float) * kAttnPartUnits * kAttnPartSlices * pw));
+            LUMI_CUDA(cudaMalloc(&s->attn_part_count, sizeof(int32_t) * kAttnPartUnits));
+            LUMI_CUDA(cudaMemset(s->attn_part_count, 0, sizeof(int32_t) * kAttnPartUnits));
+        }
         std::vector<int32_t> pt(B * s->pages_per_seq);
         for (size_t i = 0; i < pt.size(); ++i) pt[i] = (int32_t)i;       // slot b owns pages [b*pps, (b+1)*pps)
         LUMI_CUDA(cudaMemcpy(s->page_table, pt.data(), pt.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
@@ -431,6 +423,15 @@ static int32_t session_alloc(lumi_session* s) {
         LUMI_CUDA(cudaMalloc(&s->act_lo, sizeof(__nv_bfloat16) * rows * kmax));
         LUMI_CUDA(cudaMemset(s->act_hi, 0, sizeof(__nv_bfloat16) * rows * kmax));
         LUMI_CUDA(cudaMemset(s->act_lo, 0, sizeof(__nv_bfloat16) * rows * kmax));
+        // the residual stream times the next norm's weights (bf16 halves) and its per-row partial sums of squares:
+        // written by the epilogue of the product that updates the residual, read by the next product
+        s->ssq_stride = (c.d_model + 31) / 32;
+        LUMI_CUDA(cudaMalloc(&s->xn_hi, sizeof(__nv_bfloat16) * rows * c.d_model));
+        LUMI_CUDA(cudaMalloc(&s->xn_lo, sizeof(__nv_bfloat16) * rows * c.d_model));
+        LUMI_CUDA(cudaMemset(s->xn_hi, 0, sizeof(__nv_bfloat16) * rows * c.d_model));
+        LUMI_CUDA(cudaMemset(s->xn_lo, 0, sizeof(__nv_bfloat16) * rows * c.d_model));
+        LUMI_CUDA(cudaMalloc(&s->ssq, sizeof(float) * rows * s->ssq_stride));
+        LUMI_CUDA(cudaMemset(s->ssq, 0, sizeof(float) * rows * s->ssq_stride));
     }
     LUMI_CUDA(cudaMalloc(&s->tok_cur, sizeof(uint32_t) * B));
     LUMI_CUDA(cudaMalloc(&s->finished, sizeof(int32_t) * B));
@@ -554,6 +555,10 @@ struct StepPlan {
     int row0 = 0;                                                 // first sequence of this plan's rows (B of them)
     cudaStream_t st_hi = nullptr, st_lo = nullptr;               // GEMM / norm stream and state-step stream (both = session stream unless two lanes run)
     int fam = FAM_EMBED;                                          // family of the launches that follow
+    // tensor-core path: the residual rows times the next norm's weights (bf16 halves) and their partial sums of squares are
+    // already in xn_hi / xn_lo / ssq — left there by the epilogue of the product that last updated the residual
+    bool xn_ready = false;
+    int ssq_parts = 0;
     std::vector<std::pair<int, cudaEvent_t>>* prof = nullptr;     // profiling: an event before every launch
 };
 
@@ -576,8 +581,11 @@ bool use_tc(const lumi_session* s, int B) {
     return s->opt_gemm == 2 || B > 8;
 }
 
+// norm_in: the input is RMSNorm(residual; gamma) and the tensor-core path takes it in the folded form (rows of x * gamma
+// in xn_hi / xn_lo, scale applied in the product's epilogue).  gamma_next != null: the output IS the residual stream;
+// the tensor-core product also leaves residual * gamma_next and its sums of squares for the next product.
 int32_t linear(StepPlan& p, const DevTensor& W, const float* in32, int K, float* out, int ldd, const float* residual,
-               const float* gamma, int act, int N) {
+               const float* gamma, int act, int N, bool norm_in = false, const float* gamma_next = nullptr) {
     lumi_session* s = p.s;
     const Config& c = s->m->cfg;
     if (!p.tc) {
@@ -588,13 +596,51 @@ int32_t linear(StepPlan& p, const DevTensor& W, const float* in32, int K, float*
     }
     // tensor-core path: the caller has already put the bf16 halves of the input into this plan's
     // region of act_hi / act_lo (rows packed with leading dimension K from the region's start)
-    const size_t aoff = (size_t)p.row0 * s->act_ld;
-    GemmArgs g{s->act_hi + aoff, s->opt_split ? s->act_lo + aoff : nullptr, (const __nv_bfloat16*)W.p, out, ldd, p.B, N, K,
+    const size_t aoff = (size_t)p.row0 * s->act_ld, xoff = (size_t)p.row0 * c.d_model, soff = (size_t)p.row0 * s->ssq_stride;
+    const __nv_bfloat16* ahi = norm_in ? s->xn_hi + xoff : s->act_hi + aoff;
+    const __nv_bfloat16* alo = norm_in ? s->xn_lo + xoff : s->act_lo + aoff;
+    GemmArgs g{ahi, s->opt_split ? alo : nullptr, (const __nv_bfloat16*)W.p, out, ldd, p.B, N, K,
                residual != nullptr ? 1 : 0, &s->ctl->status, s->gemm_counters + (p.row0 > 0 ? kGemmCounters : 0), kGemmCounters,
                s->gemm_scratch + (p.row0 > 0 ? kGemmScratchFloats : 0), kGemmScratchFloats};
+    if (norm_in) {
+        g.nf.ssq_in = s->ssq + soff; g.nf.ssq_parts = p.ssq_parts; g.nf.ssq_stride = s->ssq_stride;
+        g.nf.inv_k = (float)(1.0 / (double)K); g.nf.eps = c.eps;
+    }
+    if (gamma_next != nullptr) {
+        g.nf.gamma_next = gamma_next; g.nf.out_hi = s->xn_hi + xoff; g.nf.out_lo = s->opt_split ? s->xn_lo + xoff : nullptr;
+        g.nf.ssq_out = s->ssq + soff; g.nf.ssq_stride = s->ssq_stride;
+    }
     mark(p);
     LUMI_TRY(launch_gemm_tcgen05(g, p.st_hi));
+    if (gamma_next != nullptr) { p.xn_ready = true; p.ssq_parts = (N + 31) / 32; }      // one partial sum per 32 columns, whatever the tile width
     return LUMI_OK;
+}
+
+// Tensor-core path: makes sure xn_hi / xn_lo / ssq hold residual * gamma for the norm that comes next (only the first
+// norm of a step needs a kernel of its own; afterwards the products' epilogues keep them current).
+int32_t ensure_norm_input(StepPlan& p, const float* x, const float* gamma) {
+    lumi_session* s = p.s;
+    const Config& c = s->m->cfg;
+    if (p.xn_ready) return LUMI_OK;
+    const size_t xoff = (size_t)p.row0 * c.d_model, soff = (size_t)p.row0 * s->ssq_stride;
+    const int fam = p.fam;
+    p.fam = FAM_NORM;
+    mark(p);
+    LUMI_CUDA(launch_norm_split(x, gamma, s->xn_hi + xoff, s->opt_split ? s->xn_lo + xoff : nullptr, p.B, c.d_model, c.eps, p.st_hi,
+                                s->ssq + soff, s->ssq_stride));
+    p.fam = fam;
+    p.xn_ready = true;
+    p.ssq_parts = 1;
+    return LUMI_OK;
+}
+
+// The weights of the norm that reads the residual stream after layer `li`: the next layer's first norm, or the final norm.
+const float* next_norm_gamma(const lumi_session* s, size_t li) {
+    if (li + 1 < s->m->layers.size()) {
+        const Layer& nx = s->m->layers[li + 1];
+        return nx.is_attn ? nx.a.attn_norm_g : nx.m.norm_g;
+    }
+    return s->m->final_norm_g;
 }
 
 // One Mamba block for rows [p.row0, p.row0 + p.B).  With two lanes running, `between` (if given) is
@@ -608,13 +654,11 @@ int32_t mamba_block(StepPlan& p, const Layer& L, cudaEvent_t ev_gemm_done = null
     float* x = s->x + r0 * D;
     float* proj = s->proj + r0 * R;
     float* y32 = s->y32 ? s->y32 + r0 * DI : nullptr;
-    if (p.tc) {
-        p.fam = FAM_NORM;
-        mark(p);
-        LUMI_CUDA(launch_norm_split(x, L.m.norm_g, s->act_hi + aoff, s->opt_split ? s->act_lo + aoff : nullptr, p.B, D, c.eps, p.st_hi));
-    }
+    const size_t li = (size_t)(&L - s->m->layers.data());
+    if (p.tc) LUMI_TRY(ensure_norm_input(p, x, L.m.norm_g));
     p.fam = FAM_IN_PROJ;
-    LUMI_TRY(linear(p, L.m.in_proj, x, D, proj, R, nullptr, L.m.norm_g, 0, R));
+    LUMI_TRY(linear(p, L.m.in_proj, x, D, proj, R, nullptr, L.m.norm_g, 0, R, true));
+    p.xn_ready = false;                                   // consumed; the out_proj below renews it
     if (ev_gemm_done) {
         LUMI_CUDA(cudaEventRecord(ev_gemm_done, p.st_hi));
         LUMI_CUDA(cudaStreamWaitEvent(p.st_lo, ev_gemm_done, 0));
@@ -638,7 +682,7 @@ int32_t mamba_block(StepPlan& p, const Layer& L, cudaEvent_t ev_gemm_done = null
         LUMI_CUDA(cudaStreamWaitEvent(p.st_hi, ev_ssm_done, 0));
     }
     p.fam = FAM_OUT_PROJ;
-    LUMI_TRY(linear(p, L.m.out_proj, y32, DI, x, D, x, nullptr, 0, D));
+    LUMI_TRY(linear(p, L.m.out_proj, y32, DI, x, D, x, nullptr, 0, D, false, next_norm_gamma(s, li)));
     return LUMI_OK;
 }
 
@@ -646,12 +690,12 @@ int32_t attention_block(StepPlan& p, const Layer& L) {
     lumi_session* s = p.s;
     const Config& c = s->m->cfg;
     const int D = c.d_model, KV = c.kv_dim(), Q = D + 2 * KV, MLP = c.mlp_dim();
+    const size_t li = (size_t)(&L - s->m->layers.data());
     p.fam = FAM_ATTN;
-    if (p.tc) {
-        mark(p);
-        LUMI_CUDA(launch_norm_split(s->x, L.a.attn_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, D, c.eps, p.st_hi));
-    }
-    LUMI_TRY(linear(p, L.a.qkv, s->x, D, s->proj, Q, nullptr, L.a.attn_norm_g, 0, Q));
+    if (p.tc) LUMI_TRY(ensure_norm_input(p, s->x, L.a.attn_norm_g));
+    p.fam = FAM_ATTN;
+    LUMI_TRY(linear(p, L.a.qkv, s->x, D, s->proj, Q, nullptr, L.a.attn_norm_g, 0, Q, true));
+    p.xn_ready = false;
     AttnArgs a{};
     a.qkv = s->proj; a.ldq = Q;
     a.pool = (char*)s->kv_pool + (size_t)L.kind_idx * s->kv_layer_bytes;
@@ -666,22 +710,25 @@ int32_t attention_block(StepPlan& p, const Layer& L) {
     if (a.max_tokens > s->max_tokens_kv) a.max_tokens = s->max_tokens_kv;
     a.rope_base = c.attn_rope_base;
     a.ctl = s->ctl;
+    if ((long)p.B * c.attn_kv_heads <= kAttnPartUnits) {      // few rows: the context may be split over CTAs
+        a.part = s->attn_part; a.part_count = s->attn_part_count;
+        a.max_ctx_hint = L.window > 0 ? std::min(L.window, a.max_tokens) : a.max_tokens;
+    }
     mark(p);
     cudaError_t e = launch_attention_decode(a, p.st_hi);
     if (e == cudaErrorInvalidValue) return fail(LUMI_E_UNSUPPORTED, "attention head_dim %d with %d query heads per kv head is not built", a.head_dim, a.n_heads / a.kv_heads);
     LUMI_CUDA(e);
-    LUMI_TRY(linear(p, L.a.o, s->y32, D, s->x, D, s->x, nullptr, 0, D));
+    LUMI_TRY(linear(p, L.a.o, s->y32, D, s->x, D, s->x, nullptr, 0, D, false, L.a.mlp_norm_g));
     // sigmoid-gated MLP (model.rs:546-555)
     if (p.tc) {
-        mark(p);
-        LUMI_CUDA(launch_norm_split(s->x, L.a.mlp_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, D, c.eps, p.st_hi));
-        LUMI_TRY(linear(p, L.a.gate_up, nullptr, D, s->proj, 2 * MLP, nullptr, nullptr, 0, 2 * MLP));
+        LUMI_TRY(linear(p, L.a.gate_up, nullptr, D, s->proj, 2 * MLP, nullptr, nullptr, 0, 2 * MLP, true));
+        p.xn_ready = false;
         mark(p);
         LUMI_CUDA(launch_gate_mul(s->proj, 2 * MLP, nullptr, s->act_hi, s->opt_split ? s->act_lo : nullptr, p.B, MLP, p.st_hi));
     } else {
         LUMI_TRY(linear(p, L.a.gate_up, s->x, D, s->y32, MLP, nullptr, L.a.mlp_norm_g, 1, MLP));
     }
-    LUMI_TRY(linear(p, L.a.down, s->y32, MLP, s->x, D, s->x, nullptr, 0, D));
+    LUMI_TRY(linear(p, L.a.down, s->y32, MLP, s->x, D, s->x, nullptr, 0, D, false, next_norm_gamma(s, li)));
     return LUMI_OK;
 }
 
@@ -741,14 +788,15 @@ int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches,
             LUMI_CUDA(cudaStreamWaitEvent(s->stream, s->ev_join[i], 0));
             p.n += lane[i].n;
         }
+        // both lanes left their rows of the folded-norm input behind, in the same per-strip form
+        p.xn_ready = lane[0].xn_ready && lane[1].xn_ready && lane[0].ssq_parts == lane[1].ssq_parts;
+        p.ssq_parts = lane[0].ssq_parts;
     }
     if (with_head) {
         p.fam = FAM_HEAD;
-        if (p.tc) {
-            mark(p);
-            LUMI_CUDA(launch_norm_split(s->x, s->m->final_norm_g, s->act_hi, s->opt_split ? s->act_lo : nullptr, B, c.d_model, c.eps, s->stream));
-        }
-        LUMI_TRY(linear(p, s->m->embedding, s->x, c.d_model, s->logits, c.vocab, nullptr, s->m->final_norm_g, 0, c.vocab));
+        if (p.tc) LUMI_TRY(ensure_norm_input(p, s->x, s->m->final_norm_g));
+        p.fam = FAM_HEAD;
+        LUMI_TRY(linear(p, s->m->embedding, s->x, c.d_model, s->logits, c.vocab, nullptr, s->m->final_norm_g, 0, c.vocab, true));
         p.fam = FAM_SAMPLE;
         mark(p);
         LUMI_CUDA(launch_sample(s->logits, B, c.vocab, s->ctl, s->tok_cur, s->finished, s->out_len, s->stream));
@@ -1263,6 +1311,9 @@ extern "C" int32_t lumi_generate(lumi_session* s, const uint32_t* prompts, int32
         const int64_t per_seq = (int64_t)s->m->n_mamba * 2 * 4 *
                                 ((int64_t)state_h_per_seq(cf) + cf.d_inner() + cf.n_heads * cf.d_state + cf.n_heads * (cf.d_state / 2));
         stats->bytes_per_step = s->m->weight_bytes + (int64_t)batch * per_seq;
+        const int64_t steps = std::max(0, n_new - 1);
+        stats->achieved_gbps = (steps > 0 && stats->ms_decode > 0.f) ? (float)((double)stats->bytes_per_step * (double)steps / ((double)stats->ms_decode * 1e-3) / 1e9) : 0.f;
+        stats->waves = 1;
     }
     return check_status(s);
 }

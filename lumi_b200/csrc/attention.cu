@@ -1,7 +1,8 @@
 // Single-token GQA attention over a paged KV cache, replacing AttentionBlock::forward_step's
 // cache append + softmax(q K^T / sqrt(d)) V (inference/src/model.rs:508-538, KvCache::append
-// :133-152).  One CTA per (sequence, KV head) serves all query heads of that group, so K and V
-// are read once.  The sliding window of the reference (keep the last `window` tokens) is a ring:
+// :133-152).  A CTA serves all query heads of a KV head's group, so K and V are read once; the cached
+// tokens are walked in tiles with a running softmax, and split over several CTAs when the batch alone
+// would not fill the GPU.  The sliding window of the reference (keep the last `window` tokens) is a ring:
 // token t lives in slot t % window.  Optional rotary embedding (extension, off by default).
 #include "internal.h"
 
@@ -33,15 +34,30 @@ __device__ __forceinline__ KT* kv_ptr(KT* pool, const int32_t* pt, int slot, int
     return pool + (((size_t)page * 2 + sel) * kPageTokens + (slot % kPageTokens)) * kv_dim;
 }
 
+constexpr int kAttnTile = 256;            // cached tokens scored per pass: the shared-memory footprint does not depend on the context
+constexpr int kAttnMaxSplits = 16;
+
+// Work is split three ways: token row (x), KV head (y) and, when rows x KV heads would not fill the GPU, a
+// contiguous slice of the cached tokens (z).  Every CTA walks its slice in tiles of kAttnTile tokens with a running
+// maximum / sum / context (the usual rescaling when the maximum grows), so the softmax of inference/src/model.rs:535
+// is evaluated without ever holding more than one tile of scores.  With one slice the CTA normalises and writes the
+// context itself.  With several, each parks (max, sum, unnormalised context) per query head in `part`, and the CTA
+// that arrives last at the (row, KV head) counter merges the slices in slice order — a fixed order, so the result
+// does not depend on timing; nobody waits for anybody.
+// The new token's K / V row is appended to the cache by slice 0; every slice reads that row from its own
+// shared-memory copy (rounded through the cache's element type, i.e. the value the cache will hold) instead of from
+// the cache, so no CTA depends on another CTA's store.
 template <typename KT, int HD, int HPK>
 __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) {
-    extern __shared__ float smem[];
-    float* qs = smem;                      // [HD][HPK]   (rotated q, head-interleaved)
-    float* red = qs + HD * HPK;            // [4 warps][HPK * HD] cross-warp reduction / scratch
-    float* sc = red + 4 * HPK * HD;        // [HPK][T]
+    __shared__ float qs[HD * HPK];                       // rotated q, head-interleaved [HD][HPK]
+    __shared__ float red[4 * HPK * HD];                  // cross-warp reductions
+    __shared__ float sc[HPK * kAttnTile];                // scores / weights of the current tile
+    __shared__ __align__(16) KT knew[HD], vnew[HD];      // the new token's rows as the cache will hold them
     __shared__ float hmax[HPK], hsum[HPK];
+    __shared__ int32_t pages[64];
+    __shared__ int is_last;
 
-    const int r = blockIdx.y, kvh = blockIdx.x;          // r: token row (decode: the sequence)
+    const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
     const int b = a.b0 + r / a.rows_per_seq;             // sequence slot
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int D = a.n_heads * HD, KV = a.kv_heads * HD;
@@ -59,8 +75,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
         return;
     }
 
-    // rotary embedding on interleaved pairs at the absolute position (extension), then stage q and
-    // append the new K / V row
+    // rotary embedding on interleaved pairs at the absolute position (extension), then stage q and the new K / V row
     for (int i = tid; i < HPK * HD / 2; i += 128) {
         const int hq = i / (HD / 2), pr = i % (HD / 2);
         float q0 = q[hq * HD + 2 * pr], q1 = q[hq * HD + 2 * pr + 1];
@@ -87,33 +102,36 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
             float r1 = __fadd_rn(__fmul_rn(sa, k0), __fmul_rn(ca, k1));
             k0 = r0; k1 = r1;
         }
-        KT* kd = kv_ptr(pool, pt, slot_new, 0, KV) + kvh * HD;
-        KT* vd = kv_ptr(pool, pt, slot_new, 1, KV) + kvh * HD;
-        KvIo<KT>::st(kd + 2 * pr, k0);
-        KvIo<KT>::st(kd + 2 * pr + 1, k1);
-        KvIo<KT>::st(vd + 2 * pr, vn[2 * pr]);
-        KvIo<KT>::st(vd + 2 * pr + 1, vn[2 * pr + 1]);
+        KvIo<KT>::st(&knew[2 * pr], k0);
+        KvIo<KT>::st(&knew[2 * pr + 1], k1);
+        KvIo<KT>::st(&vnew[2 * pr], vn[2 * pr]);
+        KvIo<KT>::st(&vnew[2 * pr + 1], vn[2 * pr + 1]);
+        if (split == 0) {                                // KvCache::append (model.rs:133-152)
+            KT* kd = kv_ptr(pool, pt, slot_new, 0, KV) + kvh * HD;
+            KT* vd = kv_ptr(pool, pt, slot_new, 1, KV) + kvh * HD;
+            kd[2 * pr] = knew[2 * pr]; kd[2 * pr + 1] = knew[2 * pr + 1];
+            vd[2 * pr] = vnew[2 * pr]; vd[2 * pr + 1] = vnew[2 * pr + 1];
+        }
     }
     if (a.phase == 1) return;                            // append only
+    const int local_slot = a.phase == 2 ? -1 : slot_new; // attend only: every row is already in the cache
+    const bool pages_ok = a.pages_per_seq <= 64;
+    if (pages_ok) for (int i = tid; i < a.pages_per_seq; i += 128) pages[i] = pt[i];
     __syncthreads();
 
-    // scores: a cached K row is HD * sizeof(KT) bytes = LPR lanes x 16 bytes, so one warp-wide 16-byte load
-    // covers RPI rows; UNR such loads are in flight per lane.  Lane (rg, sub) multiplies its EPL elements of
-    // row rg with the same elements of the HPK query heads (kept in registers) and the LPR partial sums of a
-    // row are added by a xor tree.
+    // A cached K row is HD * sizeof(KT) bytes = LPR lanes x 16 bytes, so one warp-wide 16-byte load covers RPI rows;
+    // UNR such loads are in flight per lane.  Lane (rg, sub) multiplies its EPL elements of row rg with the same
+    // elements of the HPK query heads (kept in registers) and the LPR partial sums of a row are added by a xor tree.
     constexpr int EPL = 16 / (int)sizeof(KT);          // elements per lane per row
     constexpr int LPR = HD / EPL;                      // lanes per row
     constexpr int RPI = 32 / LPR;                      // rows per warp-wide load
     constexpr int UNR = 4;
     static_assert(LPR >= 1 && LPR <= 32 && (32 % LPR) == 0, "a row must be 16 to 512 bytes");
     const int rg = lane / LPR, sub = lane % LPR;
-    __shared__ int32_t pages[64];
-    const bool pages_ok = a.pages_per_seq <= 64;
-    if (pages_ok) for (int i = tid; i < a.pages_per_seq; i += 128) pages[i] = pt[i];
-    __syncthreads();
-    auto row_ptr = [&](int t, int sel) -> const KT* {
+    auto load_row = [&](int t, int sel) -> uint4 {
+        if (t == local_slot) return reinterpret_cast<const uint4*>(sel == 0 ? knew : vnew)[sub];
         const int page = pages_ok ? pages[t / kPageTokens] : pt[t / kPageTokens];
-        return pool + (((size_t)page * 2 + sel) * kPageTokens + (t % kPageTokens)) * KV + kvh * HD + sub * EPL;
+        return *reinterpret_cast<const uint4*>(pool + (((size_t)page * 2 + sel) * kPageTokens + (t % kPageTokens)) * KV + kvh * HD + sub * EPL);
     };
     auto unpack = [](const uint4& raw, float (&f)[EPL]) {
         if constexpr (sizeof(KT) == 4) {
@@ -130,62 +148,109 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
 #pragma unroll
         for (int e = 0; e < EPL; ++e) qr[hq][e] = qs[(sub * EPL + e) * HPK + hq];
     const float scale = (float)(1.0 / sqrt((double)HD));            // model.rs:530
-    float lmax[HPK];
+
+    // this CTA's slice of the cached tokens
+    const int per = (T + nsplit - 1) / nsplit;
+    const int tb = split * per, te = min(T, tb + per);
+    float m_run[HPK], lsum[HPK], ctx[HPK][EPL];        // running maximum (uniform), this thread's share of the sum and the context
 #pragma unroll
-    for (int hq = 0; hq < HPK; ++hq) lmax[hq] = -INFINITY;
-    for (int t0 = warp * RPI; t0 < T; t0 += 4 * RPI * UNR) {
-        uint4 raw[UNR];
+    for (int hq = 0; hq < HPK; ++hq) {
+        m_run[hq] = -INFINITY; lsum[hq] = 0.f;
 #pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            const int t = t0 + u * 4 * RPI + rg;
-            raw[u] = t < T ? *reinterpret_cast<const uint4*>(row_ptr(t, 0)) : make_uint4(0u, 0u, 0u, 0u);
-        }
+        for (int e = 0; e < EPL; ++e) ctx[hq][e] = 0.f;
+    }
+    for (int t00 = tb; t00 < te; t00 += kAttnTile) {
+        const int tn = min(kAttnTile, te - t00);        // tokens of this tile
+        float lmax[HPK];
 #pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            const int t = t0 + u * 4 * RPI + rg;
-            float kf[EPL];
-            unpack(raw[u], kf);
-            float acc[HPK];
+        for (int hq = 0; hq < HPK; ++hq) lmax[hq] = -INFINITY;
+        for (int t0 = warp * RPI; t0 < tn; t0 += 4 * RPI * UNR) {
+            uint4 raw[UNR];
 #pragma unroll
-            for (int hq = 0; hq < HPK; ++hq) {
-                acc[hq] = 0.f;
-#pragma unroll
-                for (int e = 0; e < EPL; ++e) acc[hq] = fmaf(qr[hq][e], kf[e], acc[hq]);
-#pragma unroll
-                for (int o = LPR / 2; o > 0; o >>= 1) acc[hq] += __shfl_xor_sync(0xffffffffu, acc[hq], o);
+            for (int u = 0; u < UNR; ++u) {
+                const int t = t0 + u * 4 * RPI + rg;
+                raw[u] = t < tn ? load_row(t00 + t, 0) : make_uint4(0u, 0u, 0u, 0u);
             }
-            if (sub == 0 && t < T) {
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+                const int t = t0 + u * 4 * RPI + rg;
+                float kf[EPL];
+                unpack(raw[u], kf);
+                float acc[HPK];
 #pragma unroll
                 for (int hq = 0; hq < HPK; ++hq) {
-                    const float sv = __fmul_rn(acc[hq], scale);     // model.rs:532
-                    sc[hq * T + t] = sv;
-                    lmax[hq] = fmaxf(lmax[hq], sv);
+                    acc[hq] = 0.f;
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) acc[hq] = fmaf(qr[hq][e], kf[e], acc[hq]);
+#pragma unroll
+                    for (int o = LPR / 2; o > 0; o >>= 1) acc[hq] += __shfl_xor_sync(0xffffffffu, acc[hq], o);
+                }
+                if (sub == 0 && t < tn) {
+#pragma unroll
+                    for (int hq = 0; hq < HPK; ++hq) {
+                        const float sv = __fmul_rn(acc[hq], scale);     // model.rs:532
+                        sc[hq * kAttnTile + t] = sv;
+                        lmax[hq] = fmaxf(lmax[hq], sv);
+                    }
                 }
             }
         }
-    }
-    // block max per head
-#pragma unroll
-    for (int hq = 0; hq < HPK; ++hq) {
-        float v = lmax[hq];
-        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-        if (lane == 0) red[warp * HPK + hq] = v;
-    }
-    __syncthreads();
-    if (tid < HPK) hmax[tid] = fmaxf(fmaxf(red[tid], red[HPK + tid]), fmaxf(red[2 * HPK + tid], red[3 * HPK + tid]));
-    __syncthreads();
-    float lsum[HPK];
-#pragma unroll
-    for (int hq = 0; hq < HPK; ++hq) lsum[hq] = 0.f;
-    for (int t = tid; t < T; t += 128) {
+        // tile maximum per head, then the new running maximum and the factor that brings the old sums to it
 #pragma unroll
         for (int hq = 0; hq < HPK; ++hq) {
-            float e = expf(__fsub_rn(sc[hq * T + t], hmax[hq]));    // model.rs:535
-            sc[hq * T + t] = e;
-            lsum[hq] += e;
+            float v = lmax[hq];
+            for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+            if (lane == 0) red[warp * HPK + hq] = v;
         }
+        __syncthreads();
+        if (tid < HPK) {
+            hmax[tid] = fmaxf(fmaxf(red[tid], red[HPK + tid]), fmaxf(red[2 * HPK + tid], red[3 * HPK + tid]));
+        }
+        __syncthreads();
+#pragma unroll
+        for (int hq = 0; hq < HPK; ++hq) {
+            const float mn = fmaxf(m_run[hq], hmax[hq]);
+            const float f = m_run[hq] == -INFINITY ? 0.f : expf(__fsub_rn(m_run[hq], mn));
+            m_run[hq] = mn;
+            lsum[hq] *= f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) ctx[hq][e] *= f;
+        }
+        for (int t = tid; t < tn; t += 128) {
+#pragma unroll
+            for (int hq = 0; hq < HPK; ++hq) {
+                const float e = expf(__fsub_rn(sc[hq * kAttnTile + t], m_run[hq]));    // model.rs:535
+                sc[hq * kAttnTile + t] = e;
+                lsum[hq] += e;
+            }
+        }
+        __syncthreads();
+        // context: same lane mapping over the V rows; a lane accumulates its EPL dims over the rows of its row group
+        for (int t0 = warp * RPI; t0 < tn; t0 += 4 * RPI * UNR) {
+            uint4 raw[UNR];
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+                const int t = t0 + u * 4 * RPI + rg;
+                raw[u] = t < tn ? load_row(t00 + t, 1) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+                const int t = t0 + u * 4 * RPI + rg;
+                if (t < tn) {
+                    float vf[EPL];
+                    unpack(raw[u], vf);
+#pragma unroll
+                    for (int hq = 0; hq < HPK; ++hq) {
+                        const float p = sc[hq * kAttnTile + t];
+#pragma unroll
+                        for (int e = 0; e < EPL; ++e) ctx[hq][e] = fmaf(p, vf[e], ctx[hq][e]);
+                    }
+                }
+            }
+        }
+        __syncthreads();                                 // sc and red are reused by the next tile
     }
-    __syncthreads();   // red is reused below
+    // block totals: the sums by a xor tree and the four warps in order; the context likewise
 #pragma unroll
     for (int hq = 0; hq < HPK; ++hq) {
         float v = lsum[hq];
@@ -195,43 +260,12 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     __syncthreads();
     if (tid < HPK) hsum[tid] = (red[tid] + red[HPK + tid]) + (red[2 * HPK + tid] + red[3 * HPK + tid]);
     __syncthreads();
-
-    // context: same lane mapping over the V rows; a lane accumulates its EPL dims over the rows of its row
-    // group, then the RPI row groups are added by a xor tree and the four warps through shared memory
-    float ctx[HPK][EPL];
-#pragma unroll
-    for (int hq = 0; hq < HPK; ++hq)
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) ctx[hq][e] = 0.f;
-    for (int t0 = warp * RPI; t0 < T; t0 += 4 * RPI * UNR) {
-        uint4 raw[UNR];
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            const int t = t0 + u * 4 * RPI + rg;
-            raw[u] = t < T ? *reinterpret_cast<const uint4*>(row_ptr(t, 1)) : make_uint4(0u, 0u, 0u, 0u);
-        }
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            const int t = t0 + u * 4 * RPI + rg;
-            if (t < T) {
-                float vf[EPL];
-                unpack(raw[u], vf);
-#pragma unroll
-                for (int hq = 0; hq < HPK; ++hq) {
-                    const float p = __fdiv_rn(sc[hq * T + t], hsum[hq]);
-#pragma unroll
-                    for (int e = 0; e < EPL; ++e) ctx[hq][e] = fmaf(p, vf[e], ctx[hq][e]);
-                }
-            }
-        }
-    }
 #pragma unroll
     for (int hq = 0; hq < HPK; ++hq)
 #pragma unroll
         for (int e = 0; e < EPL; ++e)
 #pragma unroll
             for (int o = LPR; o < 32; o <<= 1) ctx[hq][e] += __shfl_xor_sync(0xffffffffu, ctx[hq][e], o);
-    __syncthreads();
     if (rg == 0) {
 #pragma unroll
         for (int hq = 0; hq < HPK; ++hq)
@@ -239,8 +273,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
             for (int e = 0; e < EPL; ++e) red[warp * HPK * HD + hq * HD + sub * EPL + e] = ctx[hq][e];
     }
     __syncthreads();
-    for (int i = tid; i < HPK * HD; i += 128) {
-        float v = (red[i] + red[HPK * HD + i]) + (red[2 * HPK * HD + i] + red[3 * HPK * HD + i]);
+    auto emit = [&](int i, float v) {
         const size_t o = (size_t)r * D + (size_t)kvh * HPK * HD + i;
         if (a.ctx32) a.ctx32[o] = v;
         if (a.chi) {
@@ -249,20 +282,70 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
             a.chi[o] = hh;
             if (a.clo) a.clo[o] = ll;
         }
+    };
+    if (nsplit == 1) {
+        for (int i = tid; i < HPK * HD; i += 128) {
+            const float v = (red[i] + red[HPK * HD + i]) + (red[2 * HPK * HD + i] + red[3 * HPK * HD + i]);
+            emit(i, __fdiv_rn(v, hsum[i / HD]));
+        }
+        return;
     }
+    // several slices: park this slice's (max, sum, context) and let the last arriver merge them in slice order
+    constexpr int PW = HPK * (HD + 2);                   // floats per slice
+    float* mine = a.part + ((size_t)(r * a.kv_heads + kvh) * kAttnMaxSplits + split) * PW;
+    for (int i = tid; i < HPK * HD; i += 128)
+        mine[2 * HPK + i] = (red[i] + red[HPK * HD + i]) + (red[2 * HPK * HD + i] + red[3 * HPK * HD + i]);
+    if (tid < HPK) { mine[tid] = m_run[tid]; mine[HPK + tid] = hsum[tid]; }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int old = atomicAdd(a.part_count + r * a.kv_heads + kvh, 1);
+        is_last = old == nsplit - 1;
+        if (is_last) a.part_count[r * a.kv_heads + kvh] = 0;             // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const float* all = a.part + (size_t)(r * a.kv_heads + kvh) * kAttnMaxSplits * PW;
+    for (int i = tid; i < HPK * HD; i += 128) {
+        const int hq = i / HD;
+        float m = -INFINITY;
+        for (int sp = 0; sp < nsplit; ++sp) m = fmaxf(m, __ldcg(all + (size_t)sp * PW + hq));
+        float den = 0.f, num = 0.f;
+        for (int sp = 0; sp < nsplit; ++sp) {
+            const float ms = __ldcg(all + (size_t)sp * PW + hq);
+            const float f = ms == -INFINITY ? 0.f : expf(__fsub_rn(ms, m));
+            den = fmaf(f, __ldcg(all + (size_t)sp * PW + HPK + hq), den);
+            num = fmaf(f, __ldcg(all + (size_t)sp * PW + 2 * HPK + i), num);
+        }
+        emit(i, __fdiv_rn(num, den));
+    }
+}
+
+static int attn_sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
 }
 
 template <typename KT, int HD, int HPK>
 cudaError_t launch_t(const AttnArgs& a, cudaStream_t st) {
-    const int cap = a.window > 0 ? (a.window < a.max_tokens ? a.window : a.max_tokens) : a.max_tokens;
-    size_t smem = sizeof(float) * ((size_t)HD * HPK + 4 * HPK * HD + (size_t)HPK * cap);
-    auto kern = attn_decode_kernel<KT, HD, HPK>;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
+    // slices of the context: enough CTAs for two per SM, at least one tile each, and only where the caller gave
+    // room for the partial results (decode); the batched prefill has rows to spare
+    int nsplit = 1;
+    if (a.part != nullptr && a.part_count != nullptr && a.phase == 0) {
+        const long units = (long)a.B * a.kv_heads;
+        nsplit = (int)((2L * attn_sm_count() + units - 1) / units);
+        const int by_len = (a.max_ctx_hint + kAttnTile - 1) / kAttnTile;
+        if (nsplit > by_len) nsplit = by_len;
+        if (nsplit > kAttnMaxSplits) nsplit = kAttnMaxSplits;
+        if (nsplit < 1) nsplit = 1;
     }
-    dim3 grid(a.kv_heads, a.B);
-    kern<<<grid, 128, smem, st>>>(a, reinterpret_cast<KT*>(a.pool));
+    dim3 grid(a.B, a.kv_heads, nsplit);
+    attn_decode_kernel<KT, HD, HPK><<<grid, 128, 0, st>>>(a, reinterpret_cast<KT*>(a.pool));
     return cudaGetLastError();
 }
 

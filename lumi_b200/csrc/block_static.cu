@@ -61,7 +61,7 @@ extern "C" int32_t lumi_mamba_block_static(lumi_model* m, int32_t layer, uint64_
     if (R + DI > kStaticMaxPerSeq)
         return fail(LUMI_E_UNSUPPORTED, "lumi_mamba_block_static: in_proj_out + d_inner = %d floats per sequence exceeds the fixed scratch of %d", R + DI, kStaticMaxPerSeq);
     if (!ssm_shape_supported(c.head_dim(), c.d_state)) return fail(LUMI_E_UNSUPPORTED, "head_dim %d / d_state %d not built", c.head_dim(), c.d_state);
-    LUMI_CUDA(cudaSetDevice(m->device));
+    LUMI_CUDA(cudaSetDevice(m->device));                    // stays current after the call (documented in the header)
     float* scratch = nullptr;
     LUMI_TRY(scratch_for_device(m->device, &scratch));      // first call per device: cudaGetSymbolAddress
     float* proj = scratch;                                   // [batch][R]
@@ -71,7 +71,11 @@ extern "C" int32_t lumi_mamba_block_static(lumi_model* m, int32_t layer, uint64_
     float* xd = reinterpret_cast<float*>(x);
     // Nothing in the scratch has to start at zero: in_proj writes every element of proj[0..batch) and the
     // state step every element of y[0..batch) before anything reads them.
+    // The two projections run on the multi-wave GEMV, which waits on nothing on the device: this call enqueues and
+    // returns without synchronising, so it could not report a device-side wait that gave up — it launches no kernel
+    // that has one.
     GemvArgs g1{xd, D, L.m.in_proj.p, L.m.in_proj.dtype, proj, R, nullptr, L.m.norm_g, batch, R, D, c.eps, 0};
+    g1.allow_preload = false;
     LUMI_CUDA(launch_gemv(g1, st));
     SsmArgs a{};
     a.proj = proj; a.ldp = R;
@@ -82,6 +86,7 @@ extern "C" int32_t lumi_mamba_block_static(lumi_model* m, int32_t layer, uint64_
     a.B = batch; a.H = c.n_heads; a.P = c.head_dim(); a.N = c.d_state; a.G = c.n_groups; a.eps = c.eps;
     LUMI_CUDA(launch_ssm_step(a, st));
     GemvArgs g2{y, DI, L.m.out_proj.p, L.m.out_proj.dtype, xd, D, xd, nullptr, batch, D, DI, c.eps, 0};
+    g2.allow_preload = false;
     LUMI_CUDA(launch_gemv(g2, st));
     return LUMI_OK;
 }

@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(192, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
                        const __grid_constant__ CUtensorMap map_w, float* D, int ldd, int M, int N, int K,
                        int accumulate, int tiles_m, int ntiles, int splits, int32_t* tile_counters, float* scratch, int32_t* status,
-                       uint64_t wait_ns, int skip_unit) {
+                       uint64_t wait_ns, int skip_unit, NormFuse nf) {
     using T = Tile<BN, SPLIT, 1>;
     constexpr int S = T::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -373,6 +373,27 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
             const uint32_t as = it & 1u, aph = (it >> 1) & 1u;
             const int t = u / splits, sp = u - t * splits;
             const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+            // RMSNorm folded around the product (inference/src/model.rs:100-106 with the per-row scale moved behind the
+            // contraction): the rows of A were written as x * gamma WITHOUT the scale 1 / sqrt(mean(x^2) + eps); the
+            // sums of squares arrive as `ssq_parts` partial sums per row (one per 32 columns of x, added in column order,
+            // so the result does not depend on any tile shape) and the scale multiplies the accumulator below.
+            // Read while the tensor core still works on this tile.
+            float rs = 1.0f;
+            if (nf.ssq_in != nullptr && m0 + q * 32 + lane < M) {
+                const float* pp = nf.ssq_in + (size_t)(m0 + q * 32 + lane) * nf.ssq_stride;
+                float t = 0.f;
+                int pz = 0;
+                if ((nf.ssq_stride & 3) == 0) {
+                    for (; pz + 16 <= nf.ssq_parts; pz += 16) {          // four 16-byte loads in flight, added in column order
+                        const float4 a0 = *reinterpret_cast<const float4*>(pp + pz), a1 = *reinterpret_cast<const float4*>(pp + pz + 4);
+                        const float4 a2 = *reinterpret_cast<const float4*>(pp + pz + 8), a3 = *reinterpret_cast<const float4*>(pp + pz + 12);
+                        t += a0.x; t += a0.y; t += a0.z; t += a0.w; t += a1.x; t += a1.y; t += a1.z; t += a1.w;
+                        t += a2.x; t += a2.y; t += a2.z; t += a2.w; t += a3.x; t += a3.y; t += a3.z; t += a3.w;
+                    }
+                }
+                for (; pz < nf.ssq_parts; ++pz) t += pp[pz];
+                rs = __frcp_rn(__fsqrt_rn(__fadd_rn(__fmul_rn(t, nf.inv_k), nf.eps)));
+            }
             if (!mbar_wait(&tmem_full[as], aph, wait_ns)) timed_out = true;
             timed_out = __any_sync(0xffffffffu, timed_out);     // tcgen05.ld below is warp-collective
             if (timed_out) break;
@@ -439,29 +460,67 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + as * ACC_COLS + (uint32_t)(cb * 32), r);
                 const int col0 = n0 + cb * 32;
                 const int nlim = min(N, n0 + BN);            // columns of this tile that exist
+                float ssq = 0.f;                             // producer side: this row's sum of squares over this 32-column strip
                 if (row < M && col0 < nlim) {
                     float* dp = D + (size_t)row * ldd + col0;
                     if (vec_ok && col0 + 32 <= nlim) {
+                        // every load of this 32-column strip goes out before the first store: the output pointers may alias
+                        // as far as the compiler can tell, and a load behind a store would wait a whole L2 round trip
+                        float4 o[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                            if (acc_in) {
-                                float4 o = __ldcg(reinterpret_cast<const float4*>(dp + 4 * j));
-                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                        for (int j = 0; j < 8; ++j) o[j] = acc_in ? __ldcg(reinterpret_cast<const float4*>(dp + 4 * j)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        float4 v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            v[j] = make_float4(fmaf(__uint_as_float(r[4 * j]), rs, o[j].x), fmaf(__uint_as_float(r[4 * j + 1]), rs, o[j].y),
+                                               fmaf(__uint_as_float(r[4 * j + 2]), rs, o[j].z), fmaf(__uint_as_float(r[4 * j + 3]), rs, o[j].w));
+                        if (nf.out_hi != nullptr) {
+                            // the next RMSNorm's input for the next product: x * gamma as bf16 hi + lo (16-byte stores), and x^2 summed
+                            float4 gm[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) gm[j] = __ldg(reinterpret_cast<const float4*>(nf.gamma_next + col0 + 4 * j));
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(dp + 4 * j) = v[j];
+#pragma unroll
+                            for (int jj = 0; jj < 4; ++jj) {
+                                uint32_t hw[4], lw[4];
+#pragma unroll
+                                for (int e = 0; e < 2; ++e) {
+                                    const float4 vv = v[2 * jj + e], gg = gm[2 * jj + e];
+                                    ssq = fmaf(vv.x, vv.x, fmaf(vv.y, vv.y, fmaf(vv.z, vv.z, fmaf(vv.w, vv.w, ssq))));
+                                    const float w0 = vv.x * gg.x, w1 = vv.y * gg.y, w2 = vv.z * gg.z, w3 = vv.w * gg.w;
+                                    const __nv_bfloat162 h01 = __floats2bfloat162_rn(w0, w1), h23 = __floats2bfloat162_rn(w2, w3);
+                                    const float2 f01 = __bfloat1622float2(h01), f23 = __bfloat1622float2(h23);
+                                    const __nv_bfloat162 l01 = __floats2bfloat162_rn(w0 - f01.x, w1 - f01.y), l23 = __floats2bfloat162_rn(w2 - f23.x, w3 - f23.y);
+                                    hw[2 * e] = *reinterpret_cast<const uint32_t*>(&h01); hw[2 * e + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+                                    lw[2 * e] = *reinterpret_cast<const uint32_t*>(&l01); lw[2 * e + 1] = *reinterpret_cast<const uint32_t*>(&l23);
+                                }
+                                const size_t oo = (size_t)row * N + col0 + 8 * jj;
+                                *reinterpret_cast<uint4*>(nf.out_hi + oo) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                                if (nf.out_lo != nullptr) *reinterpret_cast<uint4*>(nf.out_lo + oo) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
                             }
-                            *reinterpret_cast<float4*>(dp + 4 * j) = v;
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) *reinterpret_cast<float4*>(dp + 4 * j) = v[j];
                         }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             if (col0 + j < nlim) {
-                                float v = __uint_as_float(r[j]);
+                                float v = __uint_as_float(r[j]) * rs;
                                 if (acc_in) v += __ldcg(dp + j);
                                 dp[j] = v;
+                                if (nf.out_hi != nullptr) {
+                                    ssq = fmaf(v, v, ssq);
+                                    const float w0 = v * nf.gamma_next[col0 + j];
+                                    const __nv_bfloat16 hh = __float2bfloat16_rn(w0);
+                                    nf.out_hi[(size_t)row * N + col0 + j] = hh;
+                                    if (nf.out_lo != nullptr) nf.out_lo[(size_t)row * N + col0 + j] = __float2bfloat16_rn(w0 - __bfloat162float(hh));
+                                }
                             }
                         }
                     }
+                    if (nf.out_hi != nullptr) nf.ssq_out[(size_t)row * nf.ssq_stride + (col0 >> 5)] = ssq;
                 }
             }
             tc_fence_before();
@@ -536,7 +595,7 @@ int32_t launch_persistent(const GemmArgs& a, int splits, cudaStream_t st) {
     const int units = ntiles * splits;
     const int grid = units < sm_count_gemm() ? units : sm_count_gemm();
     kern<<<grid, 192, T::SMEM, st>>>(mh, ml, mw, a.d, a.ldd, a.M, a.N, a.K, a.accumulate, tiles_m, ntiles, splits, a.tile_counters,
-                                     a.scratch, a.status_word, a.wait_limit_ns ? a.wait_limit_ns : kWaitLimitNs, a.debug_skip_unit);
+                                     a.scratch, a.status_word, a.wait_limit_ns ? a.wait_limit_ns : kWaitLimitNs, a.debug_skip_unit, a.nf);
     LUMI_CUDA(cudaGetLastError());
     return LUMI_OK;
 }
@@ -571,6 +630,37 @@ int32_t gemm_tcgen05_init() {
     return LUMI_OK;
 }
 
+// Tile width of the persistent kernel: the GPU works in rounds of one tile per SM, a round costs about its tile's
+// width, so take the width with the least rounds x width (7360 columns x 16 row tiles: 208 -> 4 rounds of 576 tiles,
+// against 4 rounds of 464 tiles at 256).  Ties go to the wider tile (less operand traffic per flop).
+// K can be split over CTAs as well (LUMI_GEMM_SPLITK=2, 4 or 8; at least four k-blocks per split) when the
+// tiles do not fill the SMs.  Off by default: measured slower at 64-512 rows, because the fix-up (the last
+// warp to arrive adds the parked partial tiles in split order) is a chain of L2 round trips in few warps.
+static void pick_tile(const GemmArgs& a, int* width, int* splits) {
+    static const int widths[] = {256, 224, 208, 192, 160, 128, 96, 64, 32};
+    static const int env_splits = getenv("LUMI_GEMM_SPLITK") ? atoi(getenv("LUMI_GEMM_SPLITK")) : 1;
+    const bool fused = a.nf.ssq_in != nullptr || a.nf.out_hi != nullptr;       // the folded RMSNorm lives in the unsplit epilogue
+    const int max_splits = fused ? 1 : env_splits;
+    const long tiles_m = (a.M + BM - 1) / BM;
+    const int num_kb = a.K / BK;
+    int best = 256, best_splits = 1;
+    long best_cost = -1;
+    for (int w : widths) {
+        if (a.nf.out_hi != nullptr && (w % 32) != 0) continue;       // the folded norm's partial sums are per 32 aligned columns
+        const long tiles = tiles_m * ((a.N + w - 1) / w);
+        for (int sp = 1; sp <= max_splits; sp *= 2) {
+            if (sp > 1 && (a.tile_counters == nullptr || a.scratch == nullptr || 4 * tiles > a.n_counters ||
+                           (size_t)sp * tiles * BM * w > a.scratch_floats || num_kb / sp < 4))
+                break;
+            const long rounds = (tiles * sp + sm_count_gemm() - 1) / sm_count_gemm();
+            const long cost = rounds * (w / sp + 32 + (sp > 1 ? 12 : 0));    // + 32: the part of a tile's time that does not shrink
+            if (best_cost < 0 || cost < best_cost) { best = w; best_splits = sp; best_cost = cost; }
+        }
+    }
+    *width = best;
+    *splits = best_splits;
+}
+
 int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st) {
     if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.K % BK) != 0)
         return fail(LUMI_E_UNSUPPORTED, "tcgen05 GEMM needs K %% 64 == 0 (M %d N %d K %d)", a.M, a.N, a.K);
@@ -578,39 +668,23 @@ int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st) {
         return fail(LUMI_E_INVALID, "tcgen05 GEMM operands must be 16-byte aligned");
     LUMI_TRY(gemm_tcgen05_init());
     const bool split = a.a_lo != nullptr;
+    const bool fused = a.nf.ssq_in != nullptr || a.nf.out_hi != nullptr;
+    if (a.nf.out_hi != nullptr && ((a.N & 7) != 0 || a.nf.gamma_next == nullptr || a.nf.ssq_out == nullptr || a.nf.ssq_stride * 32 < a.N))
+        return fail(LUMI_E_INVALID, "folded RMSNorm output needs N %% 8 == 0, the next norm's weights and room for N / 32 partial sums per row");
     // LUMI_GEMM_MODE (tuning aid): 0 = default choice, 1 = 128-wide tiles two CTAs per SM, 2 = 128-wide one CTA per SM,
     // 3 = 256-wide one CTA per SM
     static const int mode = getenv("LUMI_GEMM_MODE") ? atoi(getenv("LUMI_GEMM_MODE")) : 0;
-    if (mode == 1) return split ? launch_t<128, true, 2>(a, st) : launch_t<128, false, 2>(a, st);
-    if (mode == 2) return split ? launch_t<128, true, 1>(a, st) : launch_t<128, false, 1>(a, st);
-    if (mode == 3) return split ? launch_t<256, true, 1>(a, st) : launch_t<256, false, 1>(a, st);
+    if (!fused) {
+        if (mode == 1) return split ? launch_t<128, true, 2>(a, st) : launch_t<128, false, 2>(a, st);
+        if (mode == 2) return split ? launch_t<128, true, 1>(a, st) : launch_t<128, false, 1>(a, st);
+        if (mode == 3) return split ? launch_t<256, true, 1>(a, st) : launch_t<256, false, 1>(a, st);
+    }
     // wide tiles when the problem has enough of them to fill the GPU; more than one tile per SM: persistent CTAs
     const long tiles256 = (long)((a.N + 255) / 256) * ((a.M + BM - 1) / BM);
     static const int persist = getenv("LUMI_GEMM_PERSIST") ? atoi(getenv("LUMI_GEMM_PERSIST")) : 1;     // 0: tuning aid
-    if (persist) {
-        // Tile width: the GPU works in rounds of one tile per SM, a round costs about its tile's width, so take
-        // the width with the least rounds x width (7360 columns x 16 row tiles: 208 -> 4 rounds of 576 tiles,
-        // against 4 rounds of 464 tiles at 256).  Ties go to the wider tile (less operand traffic per flop).
-        // K can be split over CTAs as well (LUMI_GEMM_SPLITK=2, 4 or 8; at least four k-blocks per split) when the
-        // tiles do not fill the SMs.  Off by default: measured slower at 64-512 rows, because the fix-up (the last
-        // warp to arrive adds the parked partial tiles in split order) is a chain of L2 round trips in few warps.
-        static const int widths[] = {256, 224, 208, 192, 160, 128, 96, 64, 32};
-        static const int max_splits = getenv("LUMI_GEMM_SPLITK") ? atoi(getenv("LUMI_GEMM_SPLITK")) : 1;
-        const long tiles_m = (a.M + BM - 1) / BM;
-        const int num_kb = a.K / BK;
+    if (persist || fused) {
         int best = 256, best_splits = 1;
-        long best_cost = -1;
-        for (int w : widths) {
-            const long tiles = tiles_m * ((a.N + w - 1) / w);
-            for (int sp = 1; sp <= max_splits; sp *= 2) {
-                if (sp > 1 && (a.tile_counters == nullptr || a.scratch == nullptr || 4 * tiles > a.n_counters ||
-                               (size_t)sp * tiles * BM * w > a.scratch_floats || num_kb / sp < 4))
-                    break;
-                const long rounds = (tiles * sp + sm_count_gemm() - 1) / sm_count_gemm();
-                const long cost = rounds * (w / sp + 32 + (sp > 1 ? 12 : 0));    // + 32: the part of a tile's time that does not shrink
-                if (best_cost < 0 || cost < best_cost) { best = w; best_splits = sp; best_cost = cost; }
-            }
-        }
+        pick_tile(a, &best, &best_splits);
 #define LUMI_PERSIST_CASE(W) if (best == W) return split ? launch_persistent<W, true>(a, best_splits, st) : launch_persistent<W, false>(a, best_splits, st);
         LUMI_PERSIST_CASE(256) LUMI_PERSIST_CASE(224) LUMI_PERSIST_CASE(208) LUMI_PERSIST_CASE(192) LUMI_PERSIST_CASE(160) LUMI_PERSIST_CASE(128)
         LUMI_PERSIST_CASE(96) LUMI_PERSIST_CASE(64) LUMI_PERSIST_CASE(32)

@@ -164,11 +164,16 @@ struct lumi_session {
     size_t kv_layer_bytes = 0;
     int32_t* page_table = nullptr;     // [max_batch][pages_per_seq]
     int32_t* kv_pos = nullptr;         // [max_batch] tokens consumed so far (absolute position)
+    float* attn_part = nullptr;        // partial (max, sum, context) of attention contexts split over CTAs
+    int32_t* attn_part_count = nullptr;
     int32_t* slot_buf = nullptr;       // [max_batch] slot list of a partial reset
     int pages_per_seq = 0;
     // activations
     float *x = nullptr, *proj = nullptr, *y32 = nullptr, *logits = nullptr;
     __nv_bfloat16 *act_hi = nullptr, *act_lo = nullptr;
+    __nv_bfloat16 *xn_hi = nullptr, *xn_lo = nullptr;   // residual rows x the next norm's weights, bf16 halves [rows][d_model]
+    float* ssq = nullptr;              // [rows][ssq_stride] partial sums of squares of the residual rows
+    int ssq_stride = 0;
     uint32_t *tok_cur = nullptr;       // [max_batch] tokens the next step consumes
     int32_t *finished = nullptr, *out_len = nullptr;   // [max_batch]
     int32_t* gemm_counters = nullptr;  // [2][kGemmCounters] zeroed ints for the split-K GEMM (second half: second lane)
@@ -204,6 +209,7 @@ struct GemvArgs {
     float eps;
     int act;                         // 0 none; 1: D = sigmoid(W_gate a) * (W_up a), W = [gate rows | up rows], N = rows of each
     int32_t* status = nullptr;       // device word that receives STATUS_TIMEOUT if a bounded wait gives up; may be null
+    bool allow_preload = true;       // false: never the single-wave preloading kernel (the only GEMV with a device-side wait)
 };
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);
 cudaError_t launch_logprob(const float* logits, int B, int V, const uint32_t* targets, float* out, int out_stride, int out_col,
@@ -216,9 +222,10 @@ void set_launch_pdl(bool on);
 
 cudaError_t launch_embed(const void* emb, int dtype, const uint32_t* tok_cur, float* x, int B, int D, int vocab,
                          StepCtl* ctl, cudaStream_t st);
-// x[B][D] fp32 -> RMSNorm(gamma) -> bf16 hi (+ lo if lo != null); gamma null = plain split
+// x[B][D] fp32 -> RMSNorm(gamma) -> bf16 hi (+ lo if lo != null); gamma null = plain split.
+// ssq != null: hi / lo = x * gamma without the per-row scale, ssq[b * ssq_stride] = sum of x^2 (for a GEMM with a folded norm)
 cudaError_t launch_norm_split(const float* x, const float* gamma, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int D,
-                              float eps, cudaStream_t st);
+                              float eps, cudaStream_t st, float* ssq = nullptr, int ssq_stride = 0);
 
 struct SsmArgs {
     const float* proj; int ldp;      // [B][in_proj_out]
@@ -255,7 +262,15 @@ struct AttnArgs {
     // the rows of a slice are appended to the cache by one launch (phase 1) and attend to it in a second one (phase 2).
     // Decode: rows_per_seq = 1, phase 0 (append, then attend, in one launch).
     int rows_per_seq = 1, b0 = 0, phase = 0;
+    // decode only: room for the partial results of a context split over several CTAs — part: [B * kv_heads][16 slices]
+    // [hpk * (head_dim + 2)] floats, part_count: [B * kv_heads] zeroed ints (left zero) — and the longest context of the
+    // batch as far as the host knows it (bounds the number of slices); null / 0: one CTA per (row, KV head)
+    float* part = nullptr;
+    int32_t* part_count = nullptr;
+    int max_ctx_hint = 0;
 };
+constexpr int kAttnPartSlices = 16;
+constexpr int kAttnPartUnits = 296;        // (row, KV head) pairs below which a context is split: two CTAs per SM
 cudaError_t launch_attention_decode(const AttnArgs& a, cudaStream_t st);
 cudaError_t launch_kv_advance(int32_t* kv_pos, int b0, int nb, int by, cudaStream_t st);
 
@@ -264,6 +279,22 @@ cudaError_t launch_kv_advance(int32_t* kv_pos, int b0, int nb, int by, cudaStrea
 // D[M][N] (+)= A[M][K] W[N][K]^T ; A as bf16 hi (+ lo) halves, W bf16, fp32 accumulate and output.
 // epi: 0 store, 1 add to existing D (residual), 2 sigmoid-gate: D[m][n] = sigmoid(acc[n]) * acc[n + N] is NOT
 // done here (see gate kernel).  status_word: device int that receives STATUS_TIMEOUT if a bounded wait gives up.
+// RMSNorm folded around a tensor-core product.  Consumer side (ssq_in): the A rows hold x * gamma without the
+// per-row scale; the kernel sums `ssq_parts` partial sums of x^2 per row (stride ssq_stride) and multiplies its
+// accumulator rows by 1 / sqrt(sum * inv_k + eps).  Producer side (out_hi): beside D the kernel writes
+// D * gamma_next as bf16 hi (+ lo) rows of width N and, per row, the sum of D^2 over each strip of 32 columns into
+// ssq_out[row * ssq_stride + column / 32] (independent of the tile width, so results do not depend on the row
+// count) — the next product's consumer side.  All null: plain product.
+struct NormFuse {
+    const float* ssq_in = nullptr;
+    int ssq_parts = 0;
+    int ssq_stride = 0;
+    float inv_k = 0.f, eps = 0.f;
+    const float* gamma_next = nullptr;
+    __nv_bfloat16 *out_hi = nullptr, *out_lo = nullptr;
+    float* ssq_out = nullptr;
+};
+
 struct GemmArgs {
     const __nv_bfloat16 *a_hi, *a_lo;   // [M][K]
     const __nv_bfloat16* w;             // [N][K]
@@ -277,6 +308,7 @@ struct GemmArgs {
     size_t scratch_floats = 0;
     uint64_t wait_limit_ns = 0;         // limit of every device-side wait (0 = the default, 0.5 s)
     int debug_skip_unit = -1;           // test hook: the producer stops before this work unit, so the consumers' waits run out
+    NormFuse nf;                        // RMSNorm folded around the product (persistent kernel only)
 };
 int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st);   // returns LUMI_* status
 int32_t gemm_tcgen05_init();                                        // resolves the driver entry point

@@ -119,9 +119,11 @@ __global__ void embed_kernel(const WT* __restrict__ emb, const uint32_t* tok_cur
 }
 
 // ---- RMSNorm to bf16 halves for the tensor-core GEMMs (model.rs:100-106) ---------------------------
+// ssq == null: hi (+ lo) = x * r * gamma.  ssq != null (the form the GEMM with a folded norm consumes): hi (+ lo) =
+// x * gamma and ssq[b * ssq_stride] = sum of x^2 — the per-row scale r is applied by the GEMM's epilogue.
 __global__ void __launch_bounds__(256) norm_split_kernel(const float* x, const float* __restrict__ gamma,
                                                          __nv_bfloat16* hi, __nv_bfloat16* lo,
-                                                         int D, float eps) {
+                                                         int D, float eps, float* ssq, int ssq_stride) {
     __shared__ float red[8];
     const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
@@ -137,11 +139,12 @@ __global__ void __launch_bounds__(256) norm_split_kernel(const float* x, const f
         float t = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) t += red[w];
-        r = rms_scale(t, D, eps);
+        if (ssq != nullptr) { if (threadIdx.x == 0) ssq[(size_t)b * ssq_stride] = t; }
+        else r = rms_scale(t, D, eps);
     }
     for (int i = threadIdx.x; i < D; i += 256) {
         float v = xr[i];
-        if (gamma) v = __fmul_rn(__fmul_rn(v, r), gamma[i]);
+        if (gamma) v = ssq != nullptr ? __fmul_rn(v, gamma[i]) : __fmul_rn(__fmul_rn(v, r), gamma[i]);
         __nv_bfloat16 h, l;
         split_bf16(v, h, l);
         hi[(size_t)b * D + i] = h;
@@ -1086,8 +1089,8 @@ __global__ void advance_step_kernel(StepCtl* ctl, int32_t* kv_pos, int B, int sa
 // D = sigmoid(gate) * up for the attention block's MLP (model.rs:550-552); gu = [gate | up] per row
 __global__ void gate_mul_kernel(const float* gu, int ld, float* out32, __nv_bfloat16* hi, __nv_bfloat16* lo,
                                 int mlp) {
-    const int b = blockIdx.y;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.x;                        // rows on x: a prefill slice has more than 65535
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;
     pdl_launch_dependents();
     pdl_wait();
     if (i >= mlp) return;
@@ -1140,8 +1143,8 @@ cudaError_t launch_embed(const void* emb, int dtype, const uint32_t* tok_cur, fl
 }
 
 cudaError_t launch_norm_split(const float* x, const float* gamma, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int D,
-                              float eps, cudaStream_t st) {
-    return launch_k(norm_split_kernel, dim3(B), dim3(256), 0, st, x, gamma, hi, lo, D, eps);
+                              float eps, cudaStream_t st, float* ssq, int ssq_stride) {
+    return launch_k(norm_split_kernel, dim3(B), dim3(256), 0, st, x, gamma, hi, lo, D, eps, ssq, ssq_stride);
 }
 
 template <typename WT, int NB, int RPW, int ACT>
@@ -1240,7 +1243,7 @@ static cudaError_t gemv_pre_launch(const GemvArgs& a, int rows_per_cta, size_t s
 template <typename WT>
 static bool gemv_pre_try(const GemvArgs& a, cudaStream_t st, cudaError_t* err) {
     constexpr int E = WLoad<WT>::E;
-    if (!gemv_pre_enabled() || a.act != 0 || a.M > 4 || a.M < 1 || (a.K % E) != 0 || a.K < E) return false;
+    if (!gemv_pre_enabled() || !a.allow_preload || a.act != 0 || a.M > 4 || a.M < 1 || (a.K % E) != 0 || a.K < E) return false;
     const int KC = a.K / E;
     const int U = (KC + 31) / 32;
     if (U > 16 || KC != 32 * U || (U & (U - 1)) != 0) return false;     // rows of exactly 32 * U chunks, U a power of two
@@ -1433,7 +1436,7 @@ cudaError_t launch_advance_step(StepCtl* ctl, int32_t* kv_pos, int B, int sample
 
 cudaError_t launch_gate_mul(const float* gu, int ld, float* out32, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int mlp,
                             cudaStream_t st) {
-    dim3 grid((mlp + 255) / 256, B);
+    dim3 grid(B, (mlp + 255) / 256);
     return launch_k(gate_mul_kernel, grid, dim3(256), 0, st, gu, ld, out32, hi, lo, mlp);
 }
 

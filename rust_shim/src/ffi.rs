@@ -19,6 +19,8 @@ pub struct LumiStats {
     pub ms_decode: f32,
     pub bytes_per_step: i64,
     pub kernel_launches: i64,
+    pub achieved_gbps: f32,
+    pub waves: i32,
 }
 
 pub enum LumiModel {}
