@@ -273,9 +273,12 @@ def scan_compare(nb=64, T=2048, reps=3):
         torch.cuda.synchronize()
         ms = ev0.elapsed_time(ev1)
         theirs = ms if theirs is None else min(theirs, ms)
-    got = (yhi.float() + ylo.float()).view(nb, T, DI)
+    # agreement of the two kernels on the first 256 tokens (tests/test_gpu_reference_scan.py holds the bound; over thousands
+    # of tokens of unit-variance random rows the reference's sin/cos.approx angles drift away from any exact evaluation)
+    n_cmp = min(T, 256)
+    got = (yhi.float() + ylo.float()).view(nb, T, DI)[:, :n_cmp]
     out.update({"reference_ms": theirs, "reference_us_per_unit": theirs * 1e3 / units, "speedup": theirs / ours,
-                "max_rel_diff": float((got - yg).abs().max() / yg.abs().max())})
+                "max_rel_diff_first_256_tokens": float((got - yg[:, :n_cmp]).abs().max() / yg[:, :n_cmp].abs().max())})
     return out
 
 

@@ -936,6 +936,7 @@ __device__ BestPair block_argmax(float v, int i, BestPair* red) {
 }
 
 constexpr int kMaxTopK = 256;
+constexpr int kSelEqMax = 1024;       // tied entries at the k-th value handled by the fast selection (more: the round-by-round path)
 
 // One block per sequence.  Greedy: argmax with the lowest index on ties.  Otherwise temperature
 // softmax over the top-k survivors (or the whole vocabulary) and the walk over the cumulative
@@ -947,6 +948,8 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* logits, int V
     __shared__ int top_i[kMaxTopK];
     __shared__ float chunk_sum[1024];
     __shared__ int result;
+    __shared__ int sel_hist[256], sel_eq[kSelEqMax];
+    __shared__ int sel_digit, sel_above, sel_n, sel_neq;
     const int b = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     pdl_launch_dependents();
     pdl_wait();
@@ -975,28 +978,80 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* logits, int V
             // per thread) each thread keeps its entries in registers with a taken-mask and a cached local best,
             // so a round costs one block reduction and a rescan by the single thread that owned the winner.
             constexpr int kRegVals = 32;
+            bool selected = false;
             if (V <= nt * kRegVals) {
-                float vals[kRegVals];
+                // The row fits in registers (up to 32 entries per thread).  The k-th largest value is found by a radix
+                // select over an order-preserving integer image of the floats (four passes of 256-bin histograms in
+                // shared memory); then everything above it survives, and of the entries equal to it the ones with the
+                // lowest ids — the same set k rounds of "largest remaining, lowest id on ties" would pick.
+                uint32_t keys[kRegVals];                              // the float is recovered from its key where needed
+                auto key_to_float = [](uint32_t key) { return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key); };
 #pragma unroll
-                for (int j = 0; j < kRegVals; ++j) { const int i = tid + j * nt; vals[j] = i < V ? lg[i] : -INFINITY; }
-                uint32_t taken = 0u;
-                float lbv; int lbi;
-                auto rescan = [&]() {
-                    lbv = -INFINITY; lbi = 0x7fffffff;
+                for (int j = 0; j < kRegVals; ++j) {
+                    const int i = tid + j * nt;
+                    float v = i < V ? lg[i] : -INFINITY;
+                    if (v != v) v = -INFINITY;                       // a NaN is never chosen
+                    const uint32_t u = __float_as_uint(v);
+                    keys[j] = i < V ? ((u & 0x80000000u) ? ~u : (u | 0x80000000u)) : 0u;    // padding sorts below every real entry
+                }
+                uint32_t prefix = 0u;
+                int want = k;                                          // rank (from the top) still to be located inside the prefix
+                for (int shift = 24; shift >= 0; shift -= 8) {
+                    for (int i = tid; i < 256; i += nt) sel_hist[i] = 0;
+                    __syncthreads();
+                    const uint32_t hi_mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
 #pragma unroll
-                    for (int j = 0; j < kRegVals; ++j) {
-                        const int i = tid + j * nt;
-                        if (i < V && !((taken >> j) & 1u) && better(vals[j], i, lbv, lbi)) { lbv = vals[j]; lbi = i; }
+                    for (int j = 0; j < kRegVals; ++j)
+                        if (tid + j * nt < V && (keys[j] & hi_mask) == prefix) atomicAdd(&sel_hist[(keys[j] >> shift) & 255u], 1);
+                    __syncthreads();
+                    if (tid < 32) {
+                        // bins 8 * lane .. 8 * lane + 7; suffix counts from the top bin down
+                        int c[8], tot = 0;
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) { c[q] = sel_hist[8 * tid + q]; tot += c[q]; }
+                        int above = 0;                                  // entries in the bins of higher lanes
+                        for (int l2 = 31; l2 > 0; --l2) { const int t2 = __shfl_sync(0xffffffffu, tot, l2); if (l2 > tid) above += t2; }
+                        int acc = above;
+#pragma unroll
+                        for (int q = 7; q >= 0; --q) {
+                            if (acc < want && want <= acc + c[q]) { sel_digit = 8 * tid + q; sel_above = acc; }
+                            acc += c[q];
+                        }
                     }
-                };
-                rescan();
-                for (int round = 0; round < k; ++round) {
-                    BestPair rr = block_argmax(lbv, lbi, red);
-                    if (tid == 0) { top_v[round] = rr.v; top_i[round] = rr.i; }
-                    if (rr.i < V && rr.i % nt == tid) { taken |= 1u << (rr.i / nt); rescan(); }
+                    __syncthreads();
+                    prefix |= (uint32_t)sel_digit << shift;
+                    want -= sel_above;
+                    __syncthreads();
+                }
+                // prefix is the key of the k-th largest entry; `want` of the entries equal to it survive (lowest ids)
+                if (tid == 0) { sel_n = 0; sel_neq = 0; }
+                __syncthreads();
+#pragma unroll
+                for (int j = 0; j < kRegVals; ++j) {
+                    const int i = tid + j * nt;
+                    if (i < V) {
+                        if (keys[j] > prefix) { const int o = atomicAdd(&sel_n, 1); top_v[o] = key_to_float(keys[j]); top_i[o] = i; }
+                        else if (keys[j] == prefix) { const int o = atomicAdd(&sel_neq, 1); if (o < kSelEqMax) sel_eq[o] = i; }
+                    }
                 }
                 __syncthreads();
-            } else
+                const int n_gt = sel_n, n_eq = sel_neq;
+                if (n_eq <= kSelEqMax) {
+                    // rank of every tied entry among the tied ids; the `want` lowest go in
+                    for (int e = tid; e < n_eq; e += nt) {
+                        const int me = sel_eq[e];
+                        int rank = 0;
+                        for (int f = 0; f < n_eq; ++f) rank += sel_eq[f] < me ? 1 : 0;
+                        if (rank < want) {
+                            top_v[n_gt + rank] = key_to_float(prefix);
+                            top_i[n_gt + rank] = me;
+                        }
+                    }
+                    selected = true;
+                }
+                __syncthreads();
+            }
+            if (!selected)
             for (int round = 0; round < k; ++round) {
                 float bv = -INFINITY; int bi = 0x7fffffff;
                 for (int i = tid; i < V; i += nt) {

@@ -1,5 +1,5 @@
 // Chunked (SSD-style) prefill of the Mamba-3 trapezoidal recurrence, chunk length 64, with the chunk's
-// projection rows staged by TMA one chunk ahead and the chunk products on tensor cores.
+// projection rows staged by TMA and the chunk products on tensor cores.
 //
 // The reference prefills token by token (inference/src/main.rs:121-125) and its only NVIDIA scan
 // is sequential in time (training/csrc/ssm_scan.cu:137-227; SSD_FWD_CHUNK there is dead code).
@@ -19,16 +19,18 @@
 // same angle, rounding-level differences; the stored angle may differ from the sequential one by a multiple
 // of 2 pi).
 //
-// One CTA of four warps per (head, sequence), two CTAs per SM.
+// One CTA of four warps per (head, sequence), three CTAs per SM (69 KiB of shared memory, 168 registers).
 //   * Staging: the chunk's x, z, theta (64 x 32 fp32 each) and the group's raw B, C (64 x 64 fp32 each) arrive by
-//     five cp.async.bulk.tensor copies on one mbarrier (bounded wait); the copies for chunk c+1 are issued as
-//     soon as chunk c's raw values have been consumed, i.e. before chunk c's matrix products, and the per-token
-//     scalars (dt, lambda, A, BCNorm scales) of chunk c+1 are requested into registers at the same point.
+//     five cp.async.bulk.tensor copies on one mbarrier (bounded wait).  The operand tiles are built IN PLACE over the
+//     raw rows, so the copies for chunk c+1 are issued when chunk c's products are done; their flight time is covered
+//     by the two other CTAs of the SM (and the per-token scalars dt, lambda, A, BCNorm scales of chunk c+1 are
+//     requested into registers at the start of chunk c).
 //   * Arithmetic: every operand is an fp32 value split into bf16 hi + lo; a product is three
 //     mma.sync.m16n8k16 (hi*hi + hi*lo + lo*hi, fp32 accumulate), which keeps ~16 mantissa bits per factor.
 //     Warp w owns tokens 16w..16w+15: its C~ rows stay in registers as A fragments, G's accumulators are masked,
 //     decayed and re-used in place as the A fragments of W X (no trip through shared memory), and the state S^
 //     lives in accumulator registers across the chunks of a launch (warp w: 16 rows of P x 32 columns of N).
+//     Independent accumulators are interleaved so that no multiply-add waits for the one issued just before it.
 //   * The pointwise part (softplus / sigmoid / tanh / SiLU / sin / cos) uses the fast hardware forms here: their
 //     error (~1e-6) is far below the operand split's (1.5e-5) — the decode step keeps the exact forms.
 #include "internal.h"
@@ -141,17 +143,19 @@ __device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bflo
     lo = __float2bfloat16_rn(v - __bfloat162float(hi));
 }
 
+// Shared memory of a CTA (69 KiB: three CTAs per SM).  The five bulk tensor copies of a chunk land in rx, rth, rB, rC, rz
+// (dense boxes).  The operand tiles of the tensor-core products are then written IN PLACE over the raw rows they were
+// computed from — token i's raw B row (256 bytes) becomes B~ hi (first 128 bytes) and B~ lo (last 128 bytes) of token i,
+// the same for C, silu(x) transposed replaces the raw x rows, the gate replaces z — so no operand tile needs memory of
+// its own.  Inside a 128-byte row the eight 16-byte chunks are XOR-ed with (row % 8) so that ldmatrix and the fragment
+// stores stay free of bank conflicts without padding.
 struct PfSmem {
-    // destinations of the bulk tensor copies (dense boxes); theta becomes the angle and z the gate in place
-    float rx[LCH][32];
-    float rth[LCH][32];
-    float rB[LCH][64];
-    float rC[LCH][64];
-    float rz[2][LCH][32];
-    // bf16 operand tiles, hi and lo planes
-    __nv_bfloat16 Bt[2][LCH][TSB];     // rotated B~            [token][n]
-    __nv_bfloat16 Xt[2][32][TSB];      // silu(x) transposed    [p][token]
-    __nv_bfloat16 St[2][32][TSB];      // augmented state S^    [p][n]
+    float rx[LCH][32];                 // raw x            -> X^T: [plane hi | lo][p = 32 rows][token, 128 bytes]
+    float rth[LCH][32];                // raw theta
+    float rB[LCH][64];                 // raw B (group)    -> B~: row = token, [hi 128 bytes | lo 128 bytes]
+    float rC[LCH][64];                 // raw C (group)    -> C~: same layout
+    float rz[LCH][32];                 // raw z            -> gate silu(z)
+    uint8_t St[2 * 32 * 128];          // augmented state S^: [plane hi | lo][p = 32 rows][n, 128 bytes]
     float ell[LCH], eli[LCH], lam[LCH + 4], kap[LCH], wj[LCH], dtp[LCH], rbs[LCH], rcs[LCH];
     float seg[5][32];                  // angle prefix sums at the boundaries of the four 16-token segments
     float cum[32];
@@ -159,6 +163,12 @@ struct PfSmem {
     unsigned long long bar;
     int ok;
 };
+
+// byte offset of bf16 element (row, col) inside a tile whose rows are `pitch` bytes apart and hold 64 bf16 (128 bytes)
+// with the 16-byte chunks XOR-ed by row % 8
+__device__ __forceinline__ int swz(int row, int col, int pitch) {
+    return row * pitch + ((((col >> 3) ^ (row & 7)) << 4) | ((col & 7) << 1));
+}
 
 constexpr uint32_t kChunkTxBytes = 3 * LCH * 32 * 4 + 2 * LCH * 64 * 4;
 
@@ -201,7 +211,7 @@ __global__ void gather_last_kernel(const float* __restrict__ xr, float* __restri
     for (int k = threadIdx.x; k < D; k += blockDim.x) x[(size_t)(b0 + b) * D + k] = xr[((size_t)b * ts + ts - 1) * D + k];
 }
 
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(128, 3)
 ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_constant__ CUtensorMap map64, PrefillArgs a) {
     constexpr int P = 32, N = 64, HN = 32;
     extern __shared__ uint8_t pf_raw[];
@@ -233,15 +243,19 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
     }
     __syncthreads();
 
-    auto issue_chunk = [&](int t0, int zb) {       // one thread: the five box copies of the chunk starting at token t0
+    auto issue_chunk = [&](int t0) {               // one thread: the five box copies of the chunk starting at token t0
         const int row0 = b * ts + t0;
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(kChunkTxBytes) : "memory");
         tma_load_2d(&sm.rx[0][0], &map32, bar, h * P, row0);
-        tma_load_2d(&sm.rz[zb][0][0], &map32, bar, DI + h * P, row0);
+        tma_load_2d(&sm.rz[0][0], &map32, bar, DI + h * P, row0);
         tma_load_2d(&sm.rth[0][0], &map32, bar, off_dt + 3 * H + h * HN, row0);
         tma_load_2d(&sm.rB[0][0], &map64, bar, off_b + grp * N, row0);
         tma_load_2d(&sm.rC[0][0], &map64, bar, off_c + grp * N, row0);
     };
+    uint8_t* const tB = reinterpret_cast<uint8_t*>(&sm.rB[0][0]);     // B~ tile (in place): pitch 256, lo plane at +128
+    uint8_t* const tC = reinterpret_cast<uint8_t*>(&sm.rC[0][0]);     // C~ tile (in place)
+    uint8_t* const tX = reinterpret_cast<uint8_t*>(&sm.rx[0][0]);     // X^T tile (in place): pitch 128, lo plane at +4096
+    uint8_t* const tS = sm.St;                                        // S^ tile: pitch 128, lo plane at +4096
     // per-token scalars of a chunk, requested into registers one chunk ahead (threads 0..63: own token; thread 64:
     // lambda of the token after the chunk)
     float n_dt = 0.f, n_lam = 0.f, n_a = 0.f, n_rb = 0.f, n_rc = 0.f;
@@ -255,7 +269,7 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
             n_lam = prow0[(size_t)(t0 + LCH) * R + off_dt + H + h];
         }
     };
-    if (tid == 0) issue_chunk(0, 0);
+    if (tid == 0) issue_chunk(0);
     request_scalars(0);
 
     // state S^ of this warp: rows p0 + {g4, g4 + 8}, columns n0 + 8 nt + 2 t4 + {0, 1}
@@ -271,13 +285,27 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
         }
     }
 
+    // this warp's block of S^ as bf16 hi + lo into the shared tile (B operand of C~ S^T in the next chunk)
+    auto store_state_tile = [&]() {
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            uint32_t hi, lo;
+            const int col = n0 + 8 * nt + 2 * t4;
+            split2(S[nt][0], S[nt][1], hi, lo);
+            *reinterpret_cast<uint32_t*>(tS + swz(p0 + g4, col, 128)) = hi;
+            *reinterpret_cast<uint32_t*>(tS + 4096 + swz(p0 + g4, col, 128)) = lo;
+            split2(S[nt][2], S[nt][3], hi, lo);
+            *reinterpret_cast<uint32_t*>(tS + swz(p0 + g4 + 8, col, 128)) = hi;
+            *reinterpret_cast<uint32_t*>(tS + 4096 + swz(p0 + g4 + 8, col, 128)) = lo;
+        }
+    };
+
     uint32_t phase = 0;
     // One chunk.  FULL: all 64 tokens are valid, so every "past the end of the sequence" test folds away.
     auto do_chunk = [&](auto full_c, const int t0, const int chunk) -> bool {
         constexpr bool FULL = decltype(full_c)::value;
         const int nv = FULL ? LCH : min(LCH, ts - t0);     // valid tokens in this chunk
         auto valid = [&](int i) { return FULL || i < nv; };
-        const int zb = chunk & 1;
         const bool last_chunk = t0 + LCH >= ts;
         // ---- 0. the chunk's raw rows have landed (one thread waits, bounded; everyone follows its verdict)
         if (tid == 0) sm.ok = mbar_wait(bar, phase, kScanWaitLimitNs) ? 1 : 0;
@@ -298,6 +326,7 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
         __syncthreads();
         if (!sm.ok) return false;
         phase ^= 1;
+        if (!last_chunk) request_scalars(t0 + LCH);        // the next chunk's scalars travel while this chunk is computed
         if (tid < 32) {                                    // inclusive prefix of log a over the chunk
             float v0 = sm.ell[2 * lane], v1 = sm.ell[2 * lane + 1];
             float s = v0 + v1, incl = s;
@@ -329,19 +358,11 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
                 S[nt][0] = fmaf(xp0, bp.x, S[nt][0]); S[nt][1] = fmaf(xp0, bp.y, S[nt][1]);
                 S[nt][2] = fmaf(xp1, bp.x, S[nt][2]); S[nt][3] = fmaf(xp1, bp.y, S[nt][3]);
             }
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                uint32_t hi, lo;
-                split2(S[nt][0], S[nt][1], hi, lo);
-                *reinterpret_cast<uint32_t*>(&sm.St[0][p0 + g4][n0 + 8 * nt + 2 * t4]) = hi;
-                *reinterpret_cast<uint32_t*>(&sm.St[1][p0 + g4][n0 + 8 * nt + 2 * t4]) = lo;
-                split2(S[nt][2], S[nt][3], hi, lo);
-                *reinterpret_cast<uint32_t*>(&sm.St[0][p0 + g4 + 8][n0 + 8 * nt + 2 * t4]) = hi;
-                *reinterpret_cast<uint32_t*>(&sm.St[1][p0 + g4 + 8][n0 + 8 * nt + 2 * t4]) = lo;
-            }
+            store_state_tile();
         }
-        // ---- 2. thread (lane, warp) takes column `lane` (angle pair k, head dim p) of the warp's 16 tokens:
-        //         angles, rotated B~, silu(x) transposed, gate
+        // ---- 2. thread (lane, warp) takes column `lane` (angle pair k, head dim p) of the warp's 16 tokens: angles, rotated
+        //         B~ and C~ (one sin / cos for both), silu(x) transposed, gate.  Every raw row is read only by the warp that owns
+        //         its token, so a row can be overwritten by its operand tile after a warp-level barrier.
         {
             const int k = lane, i0 = 16 * warp;
             float loc[16], run = 0.f;
@@ -352,6 +373,16 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
                 loc[ii] = run;
             }
             sm.seg[warp + 1][k] = run;
+            // x -> silu (registers; the tile is written after every warp has read its raw x) ; z -> gate in place
+            const int p = lane;
+            float xs[16];
+#pragma unroll
+            for (int ii = 0; ii < 16; ++ii) {
+                const int i = i0 + ii;
+                xs[ii] = valid(i) ? silu_fast(sm.rx[i][p]) : 0.f;                              // model.rs:310
+                sm.rz[i][p] = valid(i) ? silu_fast(sm.rz[i][p]) : 0.f;                         // model.rs:370
+                if (last_chunk && i == nv - 1) a.xprev[bh * P + p] = xs[ii];                   // hand-over: x of the launch's last token
+            }
             __syncthreads();
             if (tid < 32) {
                 float off = sm.cum[tid];
@@ -360,81 +391,70 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
                 for (int s2 = 1; s2 <= 4; ++s2) { off = fmodf(off + sm.seg[s2][tid], TWO_PI); sm.seg[s2][tid] = off; }
                 sm.cum[tid] = off;                         // angle after the chunk's last valid token
             }
+            // X^T tile over the raw x rows: row p, tokens i0 .. i0 + 15 (two per 32-bit word)
+#pragma unroll
+            for (int ii = 0; ii < 16; ii += 2) {
+                uint32_t hi, lo;
+                split2(xs[ii], xs[ii + 1], hi, lo);
+                *reinterpret_cast<uint32_t*>(tX + swz(p, i0 + ii, 128)) = hi;
+                *reinterpret_cast<uint32_t*>(tX + 4096 + swz(p, i0 + ii, 128)) = lo;
+            }
             __syncthreads();
             const float base = sm.seg[warp][k];
             const float bgm0 = sm.gam[0][2 * k], bgm1 = sm.gam[0][2 * k + 1], bbs0 = sm.gam[1][2 * k], bbs1 = sm.gam[1][2 * k + 1];
+            const float cgm0 = sm.gam[2][2 * k], cgm1 = sm.gam[2][2 * k + 1], cbs0 = sm.gam[3][2 * k], cbs1 = sm.gam[3][2 * k + 1];
 #pragma unroll
-            for (int ii = 0; ii < 16; ++ii) {
-                const int i = i0 + ii;
-                float ang = base + loc[ii];
-                ang -= TWO_PI * rintf(ang * INV_TWO_PI);                     // into [-pi, pi] for the fast sin / cos
-                sm.rth[i][k] = ang;
-                float b0 = 0.f, b1 = 0.f;
-                if (valid(i)) {
-                    const float2 raw = *reinterpret_cast<const float2*>(&sm.rB[i][2 * k]);
-                    const float rb = sm.rbs[i];
-                    const float nb0 = fmaf(raw.x * rb, bgm0, bbs0), nb1 = fmaf(raw.y * rb, bgm1, bbs1);      // model.rs:311-313
-                    float sa, ca;
-                    __sincosf(ang, &sa, &ca);
-                    b0 = ca * nb0 - sa * nb1;                                // model.rs:345-348
-                    b1 = sa * nb0 + ca * nb1;
-                    if (last_chunk && i == nv - 1) {                         // hand-over: B~ of the launch's last token, in fp32
-                        a.bprev[bh * N + 2 * k] = b0;
-                        a.bprev[bh * N + 2 * k + 1] = b1;
-                    }
+            for (int i4 = 0; i4 < 16; i4 += 4) {           // four tokens at a time: all lanes read the raw rows, then overwrite them
+                float2 rawb[4], rawc[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    rawb[q] = *reinterpret_cast<const float2*>(&sm.rB[i0 + i4 + q][2 * k]);
+                    rawc[q] = *reinterpret_cast<const float2*>(&sm.rC[i0 + i4 + q][2 * k]);
                 }
-                uint32_t hi, lo;
-                split2(b0, b1, hi, lo);
-                *reinterpret_cast<uint32_t*>(&sm.Bt[0][i][2 * k]) = hi;
-                *reinterpret_cast<uint32_t*>(&sm.Bt[1][i][2 * k]) = lo;
-            }
-            // x -> silu -> Xt[p][token] (two tokens per 32-bit word); z -> gate in place
-            const int p = lane;
+                __syncwarp();
 #pragma unroll
-            for (int ii = 0; ii < 16; ii += 2) {
-                const int i = i0 + ii;
-                const float x0 = valid(i) ? silu_fast(sm.rx[i][p]) : 0.f;                        // model.rs:310
-                const float x1 = valid(i + 1) ? silu_fast(sm.rx[i + 1][p]) : 0.f;
-                uint32_t hi, lo;
-                split2(x0, x1, hi, lo);
-                *reinterpret_cast<uint32_t*>(&sm.Xt[0][p][i]) = hi;
-                *reinterpret_cast<uint32_t*>(&sm.Xt[1][p][i]) = lo;
-                if (last_chunk && (i == nv - 1 || i + 1 == nv - 1)) a.xprev[bh * P + p] = (i == nv - 1) ? x0 : x1;
-                sm.rz[zb][i][p] = valid(i) ? silu_fast(sm.rz[zb][i][p]) : 0.f;                   // model.rs:370
-                sm.rz[zb][i + 1][p] = valid(i + 1) ? silu_fast(sm.rz[zb][i + 1][p]) : 0.f;
-            }
-        }
-        __syncthreads();
-        // ---- 2b. this warp's C~ rows as A fragments (hi, lo), built straight from the raw C rows and the angles
-        uint32_t Ch[4][4], Cl[4][4];
-        {
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int k = t4 + 4 * q, ks = q >> 1, odd = q & 1;
-                const float cg0 = sm.gam[2][2 * k], cg1 = sm.gam[2][2 * k + 1], cb0 = sm.gam[3][2 * k], cb1 = sm.gam[3][2 * k + 1];
-#pragma unroll
-                for (int rr = 0; rr < 2; ++rr) {
-                    const int i = 16 * warp + g4 + 8 * rr;
-                    float c0 = 0.f, c1 = 0.f;
+                for (int q = 0; q < 4; ++q) {
+                    const int i = i0 + i4 + q;
+                    float ang = base + loc[i4 + q];
+                    ang -= TWO_PI * rintf(ang * INV_TWO_PI);                 // into [-pi, pi] for the fast sin / cos
+                    float b0 = 0.f, b1 = 0.f, c0 = 0.f, c1 = 0.f;
                     if (valid(i)) {
-                        const float2 raw = *reinterpret_cast<const float2*>(&sm.rC[i][2 * k]);
-                        const float rc = sm.rcs[i];
-                        const float nc0 = fmaf(raw.x * rc, cg0, cb0), nc1 = fmaf(raw.y * rc, cg1, cb1);
+                        const float rb = sm.rbs[i], rc = sm.rcs[i];
+                        const float nb0 = fmaf(rawb[q].x * rb, bgm0, bbs0), nb1 = fmaf(rawb[q].y * rb, bgm1, bbs1);      // model.rs:311-313
+                        const float nc0 = fmaf(rawc[q].x * rc, cgm0, cbs0), nc1 = fmaf(rawc[q].y * rc, cgm1, cbs1);
                         float sa, ca;
-                        __sincosf(sm.rth[i][k], &sa, &ca);
+                        __sincosf(ang, &sa, &ca);
+                        b0 = ca * nb0 - sa * nb1;                            // model.rs:345-348
+                        b1 = sa * nb0 + ca * nb1;
                         c0 = ca * nc0 - sa * nc1;
                         c1 = sa * nc0 + ca * nc1;
+                        if (last_chunk && i == nv - 1) {                     // hand-over: B~ of the launch's last token, in fp32
+                            a.bprev[bh * N + 2 * k] = b0;
+                            a.bprev[bh * N + 2 * k + 1] = b1;
+                        }
                     }
-                    split2(c0, c1, Ch[ks][2 * odd + rr], Cl[ks][2 * odd + rr]);
+                    uint32_t hi, lo;
+                    split2(b0, b1, hi, lo);
+                    *reinterpret_cast<uint32_t*>(tB + swz(i, 2 * k, 256)) = hi;
+                    *reinterpret_cast<uint32_t*>(tB + 128 + swz(i, 2 * k, 256)) = lo;
+                    split2(c0, c1, hi, lo);
+                    *reinterpret_cast<uint32_t*>(tC + swz(i, 2 * k, 256)) = hi;
+                    *reinterpret_cast<uint32_t*>(tC + 128 + swz(i, 2 * k, 256)) = lo;
                 }
+                __syncwarp();
             }
         }
-        // every raw value of this chunk has been consumed: order these generic-proxy accesses before the next copies
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();
-        if (!last_chunk) {
-            if (tid == 0) issue_chunk(t0 + LCH, zb ^ 1);
-            request_scalars(t0 + LCH);
+        // ---- 2b. this warp's C~ rows as A fragments (hi, lo) from its own rows of the tile
+        uint32_t Ch[4][4], Cl[4][4];
+        {
+            const int lm = lane >> 3, lr = lane & 7;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                const int row = 16 * warp + 8 * (lm & 1) + lr, col = 16 * ks + 8 * (lm >> 1);
+                ldsm_x4(Ch[ks], tC + swz(row, col, 256));
+                ldsm_x4(Cl[ks], tC + 128 + swz(row, col, 256));
+            }
         }
         // ---- 3. Y2 = C~ S^_in^T, G = C~ B~^T (causal part), W = mask / decay (G) (+ D on the diagonal), Y1 = W X
         float y1[4][4], y2[4][4];
@@ -449,10 +469,10 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
             for (int ks = 0; ks < 4; ++ks) {
                 uint32_t sh0[4], sl0[4], sh1[4], sl1[4];   // p tiles 0, 1 and 2, 3
                 const int row = 8 * (lm >> 1) + lr, col = 16 * ks + 8 * (lm & 1);
-                ldsm_x4(sh0, &sm.St[0][row][col]);
-                ldsm_x4(sl0, &sm.St[1][row][col]);
-                ldsm_x4(sh1, &sm.St[0][row + 16][col]);
-                ldsm_x4(sl1, &sm.St[1][row + 16][col]);
+                ldsm_x4(sh0, tS + swz(row, col, 128));
+                ldsm_x4(sl0, tS + 4096 + swz(row, col, 128));
+                ldsm_x4(sh1, tS + swz(row + 16, col, 128));
+                ldsm_x4(sl1, tS + 4096 + swz(row + 16, col, 128));
                 mma3x4(y2[0], y2[1], y2[2], y2[3], Ch[ks], Cl[ks], sh0, sl0, sh1, sl1);
             }
             const int ia = 16 * warp + g4, ib = ia + 8;
@@ -465,8 +485,8 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
                 for (int ks = 0; ks < 4; ++ks) {
                     uint32_t bh4[4], bl4[4];
                     const int row = 16 * jp + 8 * (lm >> 1) + lr, col = 16 * ks + 8 * (lm & 1);
-                    ldsm_x4(bh4, &sm.Bt[0][row][col]);
-                    ldsm_x4(bl4, &sm.Bt[1][row][col]);
+                    ldsm_x4(bh4, tB + swz(row, col, 256));
+                    ldsm_x4(bl4, tB + 128 + swz(row, col, 256));
                     mma_bf16(g0, Ch[ks], bh4[0], bh4[1]);
                     mma_bf16(g1, Ch[ks], bh4[2], bh4[3]);
                     mma_bf16(g0b, Ch[ks], bl4[0], bl4[1]);
@@ -497,10 +517,10 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
                 {
                     uint32_t xh0[4], xl0[4], xh1[4], xl1[4];
                     const int row = 8 * (lm >> 1) + lr, col = 16 * jp + 8 * (lm & 1);
-                    ldsm_x4(xh0, &sm.Xt[0][row][col]);
-                    ldsm_x4(xl0, &sm.Xt[1][row][col]);
-                    ldsm_x4(xh1, &sm.Xt[0][row + 16][col]);
-                    ldsm_x4(xl1, &sm.Xt[1][row + 16][col]);
+                    ldsm_x4(xh0, tX + swz(row, col, 128));
+                    ldsm_x4(xl0, tX + 4096 + swz(row, col, 128));
+                    ldsm_x4(xh1, tX + swz(row + 16, col, 128));
+                    ldsm_x4(xl1, tX + 4096 + swz(row + 16, col, 128));
                     mma3x4(y1[0], y1[1], y1[2], y1[3], wh, wl, xh0, xl0, xh1, xl1);
                 }
             }
@@ -509,8 +529,8 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
             uint32_t oh[2][4], ol[2][4];                   // [row a / b][p tile]
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt) {
-                const float2 ga = *reinterpret_cast<const float2*>(&sm.rz[zb][ia][8 * nt + 2 * t4]);
-                const float2 gb = *reinterpret_cast<const float2*>(&sm.rz[zb][ib][8 * nt + 2 * t4]);
+                const float2 ga = *reinterpret_cast<const float2*>(&sm.rz[ia][8 * nt + 2 * t4]);
+                const float2 gb = *reinterpret_cast<const float2*>(&sm.rz[ib][8 * nt + 2 * t4]);
                 split2(fmaf(ela, y2[nt][0], y1[nt][0]) * ga.x, fmaf(ela, y2[nt][1], y1[nt][1]) * ga.y, oh[0][nt], ol[0][nt]);
                 split2(fmaf(elb, y2[nt][2], y1[nt][2]) * gb.x, fmaf(elb, y2[nt][3], y1[nt][3]) * gb.y, oh[1][nt], ol[1][nt]);
             }
@@ -553,34 +573,26 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int p = p0 + g4 + 8 * (e & 1), j = 16 * ks + 2 * t4 + 8 * (e >> 1);
-                    const float2 xh = unpack2(*reinterpret_cast<const uint32_t*>(&sm.Xt[0][p][j]));
-                    const float2 xl = unpack2(*reinterpret_cast<const uint32_t*>(&sm.Xt[1][p][j]));
+                    const float2 xh = unpack2(*reinterpret_cast<const uint32_t*>(tX + swz(p, j, 128)));
+                    const float2 xl = unpack2(*reinterpret_cast<const uint32_t*>(tX + 4096 + swz(p, j, 128)));
                     split2((xh.x + xl.x) * sm.wj[j], (xh.y + xl.y) * sm.wj[j + 1], ah[e], al[e]);
                 }
                 {
                     uint32_t bh0[4], bl0[4], bh1[4], bl1[4];   // state columns n0 .. n0 + 15 and n0 + 16 .. n0 + 31
                     const int row = 16 * ks + 8 * (lm & 1) + lr, col = n0 + 8 * (lm >> 1);
-                    ldsm_x4_trans(bh0, &sm.Bt[0][row][col]);
-                    ldsm_x4_trans(bl0, &sm.Bt[1][row][col]);
-                    ldsm_x4_trans(bh1, &sm.Bt[0][row][col + 16]);
-                    ldsm_x4_trans(bl1, &sm.Bt[1][row][col + 16]);
+                    ldsm_x4_trans(bh0, tB + swz(row, col, 256));
+                    ldsm_x4_trans(bl0, tB + 128 + swz(row, col, 256));
+                    ldsm_x4_trans(bh1, tB + swz(row, col + 16, 256));
+                    ldsm_x4_trans(bl1, tB + 128 + swz(row, col + 16, 256));
                     mma3x4(S[0], S[1], S[2], S[3], ah, al, bh0, bl0, bh1, bl1);
                 }
             }
-            if (!last_chunk) {
-#pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
-                    uint32_t hi, lo;
-                    split2(S[nt][0], S[nt][1], hi, lo);
-                    *reinterpret_cast<uint32_t*>(&sm.St[0][p0 + g4][n0 + 8 * nt + 2 * t4]) = hi;
-                    *reinterpret_cast<uint32_t*>(&sm.St[1][p0 + g4][n0 + 8 * nt + 2 * t4]) = lo;
-                    split2(S[nt][2], S[nt][3], hi, lo);
-                    *reinterpret_cast<uint32_t*>(&sm.St[0][p0 + g4 + 8][n0 + 8 * nt + 2 * t4]) = hi;
-                    *reinterpret_cast<uint32_t*>(&sm.St[1][p0 + g4 + 8][n0 + 8 * nt + 2 * t4]) = lo;
-                }
-            }
+            if (!last_chunk) store_state_tile();
         }
+        // every operand tile and raw row of this chunk has been consumed: order these generic-proxy accesses before the copies
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();
+        if (!last_chunk && tid == 0) issue_chunk(t0 + LCH);
         return true;
     };
     bool failed = false;
