@@ -148,6 +148,15 @@ int32_t lumi_session_set_option(lumi_session* s, const char* name, int64_t value
  * position.  Sequences occupy slots 0..batch-1. */
 int32_t lumi_prefill(lumi_session* s, const uint32_t* tokens, int32_t batch, int32_t T, float* last_logits);
 
+/* The same for prompts of different lengths: tokens[batch][T_max] row-major, of which sequence b uses the first
+ * lengths[b] (1 <= lengths[b] <= T_max; what is stored behind them is not looked at).  Each sequence goes through its
+ * own tokens position by position (the reference's prefill, inference/src/main.rs:121-125, once per sequence) and ends
+ * in exactly the state a lumi_prefill of its own tokens alone would leave; last_logits [batch][vocab] (may be NULL) are
+ * those of each sequence's own last position.  Always token by token (the batched path takes rectangles only); at most
+ * 1024 sequences per call. */
+int32_t lumi_prefill_ragged(lumi_session* s, const uint32_t* tokens, const int32_t* lengths, int32_t batch, int32_t T_max,
+                            float* last_logits);
+
 /* One forward_step for each of `batch` sequences: consumes in_tokens[batch], writes the sampled /
  * argmax next token to out_tokens[batch] (may be NULL) and, if logits_out != NULL, the logits
  * [batch][vocab].  `step` indexes the Philox counter. */

@@ -23,7 +23,7 @@ _lib = None
 EXPORTS = [
     "lumi_last_error", "lumi_model_create", "lumi_model_load_tensor", "lumi_model_load_safetensors",
     "lumi_model_finalize", "lumi_model_free", "lumi_model_info", "lumi_session_create", "lumi_session_reset",
-    "lumi_session_free", "lumi_session_set_option", "lumi_prefill", "lumi_decode_step", "lumi_generate",
+    "lumi_session_free", "lumi_session_set_option", "lumi_prefill", "lumi_prefill_ragged", "lumi_decode_step", "lumi_generate",
     "lumi_decode_loop_device", "lumi_profile_step", "lumi_score", "lumi_session_read_state", "lumi_session_state_bytes", "lumi_session_save_state", "lumi_session_load_state", "lumi_debug_run_block", "lumi_k_gemm_bf16_tcgen05",
     "lumi_k_gemv", "lumi_debug_gemm_wait_timeout", "lumi_k_ssm_step", "lumi_k_ssd_prefill", "lumi_mamba_block_static",
 ]
@@ -69,6 +69,7 @@ def lib():
         L.lumi_session_free.restype = None
         L.lumi_session_set_option.argtypes = [vp, C.c_char_p, i64]
         L.lumi_prefill.argtypes = [vp, vp, i32, i32, vp]
+        L.lumi_prefill_ragged.argtypes = [vp, vp, vp, i32, i32, vp]
         L.lumi_decode_step.argtypes = [vp, vp, i32, C.POINTER(Sampling), i32, vp, vp]
         L.lumi_generate.argtypes = [vp, vp, i32, i32, i32, C.POINTER(Sampling), vp, vp, vp, C.POINTER(Stats)]
         L.lumi_decode_loop_device.argtypes = [vp, i32, i32, C.POINTER(C.c_float), C.POINTER(i64)]
@@ -212,6 +213,15 @@ class Session:
         B, T = prompts.shape
         logits = np.empty((B, self.model.config.vocab_size), dtype=np.float32) if want_logits else None
         check(lib().lumi_prefill(self._h, _ptr(prompts), B, T, _ptr(logits)))
+        return logits
+
+    def prefill_ragged(self, prompts, lengths, want_logits: bool = True):
+        """Prompts of different lengths: prompts [batch, T_max] of which row b uses the first lengths[b] tokens."""
+        prompts = np.ascontiguousarray(np.atleast_2d(prompts), dtype=np.uint32)
+        lengths = np.ascontiguousarray(lengths, dtype=np.int32)
+        B, T = prompts.shape
+        logits = np.empty((B, self.model.config.vocab_size), dtype=np.float32) if want_logits else None
+        check(lib().lumi_prefill_ragged(self._h, _ptr(prompts), _ptr(lengths), B, T, _ptr(logits)))
         return logits
 
     def score(self, tokens) -> np.ndarray:

@@ -338,7 +338,7 @@ extern "C" void lumi_session_free(lumi_session* s) {
     for (auto& g : s->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
     void* dev[] = {s->score_logits, s->gemm_counters, s->gemm_scratch, s->h, s->xprev, s->bprev, s->cum, s->kv_pool, s->page_table, s->kv_pos, s->x, s->proj, s->y32, s->logits,
                    s->act_hi, s->act_lo, s->tok_cur, s->finished, s->out_len, s->ctl, s->gen_out, s->prompt_dev, s->gen_dump,
-                   s->pf_x, s->pf_proj, s->pf_rb, s->pf_rc, s->pf_hi, s->pf_lo, s->slot_buf, s->xn_hi, s->xn_lo, s->ssq, s->attn_part, s->attn_part_count,
+                   s->pf_x, s->pf_proj, s->pf_rb, s->pf_rc, s->pf_hi, s->pf_lo, s->slot_buf, s->xn_hi, s->xn_lo, s->ssq, s->attn_part, s->attn_part_count, s->amax_val, s->amax_idx, s->row_len, s->xlast,
                    s->b1_layers, s->b1_grid_ctl, s->b1_amax_val, s->b1_amax_idx, s->b1_timing, s->b1_tagged};
     for (void* p : dev) if (p) cudaFree(p);
     if (s->ctl_host) cudaFreeHost(s->ctl_host);
@@ -391,8 +391,8 @@ static int32_t session_alloc(lumi_session* s) {
         s->kv_layer_bytes = B * s->pages_per_seq * 2 * kPageTokens * (size_t)c.kv_dim() * esz;
         LUMI_CUDA(cudaMalloc(&s->kv_pool, s->kv_layer_bytes * na));
         LUMI_CUDA(cudaMalloc(&s->page_table, sizeof(int32_t) * B * s->pages_per_seq));
-        // partial results of an attention context split over several CTAs: used only while batch x KV heads is below two
-        // CTAs per SM, so a fixed number of (row, KV head) units is enough
+        // partial results of an attention context split over several CTAs: used only while batch x KV heads is small
+        // enough for a split to pay, so a fixed number of (row, KV head) units is enough
         {
             const size_t pw = (size_t)(c.attn_n_heads / std::max(1, c.attn_kv_heads)) * (c.attn_head_dim() + 2);
             LUMI_CUDA(cudaMalloc(&s->attn_part, sizeof(float) * kAttnPartUnits * kAttnPartSlices * pw));
@@ -405,6 +405,8 @@ static int32_t session_alloc(lumi_session* s) {
     }
     LUMI_CUDA(cudaMalloc(&s->kv_pos, sizeof(int32_t) * B));
     LUMI_CUDA(cudaMalloc(&s->slot_buf, sizeof(int32_t) * B));
+    LUMI_CUDA(cudaMalloc(&s->row_len, sizeof(int32_t) * B));
+    LUMI_CUDA(cudaMalloc(&s->xlast, sizeof(float) * B * c.d_model));
     LUMI_CUDA(cudaMalloc(&s->gemm_counters, sizeof(int32_t) * 2 * kGemmCounters));
     LUMI_CUDA(cudaMemset(s->gemm_counters, 0, sizeof(int32_t) * 2 * kGemmCounters));
     LUMI_CUDA(cudaMalloc(&s->gemm_scratch, sizeof(float) * 2 * kGemmScratchFloats));
@@ -415,6 +417,10 @@ static int32_t session_alloc(lumi_session* s) {
     LUMI_CUDA(cudaMalloc(&s->proj, sizeof(float) * B * pmax));
     LUMI_CUDA(cudaMalloc(&s->y32, sizeof(float) * B * kmax));
     LUMI_CUDA(cudaMalloc(&s->logits, sizeof(float) * B * c.vocab));
+    // per-CTA argmax partials of the greedy head at batch <= 8 (at most one CTA per vocabulary row)
+    s->amax_stride = c.vocab;
+    LUMI_CUDA(cudaMalloc(&s->amax_val, sizeof(float) * 8 * (size_t)c.vocab));
+    LUMI_CUDA(cudaMalloc(&s->amax_idx, sizeof(int) * 8 * (size_t)c.vocab));
     if (s->m->wdtype == LUMI_DTYPE_BF16) {
         // rows padded to a whole 128-row tile so TMA boxes never start outside the allocation
         const size_t rows = (B + 127) / 128 * 128;
@@ -559,6 +565,7 @@ struct StepPlan {
     // already in xn_hi / xn_lo / ssq — left there by the epilogue of the product that last updated the residual
     bool xn_ready = false;
     int ssq_parts = 0;
+    const int32_t* row_len = nullptr;                             // prompts of different lengths (ragged prefill), else null
     std::vector<std::pair<int, cudaEvent_t>>* prof = nullptr;     // profiling: an event before every launch
 };
 
@@ -674,6 +681,7 @@ int32_t mamba_block(StepPlan& p, const Layer& L, cudaEvent_t ev_gemm_done = null
     a.yhi = p.tc ? s->act_hi + aoff : nullptr;
     a.ylo = (p.tc && s->opt_split) ? s->act_lo + aoff : nullptr;
     a.B = p.B; a.H = c.n_heads; a.P = c.head_dim(); a.N = c.d_state; a.G = c.n_groups; a.eps = c.eps;
+    a.row_len = p.row_len; a.ctl = s->ctl;
     p.fam = FAM_SSM;
     mark(p);
     LUMI_CUDA(launch_ssm_step(a, p.st_lo));
@@ -710,6 +718,7 @@ int32_t attention_block(StepPlan& p, const Layer& L) {
     if (a.max_tokens > s->max_tokens_kv) a.max_tokens = s->max_tokens_kv;
     a.rope_base = c.attn_rope_base;
     a.ctl = s->ctl;
+    a.row_len = p.row_len;
     if ((long)p.B * c.attn_kv_heads <= kAttnPartUnits) {      // few rows: the context may be split over CTAs
         a.part = s->attn_part; a.part_count = s->attn_part_count;
         a.max_ctx_hint = L.window > 0 ? std::min(L.window, a.max_tokens) : a.max_tokens;
@@ -742,17 +751,18 @@ static int pdl_tc_max() {
 }
 
 int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches,
-                     std::vector<std::pair<int, cudaEvent_t>>* prof = nullptr) {
+                     std::vector<std::pair<int, cudaEvent_t>>* prof = nullptr, const int32_t* row_len = nullptr) {
     const Config& c = s->m->cfg;
     StepPlan p{s, B, use_tc(s, B)};
     p.prof = prof;
+    p.row_len = row_len;
     // dependent launch overlaps each kernel's prologue (weight prefetch) with its predecessor; it is
     // used on the weight-streaming path, where launch gaps are the same order as the kernels
     struct PdlScope { PdlScope(bool on) { set_launch_pdl(on); } ~PdlScope() { set_launch_pdl(false); } } pdl_scope(s->opt_pdl && prof == nullptr && (!p.tc || (pdl_tc_max() > 0 && B <= pdl_tc_max())));
     p.st_hi = p.st_lo = s->stream;
     mark(p);
-    LUMI_CUDA(launch_embed(s->m->embedding.p, s->m->embedding.dtype, s->tok_cur, s->x, B, c.d_model, c.vocab, s->ctl, s->stream));
-    const bool two_lanes = p.tc && prof == nullptr && s->opt_overlap > 0 && B >= s->opt_overlap && s->m->n_attn == 0 && B >= 2;
+    LUMI_CUDA(launch_embed(s->m->embedding.p, s->m->embedding.dtype, s->tok_cur, s->x, B, c.d_model, c.vocab, s->ctl, s->stream, row_len));
+    const bool two_lanes = p.tc && prof == nullptr && row_len == nullptr && s->opt_overlap > 0 && B >= s->opt_overlap && s->m->n_attn == 0 && B >= 2;
     if (!two_lanes) {
         for (const Layer& L : s->m->layers) {
             if (L.is_attn) LUMI_TRY(attention_block(p, L));
@@ -792,6 +802,24 @@ int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches,
         p.xn_ready = lane[0].xn_ready && lane[1].xn_ready && lane[0].ssq_parts == lane[1].ssq_parts;
         p.ssq_parts = lane[0].ssq_parts;
     }
+    // greedy head at small batch: the argmax rides behind the lm_head GEMV (per-CTA partials) and one small kernel
+    // finishes the token and the step — no logits are written and nothing re-reads them
+    const bool fused = with_head && s->fused_head && !p.tc && B <= 8 && c.vocab >= 4096 && prof == nullptr;
+    if (fused) {
+        p.fam = FAM_HEAD;
+        int nparts = 0;
+        GemvArgs g{s->x, c.d_model, s->m->embedding.p, s->m->embedding.dtype, nullptr, c.vocab, nullptr, s->m->final_norm_g, B, c.vocab,
+                   c.d_model, c.eps, 0, &s->ctl->status};
+        g.amax_val = s->amax_val; g.amax_idx = s->amax_idx; g.amax_stride = s->amax_stride; g.amax_parts = &nparts;
+        mark(p);
+        LUMI_CUDA(launch_gemv(g, s->stream));
+        p.fam = FAM_SAMPLE;
+        mark(p);
+        LUMI_CUDA(launch_head_finish(s->amax_val, s->amax_idx, nparts, s->amax_stride, B, s->ctl, s->tok_cur, s->finished, s->out_len,
+                                     s->m->n_attn > 0 ? s->kv_pos : nullptr, s->stream));
+        *launches = p.n;
+        return LUMI_OK;
+    }
     if (with_head) {
         p.fam = FAM_HEAD;
         if (p.tc) LUMI_TRY(ensure_norm_input(p, s->x, s->m->final_norm_g));
@@ -801,9 +829,13 @@ int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches,
         mark(p);
         LUMI_CUDA(launch_sample(s->logits, B, c.vocab, s->ctl, s->tok_cur, s->finished, s->out_len, s->stream));
     }
+    if (row_len != nullptr) {                      // ragged prefill: keep the residual of every sequence that is at its last prompt token
+        mark(p);
+        LUMI_CUDA(launch_capture_last(s->x, s->xlast, row_len, s->ctl, B, c.d_model, s->stream));
+    }
     p.fam = FAM_SAMPLE;
     mark(p);
-    LUMI_CUDA(launch_advance_step(s->ctl, s->m->n_attn > 0 ? s->kv_pos : nullptr, B, with_head ? 1 : 0, s->stream));
+    LUMI_CUDA(launch_advance_step(s->ctl, s->m->n_attn > 0 ? s->kv_pos : nullptr, B, with_head ? 1 : 0, s->stream, row_len));
     if (prof) {   // closing event
         p.fam = FAM_COUNT;
         mark(p);
@@ -825,7 +857,7 @@ int32_t run_step(lumi_session* s, int B, bool with_head, int reps = 1) {
         }
         return LUMI_OK;
     }
-    const int64_t key = (((int64_t)B * 2 + (with_head ? 1 : 0)) << 8) | (int64_t)reps;
+    const int64_t key = (((((int64_t)B * 2 + (with_head ? 1 : 0)) << 1) | (s->fused_head ? 1 : 0)) << 8) | (int64_t)reps;
     auto it = s->graphs.find(key);
     if (it == s->graphs.end()) {
         GraphEntry ge;
@@ -1155,6 +1187,7 @@ extern "C" int32_t lumi_prefill(lumi_session* s, const uint32_t* tokens, int32_t
     LUMI_TRY(check_batch(s, batch));
     if (!tokens || T <= 0) return fail(LUMI_E_INVALID, "prefill needs tokens and T > 0");
     LUMI_CUDA(cudaSetDevice(s->m->device));
+    s->fused_head = false;
     LUMI_TRY(upload_prompt(s, tokens, batch, T));
     fill_ctl(s, batch, nullptr);
     s->ctl_host->prompt = s->prompt_dev;
@@ -1176,6 +1209,54 @@ extern "C" int32_t lumi_prefill(lumi_session* s, const uint32_t* tokens, int32_t
     return check_status(s);
 }
 
+// Prompts of different lengths in one call.  Every sequence goes through its own tokens position by position, as
+// lumi_prefill's token-by-token form does; once a sequence's prompt has ended, the kernels that own per-sequence state
+// (state step, cache append, position) skip it, so it simply waits for the longest one.
+extern "C" int32_t lumi_prefill_ragged(lumi_session* s, const uint32_t* tokens, const int32_t* lengths, int32_t batch, int32_t T_max,
+                                       float* last_logits) {
+    LUMI_TRY(check_batch(s, batch));
+    if (!tokens || !lengths || T_max <= 0) return fail(LUMI_E_INVALID, "ragged prefill needs tokens, lengths and T_max > 0");
+    if (batch > 1024) return fail(LUMI_E_UNSUPPORTED, "ragged prefill takes at most 1024 sequences per call");
+    int longest = 0;
+    for (int b = 0; b < batch; ++b) {
+        if (lengths[b] < 1 || lengths[b] > T_max) return fail(LUMI_E_INVALID, "length %d of sequence %d outside [1, %d]", lengths[b], b, T_max);
+        longest = std::max(longest, lengths[b]);
+    }
+    LUMI_CUDA(cudaSetDevice(s->m->device));
+    s->fused_head = false;
+    LUMI_TRY(upload_prompt(s, tokens, batch, T_max));
+    LUMI_CUDA(cudaMemcpyAsync(s->row_len, lengths, sizeof(int32_t) * batch, cudaMemcpyHostToDevice, s->stream));
+    fill_ctl(s, batch, nullptr);
+    s->ctl_host->prompt = s->prompt_dev;
+    s->ctl_host->prompt_len = longest;
+    LUMI_TRY(push_ctl(s));
+    const bool mega = s->opt_mega;
+    s->opt_mega = 0;
+    int32_t rc = LUMI_OK;
+    for (int t = 0; t < longest && rc == LUMI_OK; ++t) {       // launched directly: the captured graphs of the step do not carry the length table
+        int64_t n = 0;
+        rc = enqueue_step(s, batch, false, &n, nullptr, s->row_len);
+        s->launches += n;
+    }
+    s->opt_mega = mega;
+    LUMI_TRY(rc);
+    if (last_logits) {
+        // final norm + tied head on each sequence's residual at its own last token
+        LUMI_CUDA(cudaMemcpyAsync(s->x, s->xlast, sizeof(float) * batch * s->m->cfg.d_model, cudaMemcpyDeviceToDevice, s->stream));
+        StepPlan p{s, batch, use_tc(s, batch)};
+        p.st_hi = p.st_lo = s->stream;
+        const Config& c = s->m->cfg;
+        if (p.tc) LUMI_TRY(ensure_norm_input(p, s->x, s->m->final_norm_g));
+        p.fam = FAM_HEAD;
+        LUMI_TRY(linear(p, s->m->embedding, s->x, c.d_model, s->logits, c.vocab, nullptr, s->m->final_norm_g, 0, c.vocab, true));
+        s->launches += p.n;
+        LUMI_CUDA(cudaMemcpyAsync(last_logits, s->logits, sizeof(float) * batch * c.vocab, cudaMemcpyDeviceToHost, s->stream));
+    }
+    LUMI_TRY(pull_ctl(s));
+    LUMI_CUDA(cudaStreamSynchronize(s->stream));
+    return check_status(s);
+}
+
 // Teacher-forced scoring: log p(tokens[b][t+1] | tokens[b][0..t]) for t = 0 .. T-2, the quantity the reference's
 // `evaluate` command sums into perplexities and continuation scores (inference/src/eval.rs:39-139, over
 // forward_window's logits, model.rs:806-826).  The session's state ends up as after a prefill of all T tokens.
@@ -1183,6 +1264,7 @@ extern "C" int32_t lumi_score(lumi_session* s, const uint32_t* tokens, int32_t b
     LUMI_TRY(check_batch(s, batch));
     if (!tokens || !logprobs_out || T < 2) return fail(LUMI_E_INVALID, "score needs tokens, an output buffer and T >= 2");
     LUMI_CUDA(cudaSetDevice(s->m->device));
+    s->fused_head = false;
     LUMI_TRY(upload_prompt(s, tokens, batch, T));
     LUMI_TRY(grow(s->gen_dump, s->gen_dump_cap, (size_t)batch * (T - 1)));
     fill_ctl(s, batch, nullptr);
@@ -1222,6 +1304,7 @@ extern "C" int32_t lumi_decode_step(lumi_session* s, const uint32_t* in_tokens, 
     LUMI_TRY(check_batch(s, batch));
     if (!in_tokens) return fail(LUMI_E_INVALID, "in_tokens is null");
     LUMI_CUDA(cudaSetDevice(s->m->device));
+    s->fused_head = (!sp || sp->temperature <= 0.f) && logits_out == nullptr;
     fill_ctl(s, batch, sp);
     s->ctl_host->step = step;
     LUMI_TRY(push_ctl(s));
@@ -1250,6 +1333,7 @@ extern "C" int32_t lumi_generate(lumi_session* s, const uint32_t* prompts, int32
     if (!prompts || T <= 0 || n_new < 0 || !sp) return fail(LUMI_E_INVALID, "generate needs prompts, T > 0, n_new >= 0 and sampling parameters");
     LUMI_CUDA(cudaSetDevice(s->m->device));
     const int V = s->m->cfg.vocab;
+    s->fused_head = sp->temperature <= 0.f && logits_dump == nullptr;
     LUMI_TRY(upload_prompt(s, prompts, batch, T));
     LUMI_TRY(grow(s->gen_out, s->gen_out_cap, (size_t)std::max(1, n_new) * batch));
     if (logits_dump) LUMI_TRY(grow(s->gen_dump, s->gen_dump_cap, (size_t)std::max(1, n_new) * batch * V));
@@ -1324,6 +1408,7 @@ extern "C" int32_t lumi_decode_loop_device(lumi_session* s, int32_t batch, int32
     LUMI_CUDA(cudaSetDevice(s->m->device));
     lumi_sampling sp{};
     sp.ignore_eos = 1;
+    s->fused_head = true;
     fill_ctl(s, batch, &sp);
     LUMI_TRY(push_ctl(s));
     const int64_t l0 = s->launches;

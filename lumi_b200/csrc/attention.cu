@@ -64,6 +64,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     const float* q = a.qkv + (size_t)r * a.ldq + (size_t)kvh * HPK * HD;
     const float* kn = a.qkv + (size_t)r * a.ldq + D + kvh * HD;
     const float* vn = kn + KV;
+    if (a.row_len != nullptr) {                          // prompts of different lengths: this sequence's prompt has ended
+        const int pp = a.ctl->prompt_pos;
+        if (pp < a.ctl->prompt_len && pp >= a.row_len[b]) return;
+    }
     const int pos = a.pos[b] + r % a.rows_per_seq;
     const int32_t* pt = a.page_table + (size_t)b * a.pages_per_seq;
     const int cap = a.window > 0 ? min(a.window, a.max_tokens) : a.max_tokens;
@@ -333,12 +337,14 @@ static int attn_sm_count() {
 
 template <typename KT, int HD, int HPK>
 cudaError_t launch_t(const AttnArgs& a, cudaStream_t st) {
-    // slices of the context: enough CTAs for two per SM, at least one tile each, and only where the caller gave
+    // slices of the context: enough CTAs (see below), at least one tile each, and only where the caller gave
     // room for the partial results (decode); the batched prefill has rows to spare
     int nsplit = 1;
     if (a.part != nullptr && a.part_count != nullptr && a.phase == 0) {
+        // eight CTAs per SM: a CTA alternates between loading (scores, context) and reducing, so it takes several per
+        // SM to keep HBM busy, and a count well above the SM count evens out the last wave
         const long units = (long)a.B * a.kv_heads;
-        nsplit = (int)((2L * attn_sm_count() + units - 1) / units);
+        nsplit = (int)((8L * attn_sm_count() + units - 1) / units);
         const int by_len = (a.max_ctx_hint + kAttnTile - 1) / kAttnTile;
         if (nsplit > by_len) nsplit = by_len;
         if (nsplit > kAttnMaxSplits) nsplit = kAttnMaxSplits;

@@ -148,6 +148,12 @@ struct lumi_session {
     size_t pf_rows = 0;
     // options
     int opt_gemm = 0, opt_split = 1, opt_graph = 1, opt_pdl = 1, opt_mega = 0;
+    // greedy head with the argmax fused behind the lm_head GEMV (batch <= 8): set by the caller of a step that wants
+    // neither sampling nor the logits; per (row, CTA) partials
+    bool fused_head = false;
+    float* amax_val = nullptr;
+    int* amax_idx = nullptr;
+    int amax_stride = 0;
     // batch-1 persistent kernel
     bool b1_ok = false;
     lumi::B1Layer* b1_layers = nullptr;
@@ -167,6 +173,8 @@ struct lumi_session {
     float* attn_part = nullptr;        // partial (max, sum, context) of attention contexts split over CTAs
     int32_t* attn_part_count = nullptr;
     int32_t* slot_buf = nullptr;       // [max_batch] slot list of a partial reset
+    int32_t* row_len = nullptr;        // [max_batch] prompt lengths of a ragged prefill
+    float* xlast = nullptr;            // [max_batch][d_model] residual rows at each sequence's last prompt token
     int pages_per_seq = 0;
     // activations
     float *x = nullptr, *proj = nullptr, *y32 = nullptr, *logits = nullptr;
@@ -210,6 +218,12 @@ struct GemvArgs {
     int act;                         // 0 none; 1: D = sigmoid(W_gate a) * (W_up a), W = [gate rows | up rows], N = rows of each
     int32_t* status = nullptr;       // device word that receives STATUS_TIMEOUT if a bounded wait gives up; may be null
     bool allow_preload = true;       // false: never the single-wave preloading kernel (the only GEMV with a device-side wait)
+    // greedy head: per (batch row, CTA) the best (value, row) of the CTA's rows goes to amax_val / amax_idx
+    // [M][amax_stride]; *amax_parts (host) receives the number of partials per row; D may then be null (no logits written)
+    float* amax_val = nullptr;
+    int* amax_idx = nullptr;
+    int amax_stride = 0;
+    int* amax_parts = nullptr;
 };
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);
 cudaError_t launch_logprob(const float* logits, int B, int V, const uint32_t* targets, float* out, int out_stride, int out_col,
@@ -221,7 +235,7 @@ cudaError_t launch_logprob_rows(const float* logits, int rows, int V, const uint
 void set_launch_pdl(bool on);
 
 cudaError_t launch_embed(const void* emb, int dtype, const uint32_t* tok_cur, float* x, int B, int D, int vocab,
-                         StepCtl* ctl, cudaStream_t st);
+                         StepCtl* ctl, cudaStream_t st, const int32_t* row_len = nullptr);
 // x[B][D] fp32 -> RMSNorm(gamma) -> bf16 hi (+ lo if lo != null); gamma null = plain split.
 // ssq != null: hi / lo = x * gamma without the per-row scale, ssq[b * ssq_stride] = sum of x^2 (for a GEMM with a folded norm)
 cudaError_t launch_norm_split(const float* x, const float* gamma, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int D,
@@ -235,6 +249,10 @@ struct SsmArgs {
     __nv_bfloat16 *yhi, *ylo;        // [B][d_inner] bf16 halves, or null
     int B, H, P, N, G;
     float eps;
+    // prompts of different lengths (null otherwise): sequences whose prompt has ended (ctl->prompt_pos >= row_len[b]
+    // while the prefill runs) are left untouched
+    const int32_t* row_len = nullptr;
+    const StepCtl* ctl = nullptr;
 };
 cudaError_t launch_ssm_step(const SsmArgs& a, cudaStream_t st);
 bool ssm_shape_supported(int P, int N);
@@ -244,7 +262,11 @@ cudaError_t launch_state_reset(float* h, float* xprev, float* bprev, float* cum,
 
 cudaError_t launch_sample(const float* logits, int B, int V, StepCtl* ctl, uint32_t* tok_cur, int32_t* finished,
                           int32_t* out_len, cudaStream_t st);
-cudaError_t launch_advance_step(StepCtl* ctl, int32_t* kv_pos, int B, int sampled, cudaStream_t st);
+cudaError_t launch_advance_step(StepCtl* ctl, int32_t* kv_pos, int B, int sampled, cudaStream_t st, const int32_t* row_len = nullptr);
+cudaError_t launch_capture_last(const float* x, float* xlast, const int32_t* row_len, const StepCtl* ctl, int B, int D, cudaStream_t st);
+// greedy head, second stage for batch <= 8: argmax over the GEMV's partials, token bookkeeping, end-of-step bookkeeping
+cudaError_t launch_head_finish(const float* amax_val, const int* amax_idx, int nparts, int stride, int B, StepCtl* ctl, uint32_t* tok_cur,
+                               int32_t* finished, int32_t* out_len, int32_t* kv_pos, cudaStream_t st);
 
 // ---- attention (attention.cu) ---------------------------------------------------------------------
 struct AttnArgs {
@@ -268,9 +290,10 @@ struct AttnArgs {
     float* part = nullptr;
     int32_t* part_count = nullptr;
     int max_ctx_hint = 0;
+    const int32_t* row_len = nullptr;    // prompts of different lengths: rows whose prompt has ended are skipped (decode form only)
 };
 constexpr int kAttnPartSlices = 16;
-constexpr int kAttnPartUnits = 296;        // (row, KV head) pairs below which a context is split: two CTAs per SM
+constexpr int kAttnPartUnits = 2048;       // (row, KV head) pairs up to which a context may be split over CTAs (sizes the partial-result buffer)
 cudaError_t launch_attention_decode(const AttnArgs& a, cudaStream_t st);
 cudaError_t launch_kv_advance(int32_t* kv_pos, int b0, int nb, int by, cudaStream_t st);
 

@@ -97,13 +97,16 @@ template <> struct WLoad<__nv_bfloat16> {
 // ---- embedding gather (model.rs:772-773) -----------------------------------------------------------
 template <typename WT>
 __global__ void embed_kernel(const WT* __restrict__ emb, const uint32_t* tok_cur, float* x,
-                             int D, int vocab, StepCtl* ctl) {
+                             int D, int vocab, StepCtl* ctl, const int32_t* row_len) {
     const int b = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
     // during prefill the token comes from the uploaded prompt, afterwards from the last sampled one
     const int pp = ctl->prompt_pos;
     uint32_t t = (pp < ctl->prompt_len) ? ctl->prompt[(size_t)pp * ctl->batch + b] : tok_cur[b];
+    // prompts of different lengths: a sequence whose prompt has ended idles (its state is left alone by the kernels
+    // that own state); what is stored beyond its length is padding and is not looked at
+    if (row_len != nullptr && pp < ctl->prompt_len && pp >= row_len[b]) t = 0;
     if (t >= (uint32_t)vocab) {          // reported to the host; the row read stays in bounds
         if (threadIdx.x == 0) atomicOr(&ctl->status, STATUS_BAD_TOKEN);
         t = 0;
@@ -180,7 +183,8 @@ template <> struct WRaw<__nv_bfloat16> {
 template <typename WT, int NB, int RPW, int ACT>
 __global__ void __launch_bounds__(256) gemv_kernel(const float* A, int lda, const WT* __restrict__ W,
                                                    float* D, int ldd, const float* R,
-                                                   const float* __restrict__ gamma, int M, int N, int K, float eps, int KS) {
+                                                   const float* __restrict__ gamma, int M, int N, int K, float eps, int KS,
+                                                   float* amax_val, int* amax_idx, int amax_stride) {
     extern __shared__ float4 gemv_smem4[];
     float* xs = reinterpret_cast<float*>(gemv_smem4);
     constexpr int E = WLoad<WT>::E;
@@ -281,17 +285,23 @@ __global__ void __launch_bounds__(256) gemv_kernel(const float* A, int lda, cons
                 for (int b = 0; b < NB; ++b) part[warp][r][b] = acc[r][b];
         }
         __syncthreads();
-        if (seg != 0) return;
+        if (seg == 0) {
 #pragma unroll
-        for (int r = 0; r < NR; ++r)
+            for (int r = 0; r < NR; ++r)
 #pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                float t = part[warp][r][b];
-                for (int sg = 1; sg < KS; ++sg) t += part[warp + sg][r][b];
-                acc[r][b] = t;
-            }
+                for (int b = 0; b < NB; ++b) {
+                    float t = part[warp][r][b];
+                    for (int sg = 1; sg < KS; ++sg) t += part[warp + sg][r][b];
+                    acc[r][b] = t;
+                }
+        }
     }
-    if (lane == 0 && row0 < N) {
+    // greedy head: this warp's best (value, lowest row on ties) per batch row, for the per-CTA partial below
+    float bestv[NB];
+    int besti[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) { bestv[b] = -INFINITY; besti[b] = 0x7fffffff; }
+    if (seg == 0 && lane == 0 && row0 < N) {
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
             int row = row0 + r;
@@ -303,8 +313,29 @@ __global__ void __launch_bounds__(256) gemv_kernel(const float* A, int lda, cons
                 if constexpr (ACT == 1) v = __fmul_rn(sigmoid_ref(v), acc[RPW + r][b]);     // model.rs:550-552
                 size_t o = (size_t)(m0 + b) * ldd + row;
                 if (R != nullptr) v = __fadd_rn(v, R[o]);
-                D[o] = v;
+                if (D != nullptr) D[o] = v;
+                if (v > bestv[b] || (v == bestv[b] && row < besti[b])) { bestv[b] = v; besti[b] = row; }
             }
+        }
+    }
+    if (amax_val != nullptr) {
+        // argmax fused behind the product (replaces the host-side argmax of inference/src/main.rs:142-143): one
+        // (value, row) partial per CTA and batch row; a small second stage picks among the partials
+        __shared__ float sbv[8][NB];
+        __shared__ int sbi[8][NB];
+        if (lane == 0) {
+#pragma unroll
+            for (int b = 0; b < NB; ++b) { sbv[warp][b] = bestv[b]; sbi[warp][b] = besti[b]; }
+        }
+        __syncthreads();
+        if ((int)threadIdx.x < nb) {
+            const int b = threadIdx.x;
+            float bv = sbv[0][b];
+            int bi = sbi[0][b];
+            for (int w = 1; w < 8; ++w)
+                if (sbv[w][b] > bv || (sbv[w][b] == bv && sbi[w][b] < bi)) { bv = sbv[w][b]; bi = sbi[w][b]; }
+            amax_val[(size_t)(m0 + b) * amax_stride + blockIdx.x] = bv;
+            amax_idx[(size_t)(m0 + b) * amax_stride + blockIdx.x] = bi;
         }
     }
 }
@@ -670,6 +701,12 @@ __global__ void __launch_bounds__(256, MINB) ssm_step_kernel(SsmArgs a) {
 
     TL_T0
     pdl_launch_dependents();
+    // prompts of different lengths: a sequence whose prompt has ended keeps its state until the others are done
+    // (prompt_pos was advanced by the previous step, which has finished: see below)
+    if (a.row_len != nullptr) {
+        const int pp = a.ctl->prompt_pos;
+        if (pp < a.ctl->prompt_len && pp >= a.row_len[b]) return;
+    }
     // State is only ever written by this same kernel one token earlier, and every step starts with a
     // kernel that is not launched early, so the whole previous step has finished before this line:
     // the state can be requested ahead of the dependency wait and its HBM latency runs under the
@@ -1129,12 +1166,59 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* logits, int V
     }
 }
 
+// Greedy head, second stage (batch <= 8): one warp per sequence picks the best of the per-CTA partials the head's GEMV
+// left behind (value, lowest id on ties — the rule of the single-stage argmax), records the token exactly as
+// sample_kernel does, and the block then does the end-of-step bookkeeping of advance_step_kernel.  One launch
+// instead of two, and nothing re-reads the logits.
+__global__ void __launch_bounds__(256) head_finish_kernel(const float* amax_val, const int* amax_idx, int nparts, int stride, int B,
+                                                         StepCtl* ctl, uint32_t* tok_cur, int32_t* finished, int32_t* out_len,
+                                                         int32_t* kv_pos) {
+    const int b = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int step = ctl->step;
+    if (b < B) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = lane; i < nparts; i += 32) {
+            const float v = amax_val[(size_t)b * stride + i];
+            const int id = amax_idx[(size_t)b * stride + i];
+            if (better(v, id, bv, bi)) { bv = v; bi = id; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) {
+            tok_cur[b] = (uint32_t)bi;
+            if (ctl->record) {
+                ctl->out_tokens[(size_t)step * ctl->batch + b] = (uint32_t)bi;
+                if (!finished[b]) {
+                    if ((uint32_t)bi == ctl->eos_id && !ctl->ignore_eos) finished[b] = 1;   // main.rs:150
+                    else out_len[b] += 1;
+                }
+            }
+            if (kv_pos != nullptr) kv_pos[b] += 1;
+        }
+    }
+    __syncthreads();                       // every warp has read ctl->step
+    if (threadIdx.x == 0) {
+        if (ctl->prompt_pos < ctl->prompt_len) ctl->prompt_pos += 1;
+        ctl->step += 1;
+    }
+}
+
 // End of a step: next prompt position / next output row, and one more cached token per sequence.
-__global__ void advance_step_kernel(StepCtl* ctl, int32_t* kv_pos, int B, int sampled) {
+__global__ void advance_step_kernel(StepCtl* ctl, int32_t* kv_pos, int B, int sampled, const int32_t* row_len) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     pdl_launch_dependents();
     pdl_wait();
-    if (kv_pos != nullptr && i < B) kv_pos[i] += 1;
+    const int pp0 = ctl->prompt_pos;
+    const bool idle = row_len != nullptr && i < B && pp0 < ctl->prompt_len && pp0 >= row_len[i];
+    __syncthreads();                       // block 0 changes prompt_pos below; B <= blockDim.x * gridDim.x rows read it above
+    if (kv_pos != nullptr && i < B && !idle) kv_pos[i] += 1;
     if (i == 0) {
         if (ctl->prompt_pos < ctl->prompt_len) ctl->prompt_pos += 1;
         if (sampled) ctl->step += 1;
@@ -1182,7 +1266,7 @@ static cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_
 }
 
 cudaError_t launch_embed(const void* emb, int dtype, const uint32_t* tok_cur, float* x, int B, int D, int vocab,
-                         StepCtl* ctl, cudaStream_t st) {
+                         StepCtl* ctl, cudaStream_t st, const int32_t* row_len) {
     // The first kernel of a step is never launched early: it starts only when the previous step has
     // completely finished, which is what lets later kernels of this step read state ahead of their
     // own dependency wait.
@@ -1190,9 +1274,9 @@ cudaError_t launch_embed(const void* emb, int dtype, const uint32_t* tok_cur, fl
     g_pdl = false;
     cudaError_t e;
     if (dtype == LUMI_DTYPE_BF16)
-        e = launch_k(embed_kernel<__nv_bfloat16>, dim3(B), dim3(128), 0, st, (const __nv_bfloat16*)emb, tok_cur, x, D, vocab, ctl);
+        e = launch_k(embed_kernel<__nv_bfloat16>, dim3(B), dim3(128), 0, st, (const __nv_bfloat16*)emb, tok_cur, x, D, vocab, ctl, row_len);
     else
-        e = launch_k(embed_kernel<float>, dim3(B), dim3(128), 0, st, (const float*)emb, tok_cur, x, D, vocab, ctl);
+        e = launch_k(embed_kernel<float>, dim3(B), dim3(128), 0, st, (const float*)emb, tok_cur, x, D, vocab, ctl, row_len);
     g_pdl = keep;
     return e;
 }
@@ -1212,7 +1296,12 @@ static cudaError_t gemv_launch(const GemvArgs& a, int KS, cudaStream_t st) {
     }
     const int rows_per_cta = (8 / KS) * RPW;
     dim3 grid((a.N + rows_per_cta - 1) / rows_per_cta, (a.M + NB - 1) / NB);
-    return launch_k(kern, grid, dim3(256), smem, st, a.A, a.lda, (const WT*)a.W, a.D, a.ldd, a.R, a.gamma, a.M, a.N, a.K, a.eps, KS);
+    if (a.amax_val != nullptr) {
+        if ((int)grid.x > a.amax_stride) return cudaErrorInvalidValue;
+        if (a.amax_parts != nullptr) *a.amax_parts = (int)grid.x;
+    }
+    return launch_k(kern, grid, dim3(256), smem, st, a.A, a.lda, (const WT*)a.W, a.D, a.ldd, a.R, a.gamma, a.M, a.N, a.K, a.eps, KS,
+                    a.amax_val, a.amax_idx, a.amax_stride);
 }
 
 template <typename WT, int NB, int ACT>
@@ -1298,7 +1387,7 @@ static cudaError_t gemv_pre_launch(const GemvArgs& a, int rows_per_cta, size_t s
 template <typename WT>
 static bool gemv_pre_try(const GemvArgs& a, cudaStream_t st, cudaError_t* err) {
     constexpr int E = WLoad<WT>::E;
-    if (!gemv_pre_enabled() || !a.allow_preload || a.act != 0 || a.M > 4 || a.M < 1 || (a.K % E) != 0 || a.K < E) return false;
+    if (!gemv_pre_enabled() || !a.allow_preload || a.amax_val != nullptr || a.act != 0 || a.M > 4 || a.M < 1 || (a.K % E) != 0 || a.K < E) return false;
     const int KC = a.K / E;
     const int U = (KC + 31) / 32;
     if (U > 16 || KC != 32 * U || (U & (U - 1)) != 0) return false;     // rows of exactly 32 * U chunks, U a power of two
@@ -1485,8 +1574,27 @@ cudaError_t launch_logprob(const float* logits, int B, int V, const uint32_t* ta
     return cudaGetLastError();
 }
 
-cudaError_t launch_advance_step(StepCtl* ctl, int32_t* kv_pos, int B, int sampled, cudaStream_t st) {
-    return launch_k(advance_step_kernel, dim3((B + 127) / 128), dim3(128), 0, st, ctl, kv_pos, B, sampled);
+cudaError_t launch_head_finish(const float* amax_val, const int* amax_idx, int nparts, int stride, int B, StepCtl* ctl, uint32_t* tok_cur,
+                               int32_t* finished, int32_t* out_len, int32_t* kv_pos, cudaStream_t st) {
+    if (B < 1 || B > 8) return cudaErrorInvalidValue;
+    return launch_k(head_finish_kernel, dim3(1), dim3(256), 0, st, amax_val, amax_idx, nparts, stride, B, ctl, tok_cur, finished, out_len, kv_pos);
+}
+
+cudaError_t launch_advance_step(StepCtl* ctl, int32_t* kv_pos, int B, int sampled, cudaStream_t st, const int32_t* row_len) {
+    if (row_len != nullptr && B > 1024) return cudaErrorInvalidValue;       // one block, so every row sees prompt_pos before it moves
+    const int threads = row_len != nullptr ? ((B + 31) / 32) * 32 : 128;
+    return launch_k(advance_step_kernel, dim3((B + threads - 1) / threads), dim3(threads), 0, st, ctl, kv_pos, B, sampled, row_len);
+}
+
+// Prompts of different lengths: the residual row of every sequence that is at its last prompt token goes to xlast.
+__global__ void capture_last_kernel(const float* x, float* xlast, const int32_t* row_len, const StepCtl* ctl, int D) {
+    const int b = blockIdx.x;
+    if (ctl->prompt_pos != row_len[b] - 1) return;
+    for (int k = threadIdx.x; k < D; k += blockDim.x) xlast[(size_t)b * D + k] = x[(size_t)b * D + k];
+}
+cudaError_t launch_capture_last(const float* x, float* xlast, const int32_t* row_len, const StepCtl* ctl, int B, int D, cudaStream_t st) {
+    capture_last_kernel<<<B, 256, 0, st>>>(x, xlast, row_len, ctl, D);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_gate_mul(const float* gu, int ld, float* out32, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int mlp,

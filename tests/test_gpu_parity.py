@@ -443,3 +443,93 @@ def test_slot_reuse_by_transplanting_a_prefilled_sequence():
     assert got[0] == [int(t) for t in refs[0]] and got[2] == [int(t) for t in refs[2]]
     assert got[1] == [int(t) for t in refs[1][:4]]
     assert new_tokens == [int(t) for t in ref_new]
+
+
+@pytest.mark.parametrize("wdt,B", [("f32", 1), ("bf16", 3), ("f32", 8)])
+def test_greedy_head_with_fused_argmax_matches_logits_path_and_oracle(wdt, B):
+    """Batch <= 8, greedy, no logits asked for: the argmax rides behind the lm_head GEMV (per-CTA partials, one
+    finishing kernel) and no logits are written.  Tokens, lengths and eos handling must equal the path that writes the
+    logits and samples from them, and the oracle's greedy tokens; lumi_decode_step without a logits buffer takes the
+    same path."""
+    cfg = synth.base_config(n_layers=2, vocab_size=8192)
+    tens = list(synth.iter_tensors(cfg, seed=17, weights_dtype=wdt, perturb_ones=0.05))
+    T, n_new = 7, 24
+    prompts = synth.random_prompts(B, T, cfg.vocab_size, seed=6)
+    model = lumi_b200.NmModel.from_tensors(cfg, tens)
+    sess = model.init_states(B)
+    toks_fused, lens_fused, _, st = sess.generate(prompts, n_new, ignore_eos=True)                    # fused head
+    sess.reset()
+    toks_plain, lens_plain, dump, _ = sess.generate(prompts, n_new, ignore_eos=True, dump_logits=True)  # logits + sample_kernel
+    assert np.array_equal(toks_fused, toks_plain) and np.array_equal(lens_fused, lens_plain)
+    om = cpu_oracle.OracleModel(cfg, tens)
+    for b in (0, B - 1):
+        ref_toks, ref_logits = om.init_states().generate(prompts[b], n_new, ignore_eos=True, dump_logits=True)
+        _compare_tokens(toks_fused[b], ref_toks, ref_logits, f"fused greedy head, sequence {b}")
+    # eos: stop where the plain path stops
+    eos = int(toks_plain[0, 5])
+    sess.reset()
+    a, la, _, _ = sess.generate(prompts, n_new, eos_id=eos)
+    sess.reset()
+    b_, lb, _, _ = sess.generate(prompts, n_new, eos_id=eos, dump_logits=True)
+    assert np.array_equal(la, lb)
+    for i in range(B):
+        assert np.array_equal(a[i, :la[i]], b_[i, :lb[i]])
+    # token by token through lumi_decode_step without a logits buffer
+    sess.reset()
+    sess.prefill(prompts[:, :-1], want_logits=False)
+    tok = prompts[:, -1].copy()
+    for i in range(6):
+        _, tok = sess.forward_step(tok, want_logits=False, step=i)
+        assert np.array_equal(tok, toks_plain[:, i]), i
+
+
+@pytest.mark.parametrize("case", ["mamba_f32", "hybrid_f32", "mamba_bf16_tc"])
+def test_ragged_prefill_equals_each_prompt_alone(case):
+    """Prompts of different lengths in one call: every sequence must end in the state, and give the last-position
+    logits, of a prefill of its own tokens alone — and decoding continues from there like the oracle."""
+    if case == "hybrid_f32":
+        cfg = synth.tiny_config(attention_interval=2, attn_rope_base=10000.0, attn_window_sizes=[5])
+        wdt, B = "f32", 4
+    elif case == "mamba_bf16_tc":
+        cfg = synth.base_config(n_layers=2, vocab_size=1000)
+        wdt, B = "bf16", 12                                  # batch > 8: tensor-core GEMMs with the folded norm
+    else:
+        cfg = synth.base_config(n_layers=2, vocab_size=1000)
+        wdt, B = "f32", 3
+    tens = list(synth.iter_tensors(cfg, seed=23, weights_dtype=wdt, perturb_ones=0.05))
+    g = np.random.default_rng(5)
+    T_max = 11
+    lengths = g.integers(1, T_max + 1, size=B).astype(np.int32)
+    lengths[0], lengths[-1] = T_max, 1
+    prompts = synth.random_prompts(B, T_max, cfg.vocab_size, seed=8)
+    padded = prompts.copy()
+    for b in range(B):
+        padded[b, lengths[b]:] = 0xFFFFFFF0                  # padding is never looked at, not even range-checked
+    model = lumi_b200.NmModel.from_tensors(cfg, tens)
+    sess = model.init_states(B, 64)
+    logits = sess.prefill_ragged(padded, lengths)
+    om = cpu_oracle.OracleModel(cfg, tens)
+    mamba_layers = [i for i in range(cfg.n_layers) if not cfg.is_attention_layer(i)]
+    tol = TOL_F32
+    nxt = np.zeros(B, dtype=np.uint32)
+    refs = []
+    for b in range(B):
+        st = om.init_states()
+        for t in prompts[b, :lengths[b]]:
+            ref = st.forward_step(int(t))
+        refs.append(st)
+        assert rel_err(logits[b], ref) < tol, (case, b, int(lengths[b]))
+        nxt[b] = cpu_oracle.argmax(ref)
+        for layer in mamba_layers:
+            h, xp, bp, cum = sess.read_state(b, layer)
+            rh, rpbx, rcum = st.read_state(layer)
+            assert np.abs(h - rh).max() <= 1e-4 * max(1.0, np.abs(rh).max()), (case, b, layer)
+            assert np.abs(xp[:, :, None] * bp[:, None, :] - rpbx).max() <= 1e-4 * max(1.0, np.abs(rpbx).max())
+            assert np.abs(cum - rcum).max() < 1e-4
+    # decoding continues for all sequences together (this also checks the attention positions of the hybrid case)
+    for i in range(4):
+        lg, out = sess.forward_step(nxt, step=i)
+        for b in range(B):
+            ref = refs[b].forward_step(int(nxt[b]))
+            assert rel_err(lg[b], ref) < tol, (case, "decode", i, b)
+            nxt[b] = cpu_oracle.argmax(ref)
