@@ -303,6 +303,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    // Launched with programmatic dependent launch (small batches), this CTA may have become resident and done all of the
+    // above — barrier set-up, TMEM allocation — while its predecessor (the state step) still ran; everything below reads
+    // what predecessors produced.  Without the launch attribute this is a no-op.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     bool timed_out = false;
     if (warp == 0) {
@@ -594,9 +598,18 @@ int32_t launch_persistent(const GemmArgs& a, int splits, cudaStream_t st) {
     const int ntiles = tiles_m * tiles_n;
     const int units = ntiles * splits;
     const int grid = units < sm_count_gemm() ? units : sm_count_gemm();
-    kern<<<grid, 192, T::SMEM, st>>>(mh, ml, mw, a.d, a.ldd, a.M, a.N, a.K, a.accumulate, tiles_m, ntiles, splits, a.tile_counters,
-                                     a.scratch, a.status_word, a.wait_limit_ns ? a.wait_limit_ns : kWaitLimitNs, a.debug_skip_unit, a.nf);
-    LUMI_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = T::SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = launch_pdl_on() ? 1 : 0;        // small tensor-core batches: the set-up overlaps the predecessor's tail
+    LUMI_CUDA(cudaLaunchKernelEx(&cfg, kern, mh, ml, mw, a.d, a.ldd, a.M, a.N, a.K, a.accumulate, tiles_m, ntiles, splits, a.tile_counters,
+                                 a.scratch, a.status_word, a.wait_limit_ns ? a.wait_limit_ns : kWaitLimitNs, a.debug_skip_unit, a.nf));
     return LUMI_OK;
 }
 

@@ -233,6 +233,7 @@ cudaError_t launch_logprob_rows(const float* logits, int rows, int V, const uint
 // Kernels of kernels.cu launched by the calling thread from now on carry (or not) the
 // programmatic-dependent-launch attribute.
 void set_launch_pdl(bool on);
+bool launch_pdl_on();
 
 cudaError_t launch_embed(const void* emb, int dtype, const uint32_t* tok_cur, float* x, int B, int D, int vocab,
                          StepCtl* ctl, cudaStream_t st, const int32_t* row_len = nullptr);
@@ -293,7 +294,7 @@ struct AttnArgs {
     const int32_t* row_len = nullptr;    // prompts of different lengths: rows whose prompt has ended are skipped (decode form only)
 };
 constexpr int kAttnPartSlices = 16;
-constexpr int kAttnPartUnits = 2048;       // (row, KV head) pairs up to which a context may be split over CTAs (sizes the partial-result buffer)
+constexpr int kAttnPartUnits = 296;        // (row, KV head) pairs below which a context is split over CTAs: two CTAs per SM (sizes the partial-result buffer)
 cudaError_t launch_attention_decode(const AttnArgs& a, cudaStream_t st);
 cudaError_t launch_kv_advance(int32_t* kv_pos, int b0, int nb, int by, cudaStream_t st);
 

@@ -1248,6 +1248,7 @@ __global__ void gate_mul_kernel(const float* gu, int ld, float* out32, __nv_bflo
 // ---- launchers -------------------------------------------------------------------------------------
 static thread_local bool g_pdl = false;
 void set_launch_pdl(bool on) { g_pdl = on; }
+bool launch_pdl_on() { return g_pdl; }
 
 // Launch with (optionally) the programmatic-stream-serialization attribute.
 template <typename... KArgs, typename... Args>

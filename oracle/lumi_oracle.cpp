@@ -18,6 +18,12 @@
 // (oracle/numpy_restatement.py) and, structurally, against the reference's own pins
 // (in_proj_out == 7360, layer placement, byte-level ids).
 //
+// PINNED BY REFERENCE-AUTHORED CODE (on a GPU, by the tests): mamba_step and attention_step (without the rotary
+// extension) — whole-block outputs over a window of tokens equal those of the reference's own CUDA forward kernels
+// (training/csrc/elementwise_ops.cu, cublas_ops.cu, ssm_scan.cu, built from where they lie) chained as the
+// reference's trainer chains them (training/src/native_trainer.rs:198-266 and :110-194).  Everything else in this
+// file — embedding, final norm + head, argmax, the sampler, the extensions, the loaders — stays unpinned.
+//
 // What each function follows (paths inside the reference project):
 //   rms_norm            inference/src/model.rs:100-106
 //   sigmoid / softplus  inference/src/model.rs:12-17, 830-832
