@@ -750,6 +750,12 @@ static int pdl_tc_max() {
     return v;
 }
 
+static int pdl_gemm_max() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("LUMI_PDL_GEMM"); v = e ? atoi(e) : 1024; }     // measured: +2 % at 64-128 rows, +1.2 % at 512, neutral at 2048
+    return v;
+}
+
 int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches,
                      std::vector<std::pair<int, cudaEvent_t>>* prof = nullptr, const int32_t* row_len = nullptr) {
     const Config& c = s->m->cfg;
@@ -759,6 +765,9 @@ int32_t enqueue_step(lumi_session* s, int B, bool with_head, int64_t* launches,
     // dependent launch overlaps each kernel's prologue (weight prefetch) with its predecessor; it is
     // used on the weight-streaming path, where launch gaps are the same order as the kernels
     struct PdlScope { PdlScope(bool on) { set_launch_pdl(on); } ~PdlScope() { set_launch_pdl(false); } } pdl_scope(s->opt_pdl && prof == nullptr && (!p.tc || (pdl_tc_max() > 0 && B <= pdl_tc_max())));
+    // the tensor-core GEMMs themselves: dependent launch up to LUMI_PDL_GEMM rows (their barrier / TMEM set-up then runs under the
+    // tail of the state step; unlike an early state step this takes nothing from a running GEMM)
+    struct PdlGemmScope { PdlGemmScope(bool on) { set_launch_pdl_gemm(on); } ~PdlGemmScope() { set_launch_pdl_gemm(false); } } pdl_gemm_scope(s->opt_pdl && prof == nullptr && p.tc && B <= pdl_gemm_max());
     p.st_hi = p.st_lo = s->stream;
     mark(p);
     LUMI_CUDA(launch_embed(s->m->embedding.p, s->m->embedding.dtype, s->tok_cur, s->x, B, c.d_model, c.vocab, s->ctl, s->stream, row_len));

@@ -607,7 +607,7 @@ int32_t launch_persistent(const GemmArgs& a, int splits, cudaStream_t st) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = launch_pdl_on() ? 1 : 0;        // small tensor-core batches: the set-up overlaps the predecessor's tail
+    cfg.numAttrs = launch_pdl_gemm_on() ? 1 : 0;   // the set-up overlaps the predecessor's tail
     LUMI_CUDA(cudaLaunchKernelEx(&cfg, kern, mh, ml, mw, a.d, a.ldd, a.M, a.N, a.K, a.accumulate, tiles_m, ntiles, splits, a.tile_counters,
                                  a.scratch, a.status_word, a.wait_limit_ns ? a.wait_limit_ns : kWaitLimitNs, a.debug_skip_unit, a.nf));
     return LUMI_OK;

@@ -234,6 +234,10 @@ cudaError_t launch_logprob_rows(const float* logits, int rows, int V, const uint
 // programmatic-dependent-launch attribute.
 void set_launch_pdl(bool on);
 bool launch_pdl_on();
+// The same for the tensor-core GEMM launches alone (their set-up may overlap the predecessor's tail at batch sizes where
+// an early start of the CUDA-core kernels does not pay).
+void set_launch_pdl_gemm(bool on);
+bool launch_pdl_gemm_on();
 
 cudaError_t launch_embed(const void* emb, int dtype, const uint32_t* tok_cur, float* x, int B, int D, int vocab,
                          StepCtl* ctl, cudaStream_t st, const int32_t* row_len = nullptr);

@@ -1249,6 +1249,9 @@ __global__ void gate_mul_kernel(const float* gu, int ld, float* out32, __nv_bflo
 static thread_local bool g_pdl = false;
 void set_launch_pdl(bool on) { g_pdl = on; }
 bool launch_pdl_on() { return g_pdl; }
+static thread_local bool g_pdl_gemm = false;
+void set_launch_pdl_gemm(bool on) { g_pdl_gemm = on; }
+bool launch_pdl_gemm_on() { return g_pdl_gemm; }
 
 // Launch with (optionally) the programmatic-stream-serialization attribute.
 template <typename... KArgs, typename... Args>
