@@ -27,11 +27,12 @@ __device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bflo
     lo = __float2bfloat16_rn(v - __bfloat162float(hi));
 }
 
-// Page layout: [page][K|V][kPageTokens][kv_dim]
+// Page layout: [page][K|V][kv_head][kPageTokens][head_dim] — the rows one CTA reads (one KV head) are contiguous inside a
+// page (64 tokens x head_dim), so its loads walk whole DRAM bursts instead of one quarter of every token row.
 template <typename KT>
-__device__ __forceinline__ KT* kv_ptr(KT* pool, const int32_t* pt, int slot, int sel, int kv_dim) {
+__device__ __forceinline__ KT* kv_ptr(KT* pool, const int32_t* pt, int slot, int sel, int kv_heads, int kvh, int hd) {
     const int page = pt[slot / kPageTokens];
-    return pool + (((size_t)page * 2 + sel) * kPageTokens + (slot % kPageTokens)) * kv_dim;
+    return pool + ((((size_t)page * 2 + sel) * kv_heads + kvh) * kPageTokens + (slot % kPageTokens)) * hd;
 }
 
 constexpr int kAttnTile = 256;            // cached tokens scored per pass: the shared-memory footprint does not depend on the context
@@ -111,8 +112,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
         KvIo<KT>::st(&vnew[2 * pr], vn[2 * pr]);
         KvIo<KT>::st(&vnew[2 * pr + 1], vn[2 * pr + 1]);
         if (split == 0) {                                // KvCache::append (model.rs:133-152)
-            KT* kd = kv_ptr(pool, pt, slot_new, 0, KV) + kvh * HD;
-            KT* vd = kv_ptr(pool, pt, slot_new, 1, KV) + kvh * HD;
+            KT* kd = kv_ptr(pool, pt, slot_new, 0, a.kv_heads, kvh, HD);
+            KT* vd = kv_ptr(pool, pt, slot_new, 1, a.kv_heads, kvh, HD);
             kd[2 * pr] = knew[2 * pr]; kd[2 * pr + 1] = knew[2 * pr + 1];
             vd[2 * pr] = vnew[2 * pr]; vd[2 * pr + 1] = vnew[2 * pr + 1];
         }
@@ -135,7 +136,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     auto load_row = [&](int t, int sel) -> uint4 {
         if (t == local_slot) return reinterpret_cast<const uint4*>(sel == 0 ? knew : vnew)[sub];
         const int page = pages_ok ? pages[t / kPageTokens] : pt[t / kPageTokens];
-        return *reinterpret_cast<const uint4*>(pool + (((size_t)page * 2 + sel) * kPageTokens + (t % kPageTokens)) * KV + kvh * HD + sub * EPL);
+        return *reinterpret_cast<const uint4*>(pool + ((((size_t)page * 2 + sel) * a.kv_heads + kvh) * kPageTokens + (t % kPageTokens)) * HD + sub * EPL);
     };
     auto unpack = [](const uint4& raw, float (&f)[EPL]) {
         if constexpr (sizeof(KT) == 4) {

@@ -165,7 +165,7 @@ struct lumi_session {
     uint32_t b1_epoch = 1;
     // state, per Mamba layer l: base + l * max_batch * per-sequence size
     float *h = nullptr, *xprev = nullptr, *bprev = nullptr, *cum = nullptr;
-    // attention cache: pool of pages of kPageTokens tokens, [n_attn][pages][2][kPageTokens][kv_dim] bf16
+    // attention cache: pool of pages of kPageTokens tokens, [n_attn][pages][2][kv_heads][kPageTokens][head_dim]
     void* kv_pool = nullptr;           // element type follows the weights (fp32 or bf16)
     size_t kv_layer_bytes = 0;
     int32_t* page_table = nullptr;     // [max_batch][pages_per_seq]
