@@ -27,6 +27,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;                       // 64 bf16 = 128 bytes = one swizzle atom row
 constexpr int kSmemBudget = 196608;          // bytes of pipeline stages
+constexpr int kMaxSplits = 4;                // K split over at most this many CTAs
 constexpr uint64_t kWaitLimitNs = 500ull * 1000 * 1000;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -415,7 +416,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
                     tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + as * ACC_COLS + (uint32_t)(cb * 32), r);
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        if (cb * 32 + 4 * j < BN)
+                        if (cb * 32 + 4 * j < BN && m0 + row_l < M)
                             *reinterpret_cast<float4*>(part + cb * 32 + 4 * j) = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
                                                                                            __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
                 }
@@ -436,22 +437,75 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
                     const int row = m0 + row_l;
                     const int nlim = min(N, n0 + BN);
                     if (row < M) {
-                        for (int c4 = 0; c4 < BN; c4 += 4) {
-                            const int col = n0 + c4;
+                        // 16 columns at a time: the residual and every split's partial are requested together, added in
+                        // split order, and only then stored (a load behind a store would wait out an L2 round trip)
+                        float ssq = 0.f;
+                        for (int c16 = 0; c16 < BN; c16 += 16) {
+                            const int col = n0 + c16;
                             if (col >= nlim) break;
                             float* dp = D + (size_t)row * ldd + col;
-                            float v[4] = {0.f, 0.f, 0.f, 0.f};
-                            const bool vec = (ldd & 3) == 0 && col + 4 <= nlim;
-                            if (acc_in) {
-                                if (vec) { const float4 o = __ldcg(reinterpret_cast<const float4*>(dp)); v[0] = o.x; v[1] = o.y; v[2] = o.z; v[3] = o.w; }
-                                else for (int e = 0; e < 4; ++e) if (col + e < nlim) v[e] = __ldcg(dp + e);
+                            const bool vec = (ldd & 3) == 0 && col + 16 <= nlim;
+                            float v[16];
+                            if (vec) {
+                                float4 o[4], pv[kMaxSplits][4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) o[j] = acc_in ? __ldcg(reinterpret_cast<const float4*>(dp + 4 * j)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                                for (int s2 = 0; s2 < kMaxSplits; ++s2)
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j)
+                                        pv[s2][j] = s2 < splits ? __ldcg(reinterpret_cast<const float4*>(scratch + ((size_t)(s2 * ntiles + t) * BM + row_l) * BN + c16 + 4 * j))
+                                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    float4 sum = pv[0][j];
+#pragma unroll
+                                    for (int s2 = 1; s2 < kMaxSplits; ++s2)
+                                        if (s2 < splits) { sum.x += pv[s2][j].x; sum.y += pv[s2][j].y; sum.z += pv[s2][j].z; sum.w += pv[s2][j].w; }
+                                    v[4 * j] = fmaf(sum.x, rs, o[j].x); v[4 * j + 1] = fmaf(sum.y, rs, o[j].y);
+                                    v[4 * j + 2] = fmaf(sum.z, rs, o[j].z); v[4 * j + 3] = fmaf(sum.w, rs, o[j].w);
+                                }
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) *reinterpret_cast<float4*>(dp + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                            } else {
+                                for (int e = 0; e < 16; ++e) {
+                                    v[e] = 0.f;
+                                    if (col + e < nlim) {
+                                        float sum = 0.f;
+                                        for (int s2 = 0; s2 < splits; ++s2) sum += __ldcg(scratch + ((size_t)(s2 * ntiles + t) * BM + row_l) * BN + c16 + e);
+                                        v[e] = fmaf(sum, rs, acc_in ? __ldcg(dp + e) : 0.f);
+                                        dp[e] = v[e];
+                                    }
+                                }
                             }
-                            for (int s2 = 0; s2 < splits; ++s2) {
-                                const float4 pv = __ldcg(reinterpret_cast<const float4*>(scratch + ((size_t)(s2 * ntiles + t) * BM + row_l) * BN + c4));
-                                v[0] += pv.x; v[1] += pv.y; v[2] += pv.z; v[3] += pv.w;
+                            if (nf.out_hi != nullptr) {
+                                // the folded norm's producer side, as in the unsplit epilogue: x * gamma as bf16 hi + lo, x^2 per 32-column strip
+                                // N is a multiple of 8 here and tiles start on multiples of 32: groups of 8 columns are whole
+#pragma unroll
+                                for (int g8 = 0; g8 < 16; g8 += 8) {
+                                    if (col + g8 < nlim) {
+                                        const float4 ga = __ldg(reinterpret_cast<const float4*>(nf.gamma_next + col + g8));
+                                        const float4 gb = __ldg(reinterpret_cast<const float4*>(nf.gamma_next + col + g8 + 4));
+                                        const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+                                        uint32_t hw[4], lw[4];
+#pragma unroll
+                                        for (int e = 0; e < 8; e += 2) {
+                                            const float x0 = v[g8 + e], x1 = v[g8 + e + 1];
+                                            ssq = fmaf(x0, x0, fmaf(x1, x1, ssq));
+                                            const float w0 = x0 * gg[e], w1 = x1 * gg[e + 1];
+                                            const __nv_bfloat162 h01 = __floats2bfloat162_rn(w0, w1);
+                                            const float2 f01 = __bfloat1622float2(h01);
+                                            const __nv_bfloat162 l01 = __floats2bfloat162_rn(w0 - f01.x, w1 - f01.y);
+                                            hw[e >> 1] = *reinterpret_cast<const uint32_t*>(&h01);
+                                            lw[e >> 1] = *reinterpret_cast<const uint32_t*>(&l01);
+                                        }
+                                        const size_t oo = (size_t)row * N + col + g8;
+                                        *reinterpret_cast<uint4*>(nf.out_hi + oo) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                                        if (nf.out_lo != nullptr) *reinterpret_cast<uint4*>(nf.out_lo + oo) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+                                    }
+                                }
+                                if (((col + 16) & 31) == 0 || col + 16 >= nlim) { nf.ssq_out[(size_t)row * nf.ssq_stride + (col >> 5)] = ssq; ssq = 0.f; }
                             }
-                            if (vec) *reinterpret_cast<float4*>(dp) = make_float4(v[0], v[1], v[2], v[3]);
-                            else for (int e = 0; e < 4; ++e) if (col + e < nlim) dp[e] = v[e];
                         }
                     }
                 }
@@ -646,32 +700,45 @@ int32_t gemm_tcgen05_init() {
 // Tile width of the persistent kernel: the GPU works in rounds of one tile per SM, a round costs about its tile's
 // width, so take the width with the least rounds x width (7360 columns x 16 row tiles: 208 -> 4 rounds of 576 tiles,
 // against 4 rounds of 464 tiles at 256).  Ties go to the wider tile (less operand traffic per flop).
-// K can be split over CTAs as well (LUMI_GEMM_SPLITK=2, 4 or 8; at least four k-blocks per split) when the
-// tiles do not fill the SMs.  Off by default: measured slower at 64-512 rows, because the fix-up (the last
-// warp to arrive adds the parked partial tiles in split order) is a chain of L2 round trips in few warps.
+//
+// K is split over 2 or 4 CTAs as well where even the narrowest tiles leave most SMs idle and K is long (out_proj and the
+// FFN's second product at 64-128 rows: 32 tiles of 32 columns); the last warp to arrive at a tile adds the parked partial
+// tiles in split order.  The estimate behind the choice counts operand bytes per CTA (a k-block is the 128-row activation
+// tile, hi and lo, plus the weight rows) and charges the fix-up a round trip through L2 per 16 columns, which is what it
+// measures (about 1 us, as much as three k-blocks); a split is taken only where that comes out at least 1.3 times faster
+// (measured at 64 x 1024 x 2048: 19.1 us against 23.2 us, +12.6 % tokens per second on the 64-sequence decode; wide split
+// tiles lost more in the fix-up than they gained).
+// LUMI_GEMM_SPLITK=1 turns splitting off.
 static void pick_tile(const GemmArgs& a, int* width, int* splits) {
     static const int widths[] = {256, 224, 208, 192, 160, 128, 96, 64, 32};
-    static const int env_splits = getenv("LUMI_GEMM_SPLITK") ? atoi(getenv("LUMI_GEMM_SPLITK")) : 1;
-    const bool fused = a.nf.ssq_in != nullptr || a.nf.out_hi != nullptr;       // the folded RMSNorm lives in the unsplit epilogue
-    const int max_splits = fused ? 1 : env_splits;
+    static const int env_splits = getenv("LUMI_GEMM_SPLITK") ? atoi(getenv("LUMI_GEMM_SPLITK")) : kMaxSplits;
+    const int max_splits = env_splits < 1 ? 1 : (env_splits > kMaxSplits ? kMaxSplits : env_splits);
     const long tiles_m = (a.M + BM - 1) / BM;
     const int num_kb = a.K / BK;
-    int best = 256, best_splits = 1;
-    long best_cost = -1;
+    const long sms = sm_count_gemm();
+    int best = 256;
+    long best_cost = -1, best_rounds = 1;
     for (int w : widths) {
         if (a.nf.out_hi != nullptr && (w % 32) != 0) continue;       // the folded norm's partial sums are per 32 aligned columns
         const long tiles = tiles_m * ((a.N + w - 1) / w);
-        for (int sp = 1; sp <= max_splits; sp *= 2) {
-            if (sp > 1 && (a.tile_counters == nullptr || a.scratch == nullptr || 4 * tiles > a.n_counters ||
-                           (size_t)sp * tiles * BM * w > a.scratch_floats || num_kb / sp < 4))
-                break;
-            const long rounds = (tiles * sp + sm_count_gemm() - 1) / sm_count_gemm();
-            const long cost = rounds * (w / sp + 32 + (sp > 1 ? 12 : 0));    // + 32: the part of a tile's time that does not shrink
-            if (best_cost < 0 || cost < best_cost) { best = w; best_splits = sp; best_cost = cost; }
-        }
+        const long rounds = (tiles + sms - 1) / sms;
+        const long cost = rounds * (w + 32);                         // + 32: the part of a tile's time that does not shrink
+        if (best_cost < 0 || cost < best_cost) { best = w; best_cost = cost; best_rounds = rounds; }
     }
     *width = best;
-    *splits = best_splits;
+    *splits = 1;
+    if (max_splits < 2 || tiles_m > 1 || a.tile_counters == nullptr || a.scratch == nullptr) return;   // one row tile only: 256 rows measured 3 % slower split
+    const long a_kb = a.a_lo != nullptr ? 32 : 16;                   // KiB of activations per k-block of a 128-row tile
+    const long unsplit = best_rounds * num_kb * (a_kb + best / 8);   // KiB through one CTA
+    long best_split = -1;
+    for (int w : {64, 32}) {
+        const long tiles = tiles_m * ((a.N + w - 1) / w);
+        for (int sp = 2; sp <= max_splits; sp *= 2) {
+            if (tiles * sp > sms || num_kb / sp < 8 || 4 * tiles > a.n_counters || (size_t)sp * tiles * BM * w > a.scratch_floats) break;
+            const long est = (num_kb + sp - 1) / sp * (a_kb + w / 8) + 110 * (w / 16) + 110;
+            if (13 * est <= 10 * unsplit && (best_split < 0 || est < best_split)) { best_split = est; *width = w; *splits = sp; }
+        }
+    }
 }
 
 int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st) {

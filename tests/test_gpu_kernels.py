@@ -73,6 +73,12 @@ def test_tcgen05_gemm_matches_torch(split, M, N, K):
         err = (d.cpu().double() - want).abs().max().item() / want.abs().max().item()
         # tensor-core fp32 accumulation is not round-to-nearest at every add: allow 2e-5 of the largest output
         assert err < 2e-5, (M, N, K, split, acc, err)
+        # the same call again gives the same bits (K split over CTAs adds its partial tiles in a fixed order)
+        d2 = prev.clone().cuda()
+        lumi_b200.api.check(lumi_b200.lib().lumi_k_gemm_bf16_tcgen05(hid.data_ptr(), lod.data_ptr() if split else 0, wd.data_ptr(),
+                                                                 d2.data_ptr(), M, N, K, N, acc, 0))
+        torch.cuda.synchronize()
+        assert torch.equal(d, d2)
 
 
 def test_tcgen05_gemm_rejects_bad_k():
@@ -84,8 +90,10 @@ def test_tcgen05_gemm_rejects_bad_k():
     assert st == -10
 
 
-def test_tcgen05_gemm_k_split_variant_in_child_process():
-    """LUMI_GEMM_SPLITK is latched at first use: run the few-tile shapes with K split 8 ways in a child process."""
+def test_tcgen05_gemm_without_k_split_in_child_process():
+    """K is split over CTAs by default where the tiles alone leave SMs idle (the few-tile shapes of the test above).
+    LUMI_GEMM_SPLITK=1 turns that off and is latched at first use: run those shapes unsplit in a child process, and
+    check run-to-run bit stability there too."""
     import os, subprocess, sys
     code = (
         "import torch, lumi_b200\n"
@@ -104,6 +112,6 @@ def test_tcgen05_gemm_k_split_variant_in_child_process():
         "    assert err < 2e-5, (M, N, K, err)\n"
         "    assert torch.equal(outs[0], outs[1])\n"
         "print('ok')\n")
-    env = dict(os.environ, LUMI_GEMM_SPLITK="8", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    env = dict(os.environ, LUMI_GEMM_SPLITK="1", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-2000:]
