@@ -35,11 +35,39 @@ __device__ __forceinline__ KT* kv_ptr(KT* pool, const int32_t* pt, int slot, int
     return pool + ((((size_t)page * 2 + sel) * kv_heads + kvh) * kPageTokens + (slot % kPageTokens)) * hd;
 }
 
-constexpr int kAttnTile = 256;            // cached tokens scored per pass: the shared-memory footprint does not depend on the context
+constexpr int kAttnTile = kPageTokens;    // cached tokens scored per pass = one page: the shared-memory footprint does not depend on the context
+constexpr int kAttnSliceMin = 256;        // a slice of the context is worth a CTA from this many tokens on
 constexpr int kAttnMaxSplits = 16;
+constexpr uint64_t kAttnWaitNs = 500000000ull;   // limit of the wait for one staged page
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t timer_ns() { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+// false if the phase did not complete within the limit
+__device__ __forceinline__ bool page_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_addr(bar);
+    uint32_t done = 0, polls = 0;
+    uint64_t t0 = 0;
+    while (true) {
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((++polls & 255u) == 0u) {                   // the clock is read rarely: it is slow to read
+            const uint64_t now = timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kAttnWaitNs) return false;
+        }
+    }
+}
 
 // Work is split three ways: token row (x), KV head (y) and, when rows x KV heads would not fill the GPU, a
-// contiguous slice of the cached tokens (z).  Every CTA walks its slice in tiles of kAttnTile tokens with a running
+// contiguous slice of the cached tokens (z).  A KV head's 64 rows of a page are one contiguous block, so thread 0
+// brings the K and the V block of each page into a ring of shared-memory stages with one bulk copy each (an mbarrier
+// per stage counts the bytes; every wait on it is bounded and reports STATUS_TIMEOUT) while the CTA works on the
+// pages that have landed: the copies of the next NST - 1 pages are always in flight.  Every CTA walks its slice in tiles of kAttnTile tokens with a running
 // maximum / sum / context (the usual rescaling when the maximum grows), so the softmax of inference/src/model.rs:535
 // is evaluated without ever holding more than one tile of scores.  With one slice the CTA normalises and writes the
 // context itself.  With several, each parks (max, sum, unnormalised context) per query head in `part`, and the CTA
@@ -48,15 +76,18 @@ constexpr int kAttnMaxSplits = 16;
 // The new token's K / V row is appended to the cache by slice 0; every slice reads that row from its own
 // shared-memory copy (rounded through the cache's element type, i.e. the value the cache will hold) instead of from
 // the cache, so no CTA depends on another CTA's store.
-template <typename KT, int HD, int HPK>
+template <typename KT, int HD, int HPK, int NST>
 __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) {
     __shared__ float qs[HD * HPK];                       // rotated q, head-interleaved [HD][HPK]
     __shared__ float red[4 * HPK * HD];                  // cross-warp reductions
     __shared__ float sc[HPK * kAttnTile];                // scores / weights of the current tile
     __shared__ __align__(16) KT knew[HD], vnew[HD];      // the new token's rows as the cache will hold them
-    __shared__ float hmax[HPK], hsum[HPK];
-    __shared__ int32_t pages[64];
+    __shared__ float hsum[HPK];
+    __shared__ __align__(8) uint64_t full[NST];          // one per stage: the K and the V block of a page have landed
+    __shared__ int32_t pages[64];                        // this sequence's page table (when it fits), so that later requests need no global load
     __shared__ int is_last;
+    extern __shared__ __align__(128) unsigned char stage_mem[];      // NST x (K block, V block) of one page of this KV head
+    constexpr int BLOCK_ELEMS = kPageTokens * HD;        // elements of one K (or V) block
 
     const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
     const int b = a.b0 + r / a.rows_per_seq;             // sequence slot
@@ -78,6 +109,27 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     if (pos < 0 || slot_new >= cap || T > cap) {      // position outside the cache (full, or a corrupt position): report, write nothing
         if (tid == 0) atomicOr(&a.ctl->status, STATUS_KV_FULL);
         return;
+    }
+
+    // this CTA's slice of the cached tokens, in whole pages; its first pages are requested before anything else is done
+    const int per = ((T + nsplit - 1) / nsplit + kPageTokens - 1) / kPageTokens * kPageTokens;
+    const int tb = split * per, te = min(T, tb + per);
+    const int ntiles = a.phase == 1 || te <= tb ? 0 : (te - tb + kPageTokens - 1) / kPageTokens;
+    const bool pages_ok = a.pages_per_seq <= 64;
+    auto issue = [&](int i, bool staged) {               // thread 0: page i of the slice into stage i % NST
+        const int t00 = tb + i * kPageTokens;
+        const uint32_t bytes = (uint32_t)min(kPageTokens, te - t00) * HD * (uint32_t)sizeof(KT);
+        const int page = staged ? pages[t00 / kPageTokens] : pt[t00 / kPageTokens];
+        const size_t blk = ((size_t)page * 2 * a.kv_heads + kvh) * BLOCK_ELEMS;
+        KT* dst = reinterpret_cast<KT*>(stage_mem) + (size_t)(i % NST) * 2 * BLOCK_ELEMS;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(&full[i % NST])), "r"(2u * bytes) : "memory");
+        bulk_g2s(dst, pool + blk, bytes, &full[i % NST]);
+        bulk_g2s(dst + BLOCK_ELEMS, pool + blk + (size_t)a.kv_heads * BLOCK_ELEMS, bytes, &full[i % NST]);
+    };
+    if (tid == 0) {
+        for (int j = 0; j < NST; ++j) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&full[j])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int i = 0; i < NST && i < ntiles; ++i) issue(i, false);
     }
 
     // rotary embedding on interleaved pairs at the absolute position (extension), then stage q and the new K / V row
@@ -120,7 +172,6 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     }
     if (a.phase == 1) return;                            // append only
     const int local_slot = a.phase == 2 ? -1 : slot_new; // attend only: every row is already in the cache
-    const bool pages_ok = a.pages_per_seq <= 64;
     if (pages_ok) for (int i = tid; i < a.pages_per_seq; i += 128) pages[i] = pt[i];
     __syncthreads();
 
@@ -133,11 +184,6 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     constexpr int UNR = 4;
     static_assert(LPR >= 1 && LPR <= 32 && (32 % LPR) == 0, "a row must be 16 to 512 bytes");
     const int rg = lane / LPR, sub = lane % LPR;
-    auto load_row = [&](int t, int sel) -> uint4 {
-        if (t == local_slot) return reinterpret_cast<const uint4*>(sel == 0 ? knew : vnew)[sub];
-        const int page = pages_ok ? pages[t / kPageTokens] : pt[t / kPageTokens];
-        return *reinterpret_cast<const uint4*>(pool + ((((size_t)page * 2 + sel) * a.kv_heads + kvh) * kPageTokens + (t % kPageTokens)) * HD + sub * EPL);
-    };
     auto unpack = [](const uint4& raw, float (&f)[EPL]) {
         if constexpr (sizeof(KT) == 4) {
             f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
@@ -154,9 +200,6 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
         for (int e = 0; e < EPL; ++e) qr[hq][e] = qs[(sub * EPL + e) * HPK + hq];
     const float scale = (float)(1.0 / sqrt((double)HD));            // model.rs:530
 
-    // this CTA's slice of the cached tokens
-    const int per = (T + nsplit - 1) / nsplit;
-    const int tb = split * per, te = min(T, tb + per);
     float m_run[HPK], lsum[HPK], ctx[HPK][EPL];        // running maximum (uniform), this thread's share of the sum and the context
 #pragma unroll
     for (int hq = 0; hq < HPK; ++hq) {
@@ -164,8 +207,23 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
 #pragma unroll
         for (int e = 0; e < EPL; ++e) ctx[hq][e] = 0.f;
     }
-    for (int t00 = tb; t00 < te; t00 += kAttnTile) {
+    bool dead = false;                                   // a staged page did not arrive in time
+    int dead_it = 0;
+    for (int it = 0; it < ntiles; ++it) {
+        const int t00 = tb + it * kAttnTile;
         const int tn = min(kAttnTile, te - t00);        // tokens of this tile
+        const KT* kst = reinterpret_cast<const KT*>(stage_mem) + (size_t)(it % NST) * 2 * BLOCK_ELEMS;
+        const KT* vst = kst + BLOCK_ELEMS;
+        bool ok = page_wait(&full[it % NST], (uint32_t)(it / NST) & 1u);
+        if (ok && local_slot >= t00 && local_slot < t00 + tn && tid < 2 * LPR) {
+            // the new token's row: the value the cache will hold, from this CTA's own copy (slice 0 is still storing it)
+            KT* row = const_cast<KT*>(tid < LPR ? kst : vst) + (size_t)(local_slot - t00) * HD;
+            reinterpret_cast<uint4*>(row)[tid % LPR] = reinterpret_cast<const uint4*>(tid < LPR ? knew : vnew)[tid % LPR];
+        }
+        if (__syncthreads_or(!ok)) { dead = true; dead_it = it; break; }
+        auto load_row = [&](int t, int sel) -> uint4 {   // row t of the staged page
+            return *reinterpret_cast<const uint4*>((sel == 0 ? kst : vst) + (size_t)t * HD + sub * EPL);
+        };
         float lmax[HPK];
 #pragma unroll
         for (int hq = 0; hq < HPK; ++hq) lmax[hq] = -INFINITY;
@@ -174,7 +232,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
                 const int t = t0 + u * 4 * RPI + rg;
-                raw[u] = t < tn ? load_row(t00 + t, 0) : make_uint4(0u, 0u, 0u, 0u);
+                raw[u] = t < tn ? load_row(t, 0) : make_uint4(0u, 0u, 0u, 0u);
             }
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
@@ -208,13 +266,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
             if (lane == 0) red[warp * HPK + hq] = v;
         }
         __syncthreads();
-        if (tid < HPK) {
-            hmax[tid] = fmaxf(fmaxf(red[tid], red[HPK + tid]), fmaxf(red[2 * HPK + tid], red[3 * HPK + tid]));
-        }
-        __syncthreads();
 #pragma unroll
         for (int hq = 0; hq < HPK; ++hq) {
-            const float mn = fmaxf(m_run[hq], hmax[hq]);
+            const float hmax = fmaxf(fmaxf(red[hq], red[HPK + hq]), fmaxf(red[2 * HPK + hq], red[3 * HPK + hq]));
+            const float mn = fmaxf(m_run[hq], hmax);
             const float f = m_run[hq] == -INFINITY ? 0.f : expf(__fsub_rn(m_run[hq], mn));
             m_run[hq] = mn;
             lsum[hq] *= f;
@@ -236,7 +291,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
                 const int t = t0 + u * 4 * RPI + rg;
-                raw[u] = t < tn ? load_row(t00 + t, 1) : make_uint4(0u, 0u, 0u, 0u);
+                raw[u] = t < tn ? load_row(t, 1) : make_uint4(0u, 0u, 0u, 0u);
             }
 #pragma unroll
             for (int u = 0; u < UNR; ++u) {
@@ -253,7 +308,17 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
                 }
             }
         }
-        __syncthreads();                                 // sc and red are reused by the next tile
+        __syncthreads();                                 // sc, red and this stage are reused from here on
+        if (tid == 0 && it + NST < ntiles) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the CTA's reads of the stage come before the copy's writes
+            issue(it + NST, pages_ok);
+        }
+    }
+    if (dead && tid == 0) {
+        // report, and let the copies that are still on their way land (again with a limit) before the shared memory goes away;
+        // the CTA then finishes as usual, so that the slice counters stay consistent
+        atomicOr(&a.ctl->status, STATUS_TIMEOUT);
+        for (int j = dead_it; j < ntiles && j < dead_it + NST; ++j) page_wait(&full[j % NST], (uint32_t)(j / NST) & 1u);
     }
     // block totals: the sums by a xor tree and the four warps in order; the context likewise
 #pragma unroll
@@ -346,13 +411,22 @@ cudaError_t launch_t(const AttnArgs& a, cudaStream_t st) {
         // decode step of the hybrid model: the partial results and their merge cost more than the extra overlap brings)
         const long units = (long)a.B * a.kv_heads;
         nsplit = (int)((2L * attn_sm_count() + units - 1) / units);
-        const int by_len = (a.max_ctx_hint + kAttnTile - 1) / kAttnTile;
+        const int by_len = (a.max_ctx_hint + kAttnSliceMin - 1) / kAttnSliceMin;
         if (nsplit > by_len) nsplit = by_len;
         if (nsplit > kAttnMaxSplits) nsplit = kAttnMaxSplits;
         if (nsplit < 1) nsplit = 1;
     }
     dim3 grid(a.B, a.kv_heads, nsplit);
-    attn_decode_kernel<KT, HD, HPK><<<grid, 128, 0, st>>>(a, reinterpret_cast<KT*>(a.pool));
+    // stages of one page (K block + V block of this KV head): three of 16 KiB leave room for four CTAs per SM
+    constexpr int STAGE_BYTES = 2 * kPageTokens * HD * (int)sizeof(KT);
+    constexpr int NST = STAGE_BYTES <= 16384 ? 3 : 2;
+    static bool attr_set = false;                        // per instantiation
+    if (!attr_set) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<KT, HD, HPK, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, NST * STAGE_BYTES);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    attn_decode_kernel<KT, HD, HPK, NST><<<grid, 128, NST * STAGE_BYTES, st>>>(a, reinterpret_cast<KT*>(a.pool));
     return cudaGetLastError();
 }
 
