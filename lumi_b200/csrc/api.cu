@@ -707,6 +707,7 @@ int32_t attention_block(StepPlan& p, const Layer& L) {
     AttnArgs a{};
     a.qkv = s->proj; a.ldq = Q;
     a.pool = (char*)s->kv_pool + (size_t)L.kind_idx * s->kv_layer_bytes;
+    a.pool_bytes = s->kv_layer_bytes;
     a.kv_is_f32 = s->m->wdtype == LUMI_DTYPE_BF16 ? 0 : 1;
     a.page_table = s->page_table; a.pages_per_seq = s->pages_per_seq;
     a.pos = s->kv_pos;
@@ -1052,6 +1053,7 @@ int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head, float
                     AttnArgs a{};
                     a.qkv = s->pf_proj; a.ldq = Q;
                     a.pool = (char*)s->kv_pool + l * s->kv_layer_bytes;
+                    a.pool_bytes = s->kv_layer_bytes;
                     a.kv_is_f32 = 0;
                     a.page_table = s->page_table; a.pages_per_seq = s->pages_per_seq;
                     a.pos = s->kv_pos;

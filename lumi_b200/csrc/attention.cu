@@ -6,9 +6,13 @@
 // token t lives in slot t % window.  Optional rotary embedding (extension, off by default).
 #include "internal.h"
 
+#include <cuda.h>
+
 #include <cmath>
 
 namespace lumi {
+
+int32_t make_bf16_map_rows64(CUtensorMap* map, const void* ptr, uint64_t rows, uint32_t box_rows);     // gemm_tcgen05.cu
 
 namespace {
 
@@ -392,6 +396,339 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     }
 }
 
+// ---- bf16 cache, head_dim 64: the same walk on the tensor cores ---------------------------------------------
+// D (16x8, fp32) += A (16x16, bf16, row) * B (16x8, bf16, col)
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// two fp32 values -> bf16x2 hi word and bf16x2 lo word (first value in the low half)
+__device__ __forceinline__ void split_pair(float v0, float v1, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+    const float2 hf = __bfloat1622float2(h);
+    const __nv_bfloat162 l = __floats2bfloat162_rn(v0 - hf.x, v1 - hf.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+// byte offset of the 16-byte chunk `chunk` of row `row` in a tile of 128-byte rows stored with the 128-byte swizzle
+__device__ __forceinline__ uint32_t swz128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+constexpr int kMmaStages = 3;
+constexpr int kMmaStageBytes = 2 * kPageTokens * 128;      // K block + V block of one page of one KV head (head_dim 64, bf16)
+constexpr float kMaskedScore = -1.0e30f;                   // finite, so that a fully masked row never produces inf - inf
+
+// One CTA = up to 16 / HPK consecutive token rows of one sequence (one in decode) x the HPK query heads of one KV head:
+// 16 "query columns" m = row * HPK + head, the M side of mma.m16n8k16.  Scores S = Q K^T with A = Q (bf16 hi + lo, so
+// that fp32 queries lose nothing that matters) and B = the staged K page as it lies ([token][dim] is the col-major B
+// operand); the softmax weights of a 16-token strip are already laid out as the A operand of P V (again hi + lo), with
+// B = the staged V page through ldmatrix.trans.  The pages arrive by one tensor-map copy each for K and V (128-byte
+// swizzle, so ldmatrix meets no bank conflict) into a ring of kMmaStages stages; waits are bounded.  The four warps take
+// 16 tokens each of a page and keep their own running maximum / sum / context; they are merged at the end in warp order.
+// Rows of a CTA differ in how many cached tokens they may see (row j of a prompt slice sees one token more than row
+// j - 1); scores beyond a row's limit are replaced by a large negative constant before the maximum is taken.
+template <int HPK>
+__global__ void __launch_bounds__(128) attn_mma_kernel(AttnArgs a, const __grid_constant__ CUtensorMap kvmap, int q_rows, int groups_per_seq) {
+    constexpr int HD = 64;
+    __shared__ __align__(16) __nv_bfloat16 knew[HD], vnew[HD];
+    __shared__ __align__(8) uint64_t full[kMmaStages];
+    __shared__ int32_t pages[64];
+    __shared__ int is_last;
+    extern __shared__ unsigned char dyn_raw[];
+    // the swizzle pattern repeats every 1024 bytes: stages start on that boundary
+    unsigned char* dyn = dyn_raw + ((1024u - (smem_addr(dyn_raw) & 1023u)) & 1023u);
+    unsigned char* qtile = dyn + kMmaStages * kMmaStageBytes;       // Q hi [16][64] then Q lo [16][64], swizzled like the pages
+
+    const int grp = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
+    const int ts = a.rows_per_seq;
+    const int sidx = grp / groups_per_seq, i0 = (grp % groups_per_seq) * q_rows;
+    const int nrow = min(q_rows, ts - i0);                // token rows of this CTA
+    const int r0 = sidx * ts + i0;                        // first of them in the projection / output arrays
+    const int b = a.b0 + sidx;
+    const int D = a.n_heads * HD, KV = a.kv_heads * HD;
+    if (a.row_len != nullptr) {                          // prompts of different lengths: this sequence's prompt has ended
+        const int pp = a.ctl->prompt_pos;
+        if (pp < a.ctl->prompt_len && pp >= a.row_len[b]) return;
+    }
+    const int pos0 = a.pos[b] + i0;
+    const int32_t* pt = a.page_table + (size_t)b * a.pages_per_seq;
+    const int cap = a.window > 0 ? min(a.window, a.max_tokens) : a.max_tokens;
+    // cached tokens the first row sees; row j sees j more (several rows only without a window: the host takes care of that)
+    int T0, slot_new;
+    if (a.window > 0 && a.window <= a.max_tokens) { slot_new = pos0 % a.window; T0 = min(pos0 + 1, a.window); }
+    else { slot_new = pos0; T0 = pos0 + 1; }
+    const int T = T0 + nrow - 1;                          // ... and the last row
+    if (pos0 < 0 || slot_new >= cap || T > cap) {
+        if (tid == 0) atomicOr(&a.ctl->status, STATUS_KV_FULL);
+        return;
+    }
+    const int per = ((T + nsplit - 1) / nsplit + kPageTokens - 1) / kPageTokens * kPageTokens;
+    const int tb = split * per, te = min(T, tb + per);
+    const int ntiles = te <= tb ? 0 : (te - tb + kPageTokens - 1) / kPageTokens;
+    const bool pages_ok = a.pages_per_seq <= 64;
+    auto issue = [&](int i, bool staged) {               // thread 0: page i of the slice into stage i % kMmaStages
+        const int t00 = tb + i * kPageTokens;
+        const int page = staged ? pages[t00 / kPageTokens] : pt[t00 / kPageTokens];
+        const int row = (page * 2 * a.kv_heads + kvh) * kPageTokens;          // first row of the K block in the layer's pool
+        unsigned char* dst = dyn + (i % kMmaStages) * kMmaStageBytes;
+        uint64_t* bar = &full[i % kMmaStages];
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"((uint32_t)kMmaStageBytes) : "memory");
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                     ::"r"(smem_addr(dst)), "l"(&kvmap), "r"(smem_addr(bar)), "r"(0), "r"(row) : "memory");
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                     ::"r"(smem_addr(dst + kMmaStageBytes / 2)), "l"(&kvmap), "r"(smem_addr(bar)), "r"(0), "r"(row + a.kv_heads * kPageTokens) : "memory");
+    };
+    if (tid == 0) {
+        for (int j = 0; j < kMmaStages; ++j) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&full[j])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int i = 0; i < kMmaStages && i < ntiles; ++i) issue(i, false);
+    }
+
+    // Q: rotary embedding at each row's own position (extension), then bf16 hi / lo into the swizzled 16 x 64 tiles;
+    // query columns beyond the CTA's rows are zero
+    for (int i = tid; i < 16 * HD / 2; i += 128) {
+        const int m = i / (HD / 2), pr = i % (HD / 2);
+        const int j = m / HPK, hq = m % HPK;
+        float q0 = 0.f, q1 = 0.f;
+        if (j < nrow) {
+            const float* q = a.qkv + (size_t)(r0 + j) * a.ldq + (size_t)(kvh * HPK + hq) * HD;
+            q0 = q[2 * pr]; q1 = q[2 * pr + 1];
+            if (a.rope_base > 0.f) {
+                float inv = powf(a.rope_base, -(float)(2 * pr) / (float)HD);
+                float ang = __fmul_rn((float)(pos0 + j), inv);
+                float sa, ca;
+                sincosf(ang, &sa, &ca);
+                float x0 = __fsub_rn(__fmul_rn(ca, q0), __fmul_rn(sa, q1));
+                float x1 = __fadd_rn(__fmul_rn(sa, q0), __fmul_rn(ca, q1));
+                q0 = x0; q1 = x1;
+            }
+        }
+        uint32_t hi, lo;
+        split_pair(q0, q1, hi, lo);
+        const uint32_t off = swz128(m, pr >> 2) + (uint32_t)(pr & 3) * 4u;
+        *reinterpret_cast<uint32_t*>(qtile + off) = hi;
+        *reinterpret_cast<uint32_t*>(qtile + 16 * 128 + off) = lo;
+    }
+    // decode (phase 0): the new token's K / V row as the cache will hold it; slice 0 appends it (KvCache::append, model.rs:133-152)
+    if (a.phase == 0) {
+        const float* kn = a.qkv + (size_t)r0 * a.ldq + D + kvh * HD;
+        const float* vn = kn + KV;
+        for (int pr = tid; pr < HD / 2; pr += 128) {
+            float k0 = kn[2 * pr], k1 = kn[2 * pr + 1];
+            if (a.rope_base > 0.f) {
+                float inv = powf(a.rope_base, -(float)(2 * pr) / (float)HD);
+                float ang = __fmul_rn((float)pos0, inv);
+                float sa, ca;
+                sincosf(ang, &sa, &ca);
+                float x0 = __fsub_rn(__fmul_rn(ca, k0), __fmul_rn(sa, k1));
+                float x1 = __fadd_rn(__fmul_rn(sa, k0), __fmul_rn(ca, k1));
+                k0 = x0; k1 = x1;
+            }
+            knew[2 * pr] = __float2bfloat16_rn(k0); knew[2 * pr + 1] = __float2bfloat16_rn(k1);
+            vnew[2 * pr] = __float2bfloat16_rn(vn[2 * pr]); vnew[2 * pr + 1] = __float2bfloat16_rn(vn[2 * pr + 1]);
+            if (split == 0) {
+                __nv_bfloat16* pool = reinterpret_cast<__nv_bfloat16*>(a.pool);
+                __nv_bfloat16* kd = kv_ptr(pool, pt, slot_new, 0, a.kv_heads, kvh, HD);
+                __nv_bfloat16* vd = kv_ptr(pool, pt, slot_new, 1, a.kv_heads, kvh, HD);
+                kd[2 * pr] = knew[2 * pr]; kd[2 * pr + 1] = knew[2 * pr + 1];
+                vd[2 * pr] = vnew[2 * pr]; vd[2 * pr + 1] = vnew[2 * pr + 1];
+            }
+        }
+    }
+    const int local_slot = a.phase == 0 ? slot_new : -1; // attend only (phase 2): every row is already in the cache
+    if (pages_ok) for (int i = tid; i < a.pages_per_seq; i += 128) pages[i] = pt[i];
+    __syncthreads();
+
+    // A fragments of Q for the four 16-dim steps: matrices (rows 0-7 | 8-15) x (dims +0..7 | +8..15)
+    uint32_t qh[4][4], ql[4][4];
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        const uint32_t off = swz128(lane & 15, 2 * ks + (lane >> 4));
+        ldsm4(qh[ks], smem_addr(qtile) + off);
+        ldsm4(ql[ks], smem_addr(qtile + 16 * 128) + off);
+    }
+    // per-row limits of the two query columns this thread sees in the accumulators (g and g + 8): 0 for unused columns
+    const int lim0 = (g / HPK) < nrow ? T0 + g / HPK : 0;
+    const int lim1 = ((g + 8) / HPK) < nrow ? T0 + (g + 8) / HPK : 0;
+    const float scale = 0.125f;                          // 1 / sqrt(64), model.rs:530
+
+    float m0 = kMaskedScore, m1 = kMaskedScore, l0 = 0.f, l1 = 0.f;    // running maximum and this thread's share of the sum, rows g and g + 8
+    float o[8][4];                                       // context: 8 tiles of 8 dims; [0..1] row g, [2..3] row g + 8
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) { o[nt][0] = 0.f; o[nt][1] = 0.f; o[nt][2] = 0.f; o[nt][3] = 0.f; }
+    bool dead = false;
+    int dead_it = 0;
+    for (int it = 0; it < ntiles; ++it) {
+        const int t00 = tb + it * kPageTokens;
+        const int tn = min(kPageTokens, te - t00);
+        unsigned char* kst = dyn + (it % kMmaStages) * kMmaStageBytes;
+        unsigned char* vst = kst + kMmaStageBytes / 2;
+        const bool ok = page_wait(&full[it % kMmaStages], (uint32_t)(it / kMmaStages) & 1u);
+        if (ok) {
+            if (local_slot >= t00 && local_slot < t00 + tn && tid < 16) {
+                // the new token's row from this CTA's own copy (slice 0 is still storing it)
+                const int row = local_slot - t00, c = tid & 7;
+                *reinterpret_cast<uint4*>((tid < 8 ? kst : vst) + swz128(row, c)) = reinterpret_cast<const uint4*>(tid < 8 ? knew : vnew)[c];
+            }
+            // rows of the page that hold no token yet: their weights are zero, and zero times whatever the memory holds must stay zero
+            for (int i = tid; i < (kPageTokens - tn) * 8; i += 128)
+                *reinterpret_cast<uint4*>(vst + (tn + i / 8) * 128 + (i & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (__syncthreads_or(!ok)) { dead = true; dead_it = it; break; }
+        const int tw = 16 * warp;                        // this warp's 16 tokens of the page
+        if (tw < tn) {
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};     // tokens tw .. tw + 7 and tw + 8 .. tw + 15
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                uint32_t kb[4];
+                const int tok = tw + ((lane >> 4) << 3) + (lane & 7);
+                ldsm4(kb, smem_addr(kst) + swz128(tok, 2 * ks + ((lane >> 3) & 1)));
+                mma16816(s0, qh[ks], kb[0], kb[1]);
+                mma16816(s1, qh[ks], kb[2], kb[3]);
+                mma16816(s0, ql[ks], kb[0], kb[1]);
+                mma16816(s1, ql[ks], kb[2], kb[3]);
+            }
+            // scale (model.rs:532), mask, running maximum per query column (a quad holds one row of a tile)
+            const int tc = t00 + tw + 2 * tq;            // token of element [0] of the first tile
+            s0[0] = tc < lim0 ? __fmul_rn(s0[0], scale) : kMaskedScore;
+            s0[1] = tc + 1 < lim0 ? __fmul_rn(s0[1], scale) : kMaskedScore;
+            s0[2] = tc < lim1 ? __fmul_rn(s0[2], scale) : kMaskedScore;
+            s0[3] = tc + 1 < lim1 ? __fmul_rn(s0[3], scale) : kMaskedScore;
+            s1[0] = tc + 8 < lim0 ? __fmul_rn(s1[0], scale) : kMaskedScore;
+            s1[1] = tc + 9 < lim0 ? __fmul_rn(s1[1], scale) : kMaskedScore;
+            s1[2] = tc + 8 < lim1 ? __fmul_rn(s1[2], scale) : kMaskedScore;
+            s1[3] = tc + 9 < lim1 ? __fmul_rn(s1[3], scale) : kMaskedScore;
+            float x0 = fmaxf(fmaxf(s0[0], s0[1]), fmaxf(s1[0], s1[1]));
+            float x1 = fmaxf(fmaxf(s0[2], s0[3]), fmaxf(s1[2], s1[3]));
+            x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, 1)); x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, 2));
+            x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, 1)); x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, 2));
+            const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
+            const float f0 = expf(__fsub_rn(m0, n0)), f1 = expf(__fsub_rn(m1, n1));
+            m0 = n0; m1 = n1;
+            float p0[4], p1[4];
+            p0[0] = tc < lim0 ? expf(__fsub_rn(s0[0], n0)) : 0.f;
+            p0[1] = tc + 1 < lim0 ? expf(__fsub_rn(s0[1], n0)) : 0.f;
+            p0[2] = tc < lim1 ? expf(__fsub_rn(s0[2], n1)) : 0.f;
+            p0[3] = tc + 1 < lim1 ? expf(__fsub_rn(s0[3], n1)) : 0.f;
+            p1[0] = tc + 8 < lim0 ? expf(__fsub_rn(s1[0], n0)) : 0.f;
+            p1[1] = tc + 9 < lim0 ? expf(__fsub_rn(s1[1], n0)) : 0.f;
+            p1[2] = tc + 8 < lim1 ? expf(__fsub_rn(s1[2], n1)) : 0.f;
+            p1[3] = tc + 9 < lim1 ? expf(__fsub_rn(s1[3], n1)) : 0.f;
+            l0 = fmaf(l0, f0, (p0[0] + p0[1]) + (p1[0] + p1[1]));
+            l1 = fmaf(l1, f1, (p0[2] + p0[3]) + (p1[2] + p1[3]));
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) { o[nt][0] *= f0; o[nt][1] *= f0; o[nt][2] *= f1; o[nt][3] *= f1; }
+            // the weights as the A operand of P V: (row g | g + 8) x (tokens 2tq.. | 8 + 2tq..)
+            uint32_t ph[4], pl[4];
+            split_pair(p0[0], p0[1], ph[0], pl[0]);
+            split_pair(p0[2], p0[3], ph[1], pl[1]);
+            split_pair(p1[0], p1[1], ph[2], pl[2]);
+            split_pair(p1[2], p1[3], ph[3], pl[3]);
+#pragma unroll
+            for (int dn = 0; dn < 4; ++dn) {             // 16 dims per step: tiles 2 dn and 2 dn + 1
+                uint32_t vb[4];
+                const int tok = tw + (((lane >> 3) & 1) << 3) + (lane & 7);
+                ldsm4t(vb, smem_addr(vst) + swz128(tok, 2 * dn + (lane >> 4)));
+                mma16816(o[2 * dn], ph, vb[0], vb[1]);
+                mma16816(o[2 * dn + 1], ph, vb[2], vb[3]);
+                mma16816(o[2 * dn], pl, vb[0], vb[1]);
+                mma16816(o[2 * dn + 1], pl, vb[2], vb[3]);
+            }
+        }
+        __syncthreads();                                 // this stage is free again
+        if (tid == 0 && it + kMmaStages < ntiles) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the CTA's accesses to the stage come before the copy's writes
+            issue(it + kMmaStages, pages_ok);
+        }
+    }
+    if (dead && tid == 0) {
+        // report, and let the copies still on their way land (again with a limit) before the shared memory goes away; the CTA
+        // then finishes as usual, so that the slice counters stay consistent
+        atomicOr(&a.ctl->status, STATUS_TIMEOUT);
+        for (int j = dead_it; j < ntiles && j < dead_it + kMmaStages; ++j) page_wait(&full[j % kMmaStages], (uint32_t)(j / kMmaStages) & 1u);
+    }
+    if (dead) __syncthreads();
+
+    // merge the four warps (the stages are free: every requested page has landed and been used)
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    constexpr int CW = HD + 2;                           // per query column: maximum, sum, context
+    float* comb = reinterpret_cast<float*>(dyn);         // [4 warps][16][CW]
+    {
+        float* mine = comb + (size_t)warp * 16 * CW;
+        if (tq == 0) { mine[g * CW] = m0; mine[g * CW + 1] = l0; mine[(g + 8) * CW] = m1; mine[(g + 8) * CW + 1] = l1; }
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            mine[g * CW + 2 + nt * 8 + 2 * tq] = o[nt][0]; mine[g * CW + 2 + nt * 8 + 2 * tq + 1] = o[nt][1];
+            mine[(g + 8) * CW + 2 + nt * 8 + 2 * tq] = o[nt][2]; mine[(g + 8) * CW + 2 + nt * 8 + 2 * tq + 1] = o[nt][3];
+        }
+    }
+    __syncthreads();
+    auto emit = [&](int m, int d, float v) {
+        const size_t oo = (size_t)(r0 + m / HPK) * D + (size_t)(kvh * HPK + m % HPK) * HD + d;
+        if (a.ctx32) a.ctx32[oo] = v;
+        if (a.chi) {
+            __nv_bfloat16 hh, ll;
+            split_bf16(v, hh, ll);
+            a.chi[oo] = hh;
+            if (a.clo) a.clo[oo] = ll;
+        }
+    };
+    constexpr int PW = HPK * (HD + 2);                   // floats per slice in `part`: [HPK] maxima, [HPK] sums, [HPK][HD] context
+    float* mine = nsplit > 1 ? a.part + ((size_t)(grp * a.kv_heads + kvh) * kAttnMaxSplits + split) * PW : nullptr;
+    for (int i = tid; i < nrow * HPK * HD; i += 128) {
+        const int m = i / HD, d = i % HD;
+        float mx = comb[m * CW];
+#pragma unroll
+        for (int w = 1; w < 4; ++w) mx = fmaxf(mx, comb[(w * 16 + m) * CW]);
+        float den = 0.f, num = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = expf(__fsub_rn(comb[(w * 16 + m) * CW], mx));
+            den = fmaf(f, comb[(w * 16 + m) * CW + 1], den);
+            num = fmaf(f, comb[(w * 16 + m) * CW + 2 + d], num);
+        }
+        if (nsplit == 1) emit(m, d, __fdiv_rn(num, den));
+        else {
+            mine[2 * HPK + i] = num;                     // one row per CTA here: m is the head
+            if (d == 0) { mine[m] = mx; mine[HPK + m] = den; }
+        }
+    }
+    if (nsplit == 1) return;
+    // several slices: the last arriver merges them in slice order (nobody waits for anybody)
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int old = atomicAdd(a.part_count + grp * a.kv_heads + kvh, 1);
+        is_last = old == nsplit - 1;
+        if (is_last) a.part_count[grp * a.kv_heads + kvh] = 0;           // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const float* all = a.part + (size_t)(grp * a.kv_heads + kvh) * kAttnMaxSplits * PW;
+    for (int i = tid; i < HPK * HD; i += 128) {
+        const int hq = i / HD;
+        float m = kMaskedScore;
+        for (int sp = 0; sp < nsplit; ++sp) m = fmaxf(m, __ldcg(all + (size_t)sp * PW + hq));
+        float den = 0.f, num = 0.f;
+        for (int sp = 0; sp < nsplit; ++sp) {
+            const float f = expf(__fsub_rn(__ldcg(all + (size_t)sp * PW + hq), m));
+            den = fmaf(f, __ldcg(all + (size_t)sp * PW + HPK + hq), den);
+            num = fmaf(f, __ldcg(all + (size_t)sp * PW + 2 * HPK + i), num);
+        }
+        emit(hq, i % HD, __fdiv_rn(num, den));
+    }
+}
+
+
 static int attn_sm_count() {
     static int n = 0;
     if (n == 0) {
@@ -401,21 +738,23 @@ static int attn_sm_count() {
     return n;
 }
 
+// number of context slices: enough CTAs to give every SM two, at least kAttnSliceMin tokens each, and only where the caller
+// gave room for the partial results (decode); the batched prefill has rows to spare
+static int pick_slices(const AttnArgs& a) {
+    if (a.part == nullptr || a.part_count == nullptr || a.phase != 0) return 1;
+    // two CTAs per SM; splitting further was measured slower at 128 sequences x 4 KV heads (3.56 against 3.39 ms per
+    // decode step of the hybrid model: the partial results and their merge cost more than the extra overlap brings)
+    const long units = (long)a.B * a.kv_heads;
+    int nsplit = (int)((2L * attn_sm_count() + units - 1) / units);
+    const int by_len = (a.max_ctx_hint + kAttnSliceMin - 1) / kAttnSliceMin;
+    if (nsplit > by_len) nsplit = by_len;
+    if (nsplit > kAttnMaxSplits) nsplit = kAttnMaxSplits;
+    return nsplit < 1 ? 1 : nsplit;
+}
+
 template <typename KT, int HD, int HPK>
 cudaError_t launch_t(const AttnArgs& a, cudaStream_t st) {
-    // slices of the context: enough CTAs (see below), at least one tile each, and only where the caller gave
-    // room for the partial results (decode); the batched prefill has rows to spare
-    int nsplit = 1;
-    if (a.part != nullptr && a.part_count != nullptr && a.phase == 0) {
-        // two CTAs per SM; splitting further was measured slower at 128 sequences x 4 KV heads (3.56 against 3.39 ms per
-        // decode step of the hybrid model: the partial results and their merge cost more than the extra overlap brings)
-        const long units = (long)a.B * a.kv_heads;
-        nsplit = (int)((2L * attn_sm_count() + units - 1) / units);
-        const int by_len = (a.max_ctx_hint + kAttnSliceMin - 1) / kAttnSliceMin;
-        if (nsplit > by_len) nsplit = by_len;
-        if (nsplit > kAttnMaxSplits) nsplit = kAttnMaxSplits;
-        if (nsplit < 1) nsplit = 1;
-    }
+    const int nsplit = pick_slices(a);
     dim3 grid(a.B, a.kv_heads, nsplit);
     // stages of one page (K block + V block of this KV head): three of 16 KiB leave room for four CTAs per SM
     constexpr int STAGE_BYTES = 2 * kPageTokens * HD * (int)sizeof(KT);
@@ -430,9 +769,38 @@ cudaError_t launch_t(const AttnArgs& a, cudaStream_t st) {
     return cudaGetLastError();
 }
 
+template <int HPK>
+cudaError_t launch_mma(const AttnArgs& a, cudaStream_t st) {
+    CUtensorMap map;
+    if (make_bf16_map_rows64(&map, a.pool, a.pool_bytes / 128, kPageTokens) != LUMI_OK) return cudaErrorUnknown;
+    const int ts = a.rows_per_seq;
+    const int q_rows = a.phase == 2 ? 16 / HPK : 1;
+    const int gps = (ts + q_rows - 1) / q_rows;
+    constexpr int kDyn = kMmaStages * kMmaStageBytes + 2 * 16 * 128 + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<HPK>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDyn);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    dim3 grid((a.B / ts) * gps, a.kv_heads, pick_slices(a));
+    attn_mma_kernel<HPK><<<grid, 128, kDyn, st>>>(a, map, q_rows, gps);
+    return cudaGetLastError();
+}
+
 template <typename KT>
 cudaError_t launch_kt(const AttnArgs& a, cudaStream_t st) {
     const int hpk = a.n_heads / a.kv_heads;
+    if constexpr (sizeof(KT) == 2) {
+        // bf16 cache with 64-wide heads: the tensor-core kernel (attend; the append-only pass of a prompt slice stays below)
+        if (a.head_dim == 64 && a.phase != 1 && a.pool_bytes > 0 && a.pool_bytes / 128 < (size_t)1 << 31 && (a.B % a.rows_per_seq) == 0 &&
+            (a.phase == 0 ? (a.rows_per_seq == 1) : (a.window == 0))) {
+            if (hpk == 1) return launch_mma<1>(a, st);
+            if (hpk == 2) return launch_mma<2>(a, st);
+            if (hpk == 4) return launch_mma<4>(a, st);
+            if (hpk == 8) return launch_mma<8>(a, st);
+        }
+    }
 #define LUMI_ATT(HD_, HPK_) if (a.head_dim == HD_ && hpk == HPK_) return launch_t<KT, HD_, HPK_>(a, st);
     LUMI_ATT(64, 4) LUMI_ATT(64, 1) LUMI_ATT(64, 2) LUMI_ATT(64, 8)
     LUMI_ATT(32, 1) LUMI_ATT(32, 2) LUMI_ATT(32, 4) LUMI_ATT(32, 8)

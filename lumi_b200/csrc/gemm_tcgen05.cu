@@ -686,6 +686,21 @@ int32_t make_f32_map_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64
     return LUMI_OK;
 }
 
+// bf16 matrix [rows][64] (128-byte rows, dense) as a 2-D tensor map with a box of box_rows whole rows and the 128-byte swizzle
+// (the 16-byte chunks of row r land XOR-ed with r % 8).  Used by the attention kernel to stage KV pages.
+int32_t make_bf16_map_rows64(CUtensorMap* map, const void* ptr, uint64_t rows, uint32_t box_rows) {
+    LUMI_TRY(gemm_tcgen05_init());
+    cuuint64_t dims[2] = {64, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {128};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LUMI_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (bf16 rows %llu)", (int)r, (unsigned long long)rows);
+    return LUMI_OK;
+}
+
 int32_t gemm_tcgen05_init() {
     if (g_encode != nullptr) return LUMI_OK;
     void* fn = nullptr;

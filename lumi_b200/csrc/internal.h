@@ -296,6 +296,7 @@ struct AttnArgs {
     int32_t* part_count = nullptr;
     int max_ctx_hint = 0;
     const int32_t* row_len = nullptr;    // prompts of different lengths: rows whose prompt has ended are skipped (decode form only)
+    size_t pool_bytes = 0;               // size of this layer's page pool (bounds the tensor map of the tensor-core kernel); 0: not given
 };
 constexpr int kAttnPartSlices = 16;
 constexpr int kAttnPartUnits = 296;        // (row, KV head) pairs below which a context is split over CTAs: two CTAs per SM (sizes the partial-result buffer)

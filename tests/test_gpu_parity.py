@@ -412,6 +412,50 @@ def test_chunked_prefill_with_attention_layers(rows):
     _compare_tokens(toks[2], ref_toks, ref_logits, "hybrid chunked prefill, sequence 2")
 
 
+@pytest.mark.parametrize("case", ["hpk1", "hpk2", "hpk8", "window", "slices"])
+def test_tensor_core_attention_shapes(case):
+    """The attention kernel for a bf16 cache with 64-wide heads (tensor cores, pages staged by tensor-map copies) against
+    the oracle, over what its index arithmetic depends on: 1 / 2 / 8 query heads per KV head (16, 8, 2 token rows per
+    CTA in the batched prefill; 4 is what the other hybrid tests run, with a ragged last group: 150 is not a multiple of 16), a sliding window whose ring wraps
+    (decode form only: such a prompt goes token by token), and a context long enough to be split over several CTAs at a
+    batch of two (partial pages at the slice ends).  The batched prefill is also held against the token-by-token one."""
+    kv = {"hpk1": 16, "hpk2": 8, "hpk8": 2}.get(case, 4)
+    kw = dict(n_layers=2, vocab_size=500, attention_layers=[1], attn_mlp_dim=256, attn_rope_base=10000.0, attn_kv_heads=kv)
+    B, T, n_new, cap = 3, 150, 6, 256
+    if case == "window":
+        kw["attn_window_sizes"] = [40]
+        T = 70
+    if case == "slices":
+        B, T, cap = 2, 600, 1024
+    cfg = synth.base_config(**kw)
+    assert cfg.attn_head_dim == 64
+    tens = list(synth.iter_tensors(cfg, seed=21, weights_dtype="bf16", perturb_ones=0.05))
+    prompts = synth.random_prompts(B, T, cfg.vocab_size, seed=5)
+    model = lumi_b200.NmModel.from_tensors(cfg, tens)
+    sess = model.init_states(B, cap)
+    toks, lens, dump, st = sess.generate(prompts, n_new, ignore_eos=True, dump_logits=True)
+    om = cpu_oracle.OracleModel(cfg, tens)
+    worst = 0.0
+    for b in (0, B - 1):
+        ref_toks, ref_logits = om.init_states().generate(prompts[b], n_new, ignore_eos=True, dump_logits=True)
+        n_same = n_new if np.array_equal(toks[b], ref_toks) else int(np.argmax(toks[b] != ref_toks)) + 1
+        worst = max(worst, max(rel_err(dump[i, b], ref_logits[i]) for i in range(n_same)))
+        _compare_tokens(toks[b], ref_toks, ref_logits, f"{case}, sequence {b}")
+    print(f"{case}: worst logit error against the oracle {worst:.2e}")
+    assert worst < 2e-4            # measured 4e-6 .. 8e-6 (the cache holds bf16 K / V, the oracle fp32)
+    if case != "window":
+        step = model.init_states(B, cap)
+        step.set_option("chunked_prefill", 0)
+        lg_step = step.prefill(prompts)
+        sess.reset()
+        lg = sess.prefill(prompts)
+        for b in range(B):
+            assert rel_err(lg[b], lg_step[b]) < 2e-4, (b, rel_err(lg[b], lg_step[b]))
+        step.close()
+    sess.close()
+    model.close()
+
+
 def test_slot_reuse_by_transplanting_a_prefilled_sequence():
     """Continuous batching with the snapshot calls: while a batch of three sequences decodes, sequence 1 ends; a new
     prompt is prefilled in a one-slot side session, its snapshot is loaded into slot 1, and decoding goes on.
