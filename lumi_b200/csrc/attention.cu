@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     // this CTA's slice of the cached tokens, in whole pages; its first pages are requested before anything else is done
     const int per = ((T + nsplit - 1) / nsplit + kPageTokens - 1) / kPageTokens * kPageTokens;
     const int tb = split * per, te = min(T, tb + per);
-    const int ntiles = a.phase == 1 || te <= tb ? 0 : (te - tb + kPageTokens - 1) / kPageTokens;
+    const int ntiles = te <= tb ? 0 : (te - tb + kPageTokens - 1) / kPageTokens;
     const bool pages_ok = a.pages_per_seq <= 64;
     auto issue = [&](int i, bool staged) {               // thread 0: page i of the slice into stage i % NST
         const int t00 = tb + i * kPageTokens;
@@ -174,7 +174,6 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
             vd[2 * pr] = vnew[2 * pr]; vd[2 * pr + 1] = vnew[2 * pr + 1];
         }
     }
-    if (a.phase == 1) return;                            // append only
     const int local_slot = a.phase == 2 ? -1 : slot_new; // attend only: every row is already in the cache
     if (pages_ok) for (int i = tid; i < a.pages_per_seq; i += 128) pages[i] = pt[i];
     __syncthreads();
@@ -394,6 +393,41 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
         }
         emit(i, __fdiv_rn(num, den));
     }
+}
+
+// The append-only pass of a prompt slice (phase 1): one thread per (token row, KV head, pair of dims) rotates the K pair at the
+// row's position (extension) and stores the K and the V pair as the cache holds them (KvCache::append, model.rs:133-152).
+template <typename KT>
+__global__ void __launch_bounds__(256) kv_append_kernel(AttnArgs a, KT* pool, long total) {
+    const long i = (long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const int HD = a.head_dim, half = HD / 2;
+    const int pr = (int)(i % half), kvh = (int)((i / half) % a.kv_heads), r = (int)(i / ((long)half * a.kv_heads));
+    const int b = a.b0 + r / a.rows_per_seq;
+    const int pos = a.pos[b] + r % a.rows_per_seq;
+    const int cap = a.window > 0 ? min(a.window, a.max_tokens) : a.max_tokens;
+    const int slot = (a.window > 0 && a.window <= a.max_tokens) ? pos % a.window : pos;
+    if (pos < 0 || slot >= cap) {
+        atomicOr(&a.ctl->status, STATUS_KV_FULL);
+        return;
+    }
+    const float* kn = a.qkv + (size_t)r * a.ldq + (size_t)a.n_heads * HD + (size_t)kvh * HD;
+    const float* vn = kn + (size_t)a.kv_heads * HD;
+    float k0 = kn[2 * pr], k1 = kn[2 * pr + 1];
+    if (a.rope_base > 0.f) {
+        float inv = powf(a.rope_base, -(float)(2 * pr) / (float)HD);
+        float ang = __fmul_rn((float)pos, inv);
+        float sa, ca;
+        sincosf(ang, &sa, &ca);
+        float x0 = __fsub_rn(__fmul_rn(ca, k0), __fmul_rn(sa, k1));
+        float x1 = __fadd_rn(__fmul_rn(sa, k0), __fmul_rn(ca, k1));
+        k0 = x0; k1 = x1;
+    }
+    const int32_t* pt = a.page_table + (size_t)b * a.pages_per_seq;
+    KT* kd = kv_ptr(pool, pt, slot, 0, a.kv_heads, kvh, HD);
+    KT* vd = kv_ptr(pool, pt, slot, 1, a.kv_heads, kvh, HD);
+    KvIo<KT>::st(&kd[2 * pr], k0); KvIo<KT>::st(&kd[2 * pr + 1], k1);
+    KvIo<KT>::st(&vd[2 * pr], vn[2 * pr]); KvIo<KT>::st(&vd[2 * pr + 1], vn[2 * pr + 1]);
 }
 
 // ---- bf16 cache, head_dim 64: the same walk on the tensor cores ---------------------------------------------
@@ -791,6 +825,11 @@ cudaError_t launch_mma(const AttnArgs& a, cudaStream_t st) {
 template <typename KT>
 cudaError_t launch_kt(const AttnArgs& a, cudaStream_t st) {
     const int hpk = a.n_heads / a.kv_heads;
+    if (a.phase == 1) {
+        const long total = (long)a.B * a.kv_heads * (a.head_dim / 2);
+        kv_append_kernel<KT><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a, reinterpret_cast<KT*>(a.pool), total);
+        return cudaGetLastError();
+    }
     if constexpr (sizeof(KT) == 2) {
         // bf16 cache with 64-wide heads: the tensor-core kernel (attend; the append-only pass of a prompt slice stays below)
         if (a.head_dim == 64 && a.phase != 1 && a.pool_bytes > 0 && a.pool_bytes / 128 < (size_t)1 << 31 && (a.B % a.rows_per_seq) == 0 &&

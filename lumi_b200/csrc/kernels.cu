@@ -917,16 +917,14 @@ __global__ void __launch_bounds__(256, MINB) ssm_step_kernel(SsmArgs a) {
 // h <- h_init broadcast over head_dim (model.rs:744-748); factors and angles <- 0 (:751-752)
 __global__ void state_reset_kernel(float* h, float* xprev, float* bprev, float* cum, const float* __restrict__ h_init,
                                    const int32_t* __restrict__ slots, int H, int P, int N) {
+    // one block per (sequence, head): the head's P x N tile, its P + N factors and its N / 2 angles
     const int slot = slots ? slots[blockIdx.x] : blockIdx.x;
-    const size_t per = (size_t)H * P * N;
-    for (size_t i = threadIdx.x; i < per; i += blockDim.x) {
-        int n = i % N;
-        int hh = i / ((size_t)P * N);
-        h[(size_t)slot * per + i] = h_init ? h_init[hh * N + n] : 0.f;
-    }
-    for (int i = threadIdx.x; i < H * P; i += blockDim.x) xprev[(size_t)slot * H * P + i] = 0.f;
-    for (int i = threadIdx.x; i < H * N; i += blockDim.x) bprev[(size_t)slot * H * N + i] = 0.f;
-    for (int i = threadIdx.x; i < H * N / 2; i += blockDim.x) cum[(size_t)slot * H * (N / 2) + i] = 0.f;
+    const int hh = blockIdx.y;
+    float* ht = h + ((size_t)slot * H + hh) * P * N;
+    for (int i = threadIdx.x; i < P * N; i += blockDim.x) ht[i] = h_init ? h_init[hh * N + i % N] : 0.f;
+    for (int i = threadIdx.x; i < P; i += blockDim.x) xprev[((size_t)slot * H + hh) * P + i] = 0.f;
+    for (int i = threadIdx.x; i < N; i += blockDim.x) bprev[((size_t)slot * H + hh) * N + i] = 0.f;
+    for (int i = threadIdx.x; i < N / 2; i += blockDim.x) cum[((size_t)slot * H + hh) * (N / 2) + i] = 0.f;
 }
 
 // ---- sampling (main.rs:142-148, 197-209) -----------------------------------------------------------
@@ -1492,7 +1490,7 @@ cudaError_t launch_ssm_step(const SsmArgs& a, cudaStream_t st) {
 
 cudaError_t launch_state_reset(float* h, float* xprev, float* bprev, float* cum, const float* h_init, const int32_t* slots,
                                int n_slots, int H, int P, int N, cudaStream_t st) {
-    state_reset_kernel<<<n_slots, 256, 0, st>>>(h, xprev, bprev, cum, h_init, slots, H, P, N);
+    state_reset_kernel<<<dim3(n_slots, H), 256, 0, st>>>(h, xprev, bprev, cum, h_init, slots, H, P, N);
     return cudaGetLastError();
 }
 
