@@ -660,7 +660,22 @@ __global__ void __launch_bounds__(256, 2) gemv_pre_kernel(const float* A, int ld
             default: break;
         }
     }
-    if (timed_out && lane == 0 && status != nullptr) atomicOr(status, STATUS_TIMEOUT);
+    if (timed_out) {
+        // report, then give this warp's copies a second, equally bounded chance to land before the CTA's shared memory goes away
+        if (lane == 0 && status != nullptr) atomicOr(status, STATUS_TIMEOUT);
+        const uint32_t bar = smem_u32(&bars[warp]);
+        uint32_t done = 0, polls = 0;
+        uint64_t t0 = 0;
+        while (!done) {
+            asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\nselp.u32 %0, 1, 0, p;\n}"
+                         : "=r"(done) : "r"(bar) : "memory");
+            if (!done && (++polls & 255u) == 0u) {
+                const uint64_t now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > 500000000ull) break;
+            }
+        }
+    }
     TL_END(K == 1024 ? 1 : 3)
 }
 
