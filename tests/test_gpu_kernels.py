@@ -51,7 +51,8 @@ def test_gemv_matches_fp64(wdt, M, N, K):
 @pytest.mark.parametrize("split", [True, False])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (64, 7360, 1024), (200, 259, 1024), (300, 1024, 2048), (2048, 512, 128),
                                    (2048, 7360, 1024), (1000, 5000, 512), (2300, 4100, 64),    # more tiles than SMs: persistent CTAs
-                                   (64, 1024, 2048), (512, 1024, 2048), (100, 1024, 2816), (300, 512, 4096)])   # few tiles: K split over CTAs
+                                   (64, 1024, 2048), (512, 1024, 2048), (100, 1024, 2816), (300, 512, 4096),    # few tiles: K split over CTAs
+                                   (64, 1000, 2048), (128, 264, 4096), (17, 36, 1024)])                    # ... with ragged last tiles
 def test_tcgen05_gemm_matches_torch(split, M, N, K):
     torch = _torch()
     g = torch.Generator(device="cpu").manual_seed(M + N + K)
