@@ -150,10 +150,11 @@ int32_t lumi_prefill(lumi_session* s, const uint32_t* tokens, int32_t batch, int
 
 /* The same for prompts of different lengths: tokens[batch][T_max] row-major, of which sequence b uses the first
  * lengths[b] (1 <= lengths[b] <= T_max; what is stored behind them is not looked at).  Each sequence goes through its
- * own tokens position by position (the reference's prefill, inference/src/main.rs:121-125, once per sequence) and ends
- * in exactly the state a lumi_prefill of its own tokens alone would leave; last_logits [batch][vocab] (may be NULL) are
- * those of each sequence's own last position.  Always token by token (the batched path takes rectangles only); at most
- * 1024 sequences per call. */
+ * own tokens (the reference's prefill, inference/src/main.rs:121-125, once per sequence) and ends in the state a
+ * lumi_prefill of its own tokens alone would leave; last_logits [batch][vocab] (may be NULL) are those of each
+ * sequence's own last position.  Token by token, or, where the longest prompt qualifies for it, by the batched path of
+ * the "chunked_prefill" option over the rectangle of the longest prompt (same state to rounding).  At most 1024
+ * sequences per call. */
 int32_t lumi_prefill_ragged(lumi_session* s, const uint32_t* tokens, const int32_t* lengths, int32_t batch, int32_t T_max,
                             float* last_logits);
 

@@ -1008,7 +1008,9 @@ bool use_chunked_prefill(const lumi_session* s, int batch, int T) {
 // prompt_dev[T][batch].  Leaves the decode state of every layer as the step-by-step path would, the
 // last position's residual in x, and (with_head) its logits plus the sampled first token.
 // score_out (device, [batch][T-1]) != null: log p(next prompt token) at every position, from the head over all rows.
-int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head, float* score_out = nullptr) {
+// lens (device, [batch]) != null: prompts of different lengths inside the [T][batch] rectangle (T = the longest): every sequence
+// ends in the state after its own last token, x holds the residual at that token, and padding is never looked at.
+int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head, float* score_out = nullptr, const int32_t* lens = nullptr) {
     const Config& c = s->m->cfg;
     const int D = c.d_model, DI = c.d_inner(), R = c.in_proj_out();
     const bool hybrid = s->m->n_attn > 0;
@@ -1030,6 +1032,11 @@ int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head, float
         LUMI_CUDA(cudaMalloc(&s->pf_rc, sizeof(float) * rp));
         LUMI_CUDA(cudaMalloc(&s->pf_hi, sizeof(__nv_bfloat16) * rp * wact));
         LUMI_CUDA(cudaMalloc(&s->pf_lo, sizeof(__nv_bfloat16) * rp * wact));
+        // rows that a launch skips (padding behind a shorter prompt) keep what they held: make that finite from the start
+        LUMI_CUDA(cudaMemsetAsync(s->pf_x, 0, sizeof(float) * rp * D, s->stream));
+        LUMI_CUDA(cudaMemsetAsync(s->pf_proj, 0, sizeof(float) * rp * wproj, s->stream));
+        LUMI_CUDA(cudaMemsetAsync(s->pf_hi, 0, sizeof(__nv_bfloat16) * rp * wact, s->stream));
+        LUMI_CUDA(cudaMemsetAsync(s->pf_lo, 0, sizeof(__nv_bfloat16) * rp * wact, s->stream));
         s->pf_rows = rows_max;
     }
     const size_t B = s->max_batch;
@@ -1040,7 +1047,7 @@ int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head, float
             const int ts = std::min(TS, T - t0);
             const int M = nb * ts;
             LUMI_CUDA(launch_prefill_embed(s->m->embedding.p, s->m->embedding.dtype, s->prompt_dev, s->pf_x, D, c.vocab, M, ts, t0, b0,
-                                           batch, s->ctl, s->stream));
+                                           batch, s->ctl, s->stream, lens));
             s->launches += 1;
             for (const Layer& L : s->m->layers) {
                 const size_t l = L.kind_idx;
@@ -1063,6 +1070,7 @@ int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head, float
                     a.rope_base = c.attn_rope_base;
                     a.ctl = s->ctl;
                     a.rows_per_seq = ts; a.b0 = b0;
+                    a.row_len = lens;
                     for (int phase = 1; phase <= 2; ++phase) {
                         a.phase = phase;
                         cudaError_t e = launch_attention_decode(a, s->stream);
@@ -1095,13 +1103,14 @@ int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head, float
                 a.yhi = s->pf_hi; a.ylo = lo;
                 a.H = c.n_heads; a.G = c.n_groups; a.ts = ts; a.nb = nb; a.b0 = b0; a.eps = c.eps;
                 a.status = &s->ctl->status;
+                a.lens = lens; a.t_abs0 = t0;
                 LUMI_CUDA(launch_prefill_scan(a, s->stream));
                 GemmArgs g2{s->pf_hi, lo, (const __nv_bfloat16*)L.m.out_proj.p, s->pf_x, D, M, D, DI, 1, &s->ctl->status};
                 LUMI_TRY(launch_gemm_tcgen05(g2, s->stream));
                 s->launches += 5;
             }
             if (hybrid) {
-                LUMI_CUDA(launch_kv_advance(s->kv_pos, b0, nb, ts, s->stream));
+                LUMI_CUDA(launch_kv_advance(s->kv_pos, b0, nb, ts, s->stream, lens, t0));
                 s->launches += 1;
             }
             if (score_out != nullptr) {
@@ -1120,8 +1129,8 @@ int32_t prefill_chunked(lumi_session* s, int batch, int T, bool with_head, float
                 }
                 s->launches += 1;
             }
-            if (t0 + ts >= T) {
-                LUMI_CUDA(launch_gather_last(s->pf_x, s->x, D, ts, nb, b0, s->stream));
+            if (t0 + ts >= T || lens != nullptr) {      // different lengths: every slice may hold some sequence's last token
+                LUMI_CUDA(launch_gather_last(s->pf_x, s->x, D, ts, nb, b0, s->stream, lens, t0));
                 s->launches += 1;
             }
         }
@@ -1240,20 +1249,27 @@ extern "C" int32_t lumi_prefill_ragged(lumi_session* s, const uint32_t* tokens, 
     fill_ctl(s, batch, nullptr);
     s->ctl_host->prompt = s->prompt_dev;
     s->ctl_host->prompt_len = longest;
+    // long prompts: the batched path over the rectangle of the longest one (each sequence stops at its own length)
+    const bool chunked = use_chunked_prefill(s, batch, longest);
+    if (chunked) s->ctl_host->prompt_pos = longest;
     LUMI_TRY(push_ctl(s));
-    const bool mega = s->opt_mega;
-    s->opt_mega = 0;
-    int32_t rc = LUMI_OK;
-    for (int t = 0; t < longest && rc == LUMI_OK; ++t) {       // launched directly: the captured graphs of the step do not carry the length table
-        int64_t n = 0;
-        rc = enqueue_step(s, batch, false, &n, nullptr, s->row_len);
-        s->launches += n;
+    if (chunked) {
+        LUMI_TRY(prefill_chunked(s, batch, longest, false, nullptr, s->row_len));
+    } else {
+        const bool mega = s->opt_mega;
+        s->opt_mega = 0;
+        int32_t rc = LUMI_OK;
+        for (int t = 0; t < longest && rc == LUMI_OK; ++t) {       // launched directly: the captured graphs of the step do not carry the length table
+            int64_t n = 0;
+            rc = enqueue_step(s, batch, false, &n, nullptr, s->row_len);
+            s->launches += n;
+        }
+        s->opt_mega = mega;
+        LUMI_TRY(rc);
     }
-    s->opt_mega = mega;
-    LUMI_TRY(rc);
     if (last_logits) {
         // final norm + tied head on each sequence's residual at its own last token
-        LUMI_CUDA(cudaMemcpyAsync(s->x, s->xlast, sizeof(float) * batch * s->m->cfg.d_model, cudaMemcpyDeviceToDevice, s->stream));
+        if (!chunked) LUMI_CUDA(cudaMemcpyAsync(s->x, s->xlast, sizeof(float) * batch * s->m->cfg.d_model, cudaMemcpyDeviceToDevice, s->stream));
         StepPlan p{s, batch, use_tc(s, batch)};
         p.st_hi = p.st_lo = s->stream;
         const Config& c = s->m->cfg;

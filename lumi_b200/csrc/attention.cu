@@ -101,8 +101,19 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, KT* pool) 
     const float* kn = a.qkv + (size_t)r * a.ldq + D + kvh * HD;
     const float* vn = kn + KV;
     if (a.row_len != nullptr) {                          // prompts of different lengths: this sequence's prompt has ended
-        const int pp = a.ctl->prompt_pos;
-        if (pp < a.ctl->prompt_len && pp >= a.row_len[b]) return;
+        if (a.phase == 0) {
+            const int pp = a.ctl->prompt_pos;
+            if (pp < a.ctl->prompt_len && pp >= a.row_len[b]) return;
+        } else if (a.pos[b] + r % a.rows_per_seq >= a.row_len[b]) {
+            // a row of a prompt slice behind a shorter prompt: nothing to attend to; its output row is zero, so that
+            // whatever follows it through the layers stays finite
+            for (int i = tid; i < HPK * HD; i += 128) {
+                const size_t o = (size_t)r * D + (size_t)kvh * HPK * HD + i;
+                if (a.ctx32) a.ctx32[o] = 0.f;
+                if (a.chi) { a.chi[o] = __float2bfloat16_rn(0.f); if (a.clo) a.clo[o] = __float2bfloat16_rn(0.f); }
+            }
+            return;
+        }
     }
     const int pos = a.pos[b] + r % a.rows_per_seq;
     const int32_t* pt = a.page_table + (size_t)b * a.pages_per_seq;
@@ -405,6 +416,7 @@ __global__ void __launch_bounds__(256) kv_append_kernel(AttnArgs a, KT* pool, lo
     const int pr = (int)(i % half), kvh = (int)((i / half) % a.kv_heads), r = (int)(i / ((long)half * a.kv_heads));
     const int b = a.b0 + r / a.rows_per_seq;
     const int pos = a.pos[b] + r % a.rows_per_seq;
+    if (a.row_len != nullptr && pos >= a.row_len[b]) return;          // padding behind a shorter prompt
     const int cap = a.window > 0 ? min(a.window, a.max_tokens) : a.max_tokens;
     const int slot = (a.window > 0 && a.window <= a.max_tokens) ? pos % a.window : pos;
     if (pos < 0 || slot >= cap) {
@@ -487,18 +499,34 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnArgs a, const __grid_
     const int r0 = sidx * ts + i0;                        // first of them in the projection / output arrays
     const int b = a.b0 + sidx;
     const int D = a.n_heads * HD, KV = a.kv_heads * HD;
-    if (a.row_len != nullptr) {                          // prompts of different lengths: this sequence's prompt has ended
-        const int pp = a.ctl->prompt_pos;
-        if (pp < a.ctl->prompt_len && pp >= a.row_len[b]) return;
-    }
     const int pos0 = a.pos[b] + i0;
+    int nvalid = nrow;                                   // rows of this CTA that belong to their sequence's prompt
+    if (a.row_len != nullptr) {                          // prompts of different lengths
+        if (a.phase == 0) {                              // decode form: this sequence's prompt has ended
+            const int pp = a.ctl->prompt_pos;
+            if (pp < a.ctl->prompt_len && pp >= a.row_len[b]) return;
+        } else {
+            nvalid = max(0, min(nrow, a.row_len[b] - pos0));
+        }
+    }
+    if (nvalid < nrow) {
+        // rows of a prompt slice behind a shorter prompt: nothing to attend to; their output rows are zero, so that
+        // whatever follows them through the layers stays finite
+        for (int i = tid + nvalid * HPK * HD; i < nrow * HPK * HD; i += 128) {
+            const int m = i / HD;
+            const size_t oo = (size_t)(r0 + m / HPK) * D + (size_t)(kvh * HPK + m % HPK) * HD + i % HD;
+            if (a.ctx32) a.ctx32[oo] = 0.f;
+            if (a.chi) { a.chi[oo] = __float2bfloat16_rn(0.f); if (a.clo) a.clo[oo] = __float2bfloat16_rn(0.f); }
+        }
+        if (nvalid == 0) return;
+    }
     const int32_t* pt = a.page_table + (size_t)b * a.pages_per_seq;
     const int cap = a.window > 0 ? min(a.window, a.max_tokens) : a.max_tokens;
     // cached tokens the first row sees; row j sees j more (several rows only without a window: the host takes care of that)
     int T0, slot_new;
     if (a.window > 0 && a.window <= a.max_tokens) { slot_new = pos0 % a.window; T0 = min(pos0 + 1, a.window); }
     else { slot_new = pos0; T0 = pos0 + 1; }
-    const int T = T0 + nrow - 1;                          // ... and the last row
+    const int T = T0 + nvalid - 1;                        // ... and the last row that counts
     if (pos0 < 0 || slot_new >= cap || T > cap) {
         if (tid == 0) atomicOr(&a.ctl->status, STATUS_KV_FULL);
         return;
@@ -531,7 +559,7 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnArgs a, const __grid_
         const int m = i / (HD / 2), pr = i % (HD / 2);
         const int j = m / HPK, hq = m % HPK;
         float q0 = 0.f, q1 = 0.f;
-        if (j < nrow) {
+        if (j < nvalid) {
             const float* q = a.qkv + (size_t)(r0 + j) * a.ldq + (size_t)(kvh * HPK + hq) * HD;
             q0 = q[2 * pr]; q1 = q[2 * pr + 1];
             if (a.rope_base > 0.f) {
@@ -589,8 +617,8 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnArgs a, const __grid_
         ldsm4(ql[ks], smem_addr(qtile + 16 * 128) + off);
     }
     // per-row limits of the two query columns this thread sees in the accumulators (g and g + 8): 0 for unused columns
-    const int lim0 = (g / HPK) < nrow ? T0 + g / HPK : 0;
-    const int lim1 = ((g + 8) / HPK) < nrow ? T0 + (g + 8) / HPK : 0;
+    const int lim0 = (g / HPK) < nvalid ? T0 + g / HPK : 0;
+    const int lim1 = ((g + 8) / HPK) < nvalid ? T0 + (g + 8) / HPK : 0;
     const float scale = 0.125f;                          // 1 / sqrt(64), model.rs:530
 
     float m0 = kMaskedScore, m1 = kMaskedScore, l0 = 0.f, l1 = 0.f;    // running maximum and this thread's share of the sum, rows g and g + 8
@@ -717,7 +745,7 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnArgs a, const __grid_
     };
     constexpr int PW = HPK * (HD + 2);                   // floats per slice in `part`: [HPK] maxima, [HPK] sums, [HPK][HD] context
     float* mine = nsplit > 1 ? a.part + ((size_t)(grp * a.kv_heads + kvh) * kAttnMaxSplits + split) * PW : nullptr;
-    for (int i = tid; i < nrow * HPK * HD; i += 128) {
+    for (int i = tid; i < nvalid * HPK * HD; i += 128) {
         const int m = i / HD, d = i % HD;
         float mx = comb[m * CW];
 #pragma unroll
@@ -848,15 +876,17 @@ cudaError_t launch_kt(const AttnArgs& a, cudaStream_t st) {
     return cudaErrorInvalidValue;
 }
 
-__global__ void kv_advance_kernel(int32_t* kv_pos, int b0, int nb, int by) {
+__global__ void kv_advance_kernel(int32_t* kv_pos, int b0, int nb, int by, const int32_t* lens, int t_abs0) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < nb) kv_pos[b0 + i] += by;
+    if (i >= nb) return;
+    // prompts of different lengths: a sequence advances by the tokens of the slice that belong to its prompt
+    kv_pos[b0 + i] += lens != nullptr ? max(0, min(by, lens[b0 + i] - t_abs0)) : by;
 }
 
 }  // namespace
 
-cudaError_t launch_kv_advance(int32_t* kv_pos, int b0, int nb, int by, cudaStream_t st) {
-    kv_advance_kernel<<<(nb + 127) / 128, 128, 0, st>>>(kv_pos, b0, nb, by);
+cudaError_t launch_kv_advance(int32_t* kv_pos, int b0, int nb, int by, cudaStream_t st, const int32_t* lens, int t_abs0) {
+    kv_advance_kernel<<<(nb + 127) / 128, 128, 0, st>>>(kv_pos, b0, nb, by, lens, t_abs0);
     return cudaGetLastError();
 }
 

@@ -295,13 +295,14 @@ struct AttnArgs {
     float* part = nullptr;
     int32_t* part_count = nullptr;
     int max_ctx_hint = 0;
-    const int32_t* row_len = nullptr;    // prompts of different lengths: rows whose prompt has ended are skipped (decode form only)
+    const int32_t* row_len = nullptr;    // prompts of different lengths: rows at or past their sequence's prompt length are skipped (decode form: by the
+                                         // step's prompt position; prompt slices: by the row's own position, and their output rows are zero)
     size_t pool_bytes = 0;               // size of this layer's page pool (bounds the tensor map of the tensor-core kernel); 0: not given
 };
 constexpr int kAttnPartSlices = 16;
 constexpr int kAttnPartUnits = 296;        // (row, KV head) pairs below which a context is split over CTAs: two CTAs per SM (sizes the partial-result buffer)
 cudaError_t launch_attention_decode(const AttnArgs& a, cudaStream_t st);
-cudaError_t launch_kv_advance(int32_t* kv_pos, int b0, int nb, int by, cudaStream_t st);
+cudaError_t launch_kv_advance(int32_t* kv_pos, int b0, int nb, int by, cudaStream_t st, const int32_t* lens = nullptr, int t_abs0 = 0);
 
 
 // ---- tcgen05 GEMM (gemm_tcgen05.cu) ---------------------------------------------------------------
@@ -379,12 +380,16 @@ struct PrefillArgs {
     int H, G, ts, nb, b0;                    // heads, groups, tokens per sequence in this launch, sequences, first slot
     float eps;
     int32_t* status = nullptr;               // device word that receives STATUS_TIMEOUT if the bounded wait gives up
+    // prompts of different lengths: lens[slot] = prompt length of the sequence, t_abs0 = prompt position of this launch's first
+    // token; a sequence takes min(ts, lens - t_abs0) tokens of the launch (none: its state is left alone).  null: all take ts
+    const int32_t* lens = nullptr;
+    int t_abs0 = 0;
 };
 bool prefill_ssd_supported(const Config& c);
 cudaError_t launch_prefill_embed(const void* emb, int dtype, const uint32_t* prompt, float* x, int D, int vocab, int rows, int ts,
-                                 int t_abs0, int b_abs0, int batch_total, StepCtl* ctl, cudaStream_t st);
+                                 int t_abs0, int b_abs0, int batch_total, StepCtl* ctl, cudaStream_t st, const int32_t* lens = nullptr);
 cudaError_t launch_prefill_scan(const PrefillArgs& a, cudaStream_t st);
-cudaError_t launch_gather_last(const float* xr, float* x, int D, int ts, int nb, int b0, cudaStream_t st);
+cudaError_t launch_gather_last(const float* xr, float* x, int D, int ts, int nb, int b0, cudaStream_t st, const int32_t* lens = nullptr, int t_abs0 = 0);
 
 cudaError_t launch_gate_mul(const float* gu, int ld, float* out32, __nv_bfloat16* hi, __nv_bfloat16* lo, int B, int mlp,
                             cudaStream_t st);

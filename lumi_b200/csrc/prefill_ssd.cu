@@ -175,8 +175,12 @@ constexpr uint32_t kChunkTxBytes = 3 * LCH * 32 * 4 + 2 * LCH * 64 * 4;
 // row r = b * ts + t  of the super-chunk; token ids come from prompt[(t_abs) * batch_total + b_abs]
 template <typename WT>
 __global__ void embed_rows_kernel(const WT* __restrict__ emb, const uint32_t* __restrict__ prompt, float* __restrict__ x, int D,
-                                  int vocab, int ts, int t_abs0, int b_abs0, int batch_total, StepCtl* ctl) {
+                                  int vocab, int ts, int t_abs0, int b_abs0, int batch_total, StepCtl* ctl, const int32_t* __restrict__ lens) {
     const int r = blockIdx.x, b = r / ts, t = r - b * ts;
+    if (lens != nullptr && t_abs0 + t >= lens[b_abs0 + b]) {      // padding behind a shorter prompt: never looked at, the row is zero
+        for (int k = threadIdx.x; k < D; k += blockDim.x) x[(size_t)r * D + k] = 0.f;
+        return;
+    }
     uint32_t tok = prompt[(size_t)(t_abs0 + t) * batch_total + b_abs0 + b];
     if (tok >= (uint32_t)vocab) { if (threadIdx.x == 0) atomicOr(&ctl->status, STATUS_BAD_TOKEN); tok = 0; }
     const WT* row = emb + (size_t)tok * D;
@@ -206,9 +210,12 @@ __global__ void bc_stats_kernel(const float* __restrict__ proj, int ldp, int off
 }
 
 // last token's residual row of every sequence -> x[b][D] (for the lm_head after the prompt)
-__global__ void gather_last_kernel(const float* __restrict__ xr, float* __restrict__ x, int D, int ts, int b0) {
+__global__ void gather_last_kernel(const float* __restrict__ xr, float* __restrict__ x, int D, int ts, int b0, const int32_t* __restrict__ lens,
+                                   int t_abs0) {
     const int b = blockIdx.x;
-    for (int k = threadIdx.x; k < D; k += blockDim.x) x[(size_t)(b0 + b) * D + k] = xr[((size_t)b * ts + ts - 1) * D + k];
+    const int idx = lens != nullptr ? lens[b0 + b] - 1 - t_abs0 : ts - 1;      // the sequence's last prompt token, if this slice holds it
+    if (idx < 0 || idx >= ts) return;
+    for (int k = threadIdx.x; k < D; k += blockDim.x) x[(size_t)(b0 + b) * D + k] = xr[((size_t)b * ts + idx) * D + k];
 }
 
 __global__ void __launch_bounds__(128, 3)
@@ -218,10 +225,14 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
     PfSmem& sm = *reinterpret_cast<PfSmem*>((reinterpret_cast<uintptr_t>(pf_raw) + 1023) & ~(uintptr_t)1023);
     const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g4 = lane >> 2, t4 = lane & 3;               // mma fragment coordinates: row group, column pair
-    const int H = a.H, DI = H * P, BC = a.G * N, ts = a.ts, R = a.ldp;
+    const int H = a.H, DI = H * P, BC = a.G * N, R = a.ldp;
+    const int tsl = a.ts;                                   // rows per sequence in the projection / output arrays
+    // tokens this sequence takes from the launch (prompts of different lengths end early; none: the state stays as it is)
+    const int ts = a.lens != nullptr ? max(0, min(tsl, a.lens[a.b0 + b] - a.t_abs0)) : tsl;
+    if (ts == 0) return;
     const int grp = h / (H / a.G);
     const size_t bh = (size_t)(a.b0 + b) * H + h;
-    const float* prow0 = a.proj + (size_t)b * ts * R;      // first token row of this sequence
+    const float* prow0 = a.proj + (size_t)b * tsl * R;     // first token row of this sequence
     const int off_b = 2 * DI, off_c = off_b + BC, off_dt = off_c + BC;
     const float PI_F = 3.14159265358979323846f;
     const float TWO_PI = 6.28318530717958647692f;
@@ -244,7 +255,7 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
     __syncthreads();
 
     auto issue_chunk = [&](int t0) {               // one thread: the five box copies of the chunk starting at token t0
-        const int row0 = b * ts + t0;
+        const int row0 = b * tsl + t0;
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(kChunkTxBytes) : "memory");
         tma_load_2d(&sm.rx[0][0], &map32, bar, h * P, row0);
         tma_load_2d(&sm.rz[0][0], &map32, bar, DI + h * P, row0);
@@ -262,7 +273,7 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
     auto request_scalars = [&](int t0) {
         if (tid < LCH && t0 + tid < ts) {
             const float* pr = prow0 + (size_t)(t0 + tid) * R;
-            const size_t row = (size_t)b * ts + t0 + tid;
+            const size_t row = (size_t)b * tsl + t0 + tid;
             n_dt = pr[off_dt + h]; n_lam = pr[off_dt + H + h]; n_a = pr[off_dt + 2 * H + h];
             n_rb = a.rb[row]; n_rc = a.rc[row];
         } else if (tid == LCH && t0 + LCH < ts) {
@@ -552,7 +563,7 @@ ssd_prefill_kernel(const __grid_constant__ CUtensorMap map32, const __grid_const
                     else if (slot == 2) { vh[2] = rh; vl[2] = rl; } else { vh[3] = rh; vl[3] = rl; }
                 }
                 if (valid(i)) {
-                    const size_t o = ((size_t)b * ts + t0 + i) * DI + h * P + 8 * t4;
+                    const size_t o = ((size_t)b * tsl + t0 + i) * DI + h * P + 8 * t4;
                     *reinterpret_cast<uint4*>(a.yhi + o) = make_uint4(vh[0], vh[1], vh[2], vh[3]);
                     if (a.ylo) *reinterpret_cast<uint4*>(a.ylo + o) = make_uint4(vl[0], vl[1], vl[2], vl[3]);
                 }
@@ -633,11 +644,11 @@ bool prefill_ssd_supported(const Config& c) {
 }
 
 cudaError_t launch_prefill_embed(const void* emb, int dtype, const uint32_t* prompt, float* x, int D, int vocab, int rows, int ts,
-                                 int t_abs0, int b_abs0, int batch_total, StepCtl* ctl, cudaStream_t st) {
+                                 int t_abs0, int b_abs0, int batch_total, StepCtl* ctl, cudaStream_t st, const int32_t* lens) {
     if (dtype == LUMI_DTYPE_BF16)
-        embed_rows_kernel<__nv_bfloat16><<<rows, 128, 0, st>>>((const __nv_bfloat16*)emb, prompt, x, D, vocab, ts, t_abs0, b_abs0, batch_total, ctl);
+        embed_rows_kernel<__nv_bfloat16><<<rows, 128, 0, st>>>((const __nv_bfloat16*)emb, prompt, x, D, vocab, ts, t_abs0, b_abs0, batch_total, ctl, lens);
     else
-        embed_rows_kernel<float><<<rows, 128, 0, st>>>((const float*)emb, prompt, x, D, vocab, ts, t_abs0, b_abs0, batch_total, ctl);
+        embed_rows_kernel<float><<<rows, 128, 0, st>>>((const float*)emb, prompt, x, D, vocab, ts, t_abs0, b_abs0, batch_total, ctl, lens);
     return cudaGetLastError();
 }
 
@@ -662,8 +673,8 @@ cudaError_t launch_prefill_scan(const PrefillArgs& a, cudaStream_t st) {
     return cudaGetLastError();
 }
 
-cudaError_t launch_gather_last(const float* xr, float* x, int D, int ts, int nb, int b0, cudaStream_t st) {
-    gather_last_kernel<<<nb, 256, 0, st>>>(xr, x, D, ts, b0);
+cudaError_t launch_gather_last(const float* xr, float* x, int D, int ts, int nb, int b0, cudaStream_t st, const int32_t* lens, int t_abs0) {
+    gather_last_kernel<<<nb, 256, 0, st>>>(xr, x, D, ts, b0, lens, t_abs0);
     return cudaGetLastError();
 }
 

@@ -456,6 +456,65 @@ def test_tensor_core_attention_shapes(case):
     model.close()
 
 
+@pytest.mark.parametrize("case", ["mamba", "hybrid", "hybrid_hd32"])
+def test_ragged_prefill_of_long_prompts_takes_the_batched_path(case):
+    """Prompts of different lengths, the longest long enough for the batched prefill (chunked scan, tensor-core GEMMs, every row
+    of a slice through the attention layers at once): each sequence must end in the state, with the last-position logits
+    and the K/V cache, of a prefill of its own tokens alone; the logits are also held against the oracle, and decoding
+    continues for all sequences together.  Lengths cover: the longest, one token, exactly one chunk, one past a chunk, a
+    slice boundary (prefill_rows forces 64-token slices in the hybrid cases) and a ragged group of attention rows."""
+    kw = dict(n_layers=3, vocab_size=700)
+    if case == "hybrid":
+        kw.update(attention_layers=[1], attn_mlp_dim=256, attn_rope_base=10000.0)                 # 64-wide heads: tensor-core attention
+    if case == "hybrid_hd32":
+        kw.update(attention_layers=[1], attn_mlp_dim=256, attn_n_heads=32, attn_kv_heads=8)        # 32-wide heads: CUDA-core attention
+    cfg = synth.base_config(**kw)
+    tens = list(synth.iter_tensors(cfg, seed=29, weights_dtype="bf16", perturb_ones=0.05))
+    lengths = np.array([200, 1, 64, 65, 128, 137, 199, 3], dtype=np.int32)
+    B, T_max, cap = len(lengths), 200, 256
+    prompts = synth.random_prompts(B, T_max, cfg.vocab_size, seed=31)
+    padded = prompts.copy()
+    for b in range(B):
+        padded[b, lengths[b]:] = 0xFFFFFFF0                  # padding is never looked at, not even range-checked
+    model = lumi_b200.NmModel.from_tensors(cfg, tens)
+    sess = model.init_states(B, cap)
+    if case != "mamba":
+        sess.set_option("prefill_rows", 512)                 # 8 sequences x 64 tokens per slice
+    logits = sess.prefill_ragged(padded, lengths)
+    mamba_layers = [i for i in range(cfg.n_layers) if not cfg.is_attention_layer(i)]
+    om = cpu_oracle.OracleModel(cfg, tens)
+    alone = model.init_states(1, cap)
+    alone.set_option("chunked_prefill", 1)                  # the batched path whatever the length: the same arithmetic as above
+    nxt = np.zeros(B, dtype=np.uint32)
+    refs = []
+    for b in range(B):
+        alone.reset()
+        lg1 = alone.prefill(prompts[b:b + 1, :lengths[b]])
+        assert rel_err(logits[b], lg1[0]) < 2e-4, (case, b, int(lengths[b]), rel_err(logits[b], lg1[0]))
+        for layer in mamba_layers:
+            h, xp, bp, cum = sess.read_state(b, layer)
+            h1, xp1, bp1, cum1 = alone.read_state(0, layer)
+            assert np.abs(h - h1).max() <= 2e-4 * max(1.0, np.abs(h1).max()), (case, b, layer)
+            assert np.abs(xp - xp1).max() <= 2e-4 * max(1.0, np.abs(xp1).max()) and np.abs(bp - bp1).max() <= 2e-4 * max(1.0, np.abs(bp1).max())
+            assert np.abs(cum - cum1).max() < 2e-4
+        st = om.init_states()
+        for t in prompts[b, :lengths[b]]:
+            ref = st.forward_step(int(t))
+        refs.append(st)
+        assert rel_err(logits[b], ref) < TOL_F32, (case, b, int(lengths[b]), rel_err(logits[b], ref))
+        nxt[b] = cpu_oracle.argmax(ref)
+    # decoding continues for all sequences together: reads every sequence's K/V cache at its own position
+    for i in range(4):
+        lg, out = sess.forward_step(nxt, step=i)
+        for b in range(B):
+            ref = refs[b].forward_step(int(nxt[b]))
+            assert rel_err(lg[b], ref) < TOL_F32, (case, "decode", i, b, rel_err(lg[b], ref))
+            nxt[b] = cpu_oracle.argmax(ref)
+    alone.close()
+    sess.close()
+    model.close()
+
+
 def test_slot_reuse_by_transplanting_a_prefilled_sequence():
     """Continuous batching with the snapshot calls: while a batch of three sequences decodes, sequence 1 ends; a new
     prompt is prefilled in a one-slot side session, its snapshot is loaded into slot 1, and decoding goes on.
