@@ -4,6 +4,10 @@
 // tokens are walked in tiles with a running softmax, and split over several CTAs when the batch alone
 // would not fill the GPU.  The sliding window of the reference (keep the last `window` tokens) is a ring:
 // token t lives in slot t % window.  Optional rotary embedding (extension, off by default).
+//
+// Three kernels: attn_mma_kernel (bf16 cache, 64-wide heads: scores and context on the tensor cores, also the attend pass
+// of a prompt slice with several token rows per CTA), attn_decode_kernel (fp32 cache or other head widths: the same walk
+// on the CUDA cores), kv_append_kernel (the append pass of a prompt slice).  All stage whole pages in shared memory.
 #include "internal.h"
 
 #include <cuda.h>
@@ -71,8 +75,8 @@ __device__ __forceinline__ bool page_wait(uint64_t* bar, uint32_t parity) {
 // contiguous slice of the cached tokens (z).  A KV head's 64 rows of a page are one contiguous block, so thread 0
 // brings the K and the V block of each page into a ring of shared-memory stages with one bulk copy each (an mbarrier
 // per stage counts the bytes; every wait on it is bounded and reports STATUS_TIMEOUT) while the CTA works on the
-// pages that have landed: the copies of the next NST - 1 pages are always in flight.  Every CTA walks its slice in tiles of kAttnTile tokens with a running
-// maximum / sum / context (the usual rescaling when the maximum grows), so the softmax of inference/src/model.rs:535
+// pages that have landed: the copies of the next NST - 1 pages are always in flight.  Every CTA walks its slice in tiles
+// of kAttnTile tokens (one page) with a running maximum / sum / context (the usual rescaling when the maximum grows), so the softmax of inference/src/model.rs:535
 // is evaluated without ever holding more than one tile of scores.  With one slice the CTA normalises and writes the
 // context itself.  With several, each parks (max, sum, unnormalised context) per query head in `part`, and the CTA
 // that arrives last at the (row, KV head) counter merges the slices in slice order — a fixed order, so the result
