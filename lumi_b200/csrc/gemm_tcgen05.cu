@@ -307,6 +307,19 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
     // Launched with programmatic dependent launch (small batches), this CTA may have become resident and done all of the
     // above — barrier set-up, TMEM allocation — while its predecessor (the state step) still ran; everything below reads
     // what predecessors produced.  Without the launch attribute this is a no-op.
+    // The weights do not depend on any predecessor: the producer requests the weight tiles of its first stages before the
+    // wait, so that they stream from HBM under the predecessor's tail (at 64-128 rows the weights are most of the bytes).
+    uint32_t pre = 0;                            // stages whose weight tile is already on its way (and whose bytes are expected)
+    if (warp == 0 && lane == 0 && (int)blockIdx.x < ntiles * splits && (int)blockIdx.x != skip_unit) {
+        const int t = blockIdx.x / splits, sp = blockIdx.x - t * splits;
+        const int n0 = (t / tiles_m) * BN;
+        const int kb0 = sp * num_kb / splits, kb1 = (sp + 1) * num_kb / splits;
+        pre = (uint32_t)min(S, kb1 - kb0);
+        for (uint32_t i = 0; i < pre; ++i) {
+            mbar_expect_tx(&full_bar[i], (uint32_t)T::STAGE);
+            tma_load_2d(base + i * T::STAGE + T::A_BYTES * (SPLIT ? 2 : 1), &map_w, &full_bar[i], (kb0 + (int)i) * BK, n0);
+        }
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     bool timed_out = false;
@@ -323,10 +336,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid
                     const uint32_t ph = (kbg / S) & 1u;
                     if (!mbar_wait(&empty_bar[s], ph ^ 1u, wait_ns)) { timed_out = true; break; }
                     uint8_t* st = base + s * T::STAGE;
-                    mbar_expect_tx(&full_bar[s], (uint32_t)T::STAGE);
+                    if (kbg >= pre) mbar_expect_tx(&full_bar[s], (uint32_t)T::STAGE);
                     tma_load_2d(st, &map_ahi, &full_bar[s], kb * BK, m0);
                     if (SPLIT) tma_load_2d(st + T::A_BYTES, &map_alo, &full_bar[s], kb * BK, m0);
-                    tma_load_2d(st + T::A_BYTES * (SPLIT ? 2 : 1), &map_w, &full_bar[s], kb * BK, n0);
+                    if (kbg >= pre) tma_load_2d(st + T::A_BYTES * (SPLIT ? 2 : 1), &map_w, &full_bar[s], kb * BK, n0);
                 }
             }
             if (timed_out) {
