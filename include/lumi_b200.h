@@ -228,6 +228,13 @@ int32_t lumi_k_gemm_bf16_tcgen05(uint64_t a_hi, uint64_t a_lo, uint64_t w, uint6
 int32_t lumi_debug_gemm_wait_timeout(uint64_t a_hi, uint64_t w, uint64_t d, int32_t M, int32_t N, int32_t K,
                                      uint64_t wait_limit_ns, int32_t skip_unit, uint64_t status_word);
 
+/* Host-side only (no device is touched, nothing is launched; no counterpart in the reference): the output-tile width and
+ * the number of CTAs K is split over that lumi_k_gemm_bf16_tcgen05 and the decode / prefill steps take for a product of
+ * this shape.  two_planes: activations as bf16 hi + lo halves; producer: the epilogue also leaves the next RMSNorm's
+ * input (tile widths are then multiples of 32).  For tests of the choice and for reading profiles. */
+int32_t lumi_debug_gemm_plan(int32_t M, int32_t N, int32_t K, int32_t two_planes, int32_t producer, int32_t* width,
+                             int32_t* splits);
+
 /* Same contraction on CUDA cores with fp32 activations: D[M][N] = A[M][K] * W[N][K]^T (+ residual R).
  * w_dtype LUMI_DTYPE_*.  norm_gamma != 0 applies RMSNorm(gamma) to each row of A first. */
 int32_t lumi_k_gemv(uint64_t a_f32, uint64_t w, int32_t w_dtype, uint64_t d, uint64_t residual,

@@ -25,7 +25,7 @@ EXPORTS = [
     "lumi_model_finalize", "lumi_model_free", "lumi_model_info", "lumi_session_create", "lumi_session_reset",
     "lumi_session_free", "lumi_session_set_option", "lumi_prefill", "lumi_prefill_ragged", "lumi_decode_step", "lumi_generate",
     "lumi_decode_loop_device", "lumi_profile_step", "lumi_score", "lumi_session_read_state", "lumi_session_state_bytes", "lumi_session_save_state", "lumi_session_load_state", "lumi_debug_run_block", "lumi_k_gemm_bf16_tcgen05",
-    "lumi_k_gemv", "lumi_debug_gemm_wait_timeout", "lumi_k_ssm_step", "lumi_k_ssd_prefill", "lumi_mamba_block_static",
+    "lumi_k_gemv", "lumi_debug_gemm_wait_timeout", "lumi_debug_gemm_plan", "lumi_k_ssm_step", "lumi_k_ssd_prefill", "lumi_mamba_block_static",
 ]
 
 
@@ -84,6 +84,7 @@ def lib():
         L.lumi_k_gemv.argtypes = [u64, u64, i32, u64, u64, u64, i32, i32, i32, u64]
         L.lumi_k_ssm_step.argtypes = [u64, i32] + [u64] * 11 + [i32] * 5 + [u64]
         L.lumi_debug_gemm_wait_timeout.argtypes = [u64, u64, u64, i32, i32, i32, u64, i32, u64]
+        L.lumi_debug_gemm_plan.argtypes = [i32, i32, i32, i32, i32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
         L.lumi_k_ssd_prefill.argtypes = [u64, i32] + [u64] * 13 + [i32] * 4 + [u64]
         L.lumi_mamba_block_static.argtypes = [vp, i32, u64, u64, u64, u64, u64, i32, u64]
         _lib = L

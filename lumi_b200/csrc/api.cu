@@ -1645,6 +1645,26 @@ extern "C" int32_t lumi_k_gemm_bf16_tcgen05(uint64_t a_hi, uint64_t a_lo, uint64
 // the producer never requests.  The consumers' bounded waits run out, the kernel records STATUS_TIMEOUT in
 // *status_word (device int32, zeroed by the caller), drains what it issued, frees its TMEM and returns; the call
 // then answers LUMI_E_TIMEOUT.  Nothing faults and the context stays usable.
+// Host-side only: which tile width and K split the tensor-core GEMM takes for a shape (two_planes: activations as bf16
+// hi + lo; producer: the epilogue also leaves the next norm's input, which restricts the widths to multiples of 32).
+extern "C" int32_t lumi_debug_gemm_plan(int32_t M, int32_t N, int32_t K, int32_t two_planes, int32_t producer, int32_t* width,
+                                        int32_t* splits) {
+    if (M <= 0 || N <= 0 || K <= 0 || (K % 64) != 0 || !width || !splits) return fail(LUMI_E_INVALID, "gemm plan needs M, N > 0, K %% 64 == 0 and two outputs");
+    static int32_t dummy_counter = 0;
+    static float dummy_f = 0.f;
+    static __nv_bfloat16 dummy_h;
+    GemmArgs g{};
+    g.M = M; g.N = N; g.K = K;
+    g.a_hi = &dummy_h; g.a_lo = two_planes ? &dummy_h : nullptr;
+    g.tile_counters = &dummy_counter; g.n_counters = kGemmCounters;          // never dereferenced by the choice
+    g.scratch = &dummy_f; g.scratch_floats = kGemmScratchFloats;
+    if (producer) g.nf.out_hi = &dummy_h;
+    int w = 0, sp = 0;
+    gemm_tcgen05_plan(g, &w, &sp);
+    *width = w; *splits = sp;
+    return LUMI_OK;
+}
+
 extern "C" int32_t lumi_debug_gemm_wait_timeout(uint64_t a_hi, uint64_t w, uint64_t d, int32_t M, int32_t N, int32_t K, uint64_t wait_limit_ns,
                                                 int32_t skip_unit, uint64_t status_word) {
     if (!a_hi || !w || !d || !status_word) return fail(LUMI_E_INVALID, "null device pointer");

@@ -769,6 +769,9 @@ static void pick_tile(const GemmArgs& a, int* width, int* splits) {
     }
 }
 
+// The tile width and K split launch_gemm_tcgen05 would take for these arguments (host-side choice only; nothing is launched).
+void gemm_tcgen05_plan(const GemmArgs& a, int* width, int* splits) { pick_tile(a, width, splits); }
+
 int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st) {
     if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.K % BK) != 0)
         return fail(LUMI_E_UNSUPPORTED, "tcgen05 GEMM needs K %% 64 == 0 (M %d N %d K %d)", a.M, a.N, a.K);

@@ -341,6 +341,7 @@ struct GemmArgs {
     NormFuse nf;                        // RMSNorm folded around the product (persistent kernel only)
 };
 int32_t launch_gemm_tcgen05(const GemmArgs& a, cudaStream_t st);   // returns LUMI_* status
+void gemm_tcgen05_plan(const GemmArgs& a, int* width, int* splits);     // the tile width and K split that launch would take
 int32_t gemm_tcgen05_init();                                        // resolves the driver entry point
 
 // ---- batch-1 persistent decode kernel (decode_b1.cu) ---------------------------------------------

@@ -83,3 +83,23 @@ def test_bf16_rounding_is_nearest_even():
     got = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(x))
     assert got[0] == 1.0 and got[1] == 1.0 and got[2] == 1.015625 and got[3] == -2.5
     assert abs(got[4] - 3.14159265) < 2 ** -7
+
+
+@pytest.mark.parametrize("shape,two,producer,want", [
+    ((2048, 7360, 1024), 1, 0, (208, 1)),      # in_proj of a 2048-sequence wave: 576 tiles = 4 rounds of 148 SMs
+    ((2048, 1024, 2048), 1, 1, (128, 1)),      # out_proj: one round of 128 tiles; widths are multiples of 32 for the folded norm
+    ((64, 7360, 1024), 1, 0, (64, 1)),         # 115 tiles already fill the SMs: no split
+    ((64, 1024, 2048), 1, 1, (32, 4)),         # 32 narrow tiles and a long K: K split over 4 CTAs
+    ((128, 1024, 2816), 1, 1, (32, 4)),        # the MLP's second product at 128 rows
+    ((128, 1024, 1024), 1, 1, (32, 1)),        # K too short for a split to pay
+    ((256, 1024, 2048), 1, 1, (32, 1)),        # two row tiles: measured slower split, stays whole
+    ((512, 259, 1024), 1, 0, (32, 1)),
+])
+def test_gemm_tile_and_split_choice(shape, two, producer, want):
+    """Host logic of the tensor-core GEMM: which tile width and K split a shape gets (no device needed; 148 SMs assumed
+    where none is present)."""
+    w, sp = C.c_int32(), C.c_int32()
+    st = lumi_b200.lib().lumi_debug_gemm_plan(*shape, two, producer, C.byref(w), C.byref(sp))
+    assert st == 0 and (w.value, sp.value) == want, (shape, w.value, sp.value)
+    assert lumi_b200.lib().lumi_debug_gemm_plan(64, 64, 100, 1, 0, C.byref(w), C.byref(sp)) == -1      # K % 64
+
