@@ -412,13 +412,14 @@ def test_chunked_prefill_with_attention_layers(rows):
     _compare_tokens(toks[2], ref_toks, ref_logits, "hybrid chunked prefill, sequence 2")
 
 
-@pytest.mark.parametrize("case", ["hpk1", "hpk2", "hpk8", "window", "slices"])
+@pytest.mark.parametrize("case", ["hpk1", "hpk2", "hpk8", "window", "slices", "many_pages"])
 def test_tensor_core_attention_shapes(case):
     """The attention kernel for a bf16 cache with 64-wide heads (tensor cores, pages staged by tensor-map copies) against
     the oracle, over what its index arithmetic depends on: 1 / 2 / 8 query heads per KV head (16, 8, 2 token rows per
     CTA in the batched prefill; 4 is what the other hybrid tests run, with a ragged last group: 150 is not a multiple of 16), a sliding window whose ring wraps
     (decode form only: such a prompt goes token by token), and a context long enough to be split over several CTAs at a
-    batch of two (partial pages at the slice ends).  The batched prefill is also held against the token-by-token one."""
+    batch of two (partial pages at the slice ends), or over more slices than it has pages (empty slices; a capacity of more
+    than 64 pages).  The batched prefill is also held against the token-by-token one."""
     kv = {"hpk1": 16, "hpk2": 8, "hpk8": 2}.get(case, 4)
     kw = dict(n_layers=2, vocab_size=500, attention_layers=[1], attn_mlp_dim=256, attn_rope_base=10000.0, attn_kv_heads=kv)
     B, T, n_new, cap = 3, 150, 6, 256
@@ -427,6 +428,8 @@ def test_tensor_core_attention_shapes(case):
         T = 70
     if case == "slices":
         B, T, cap = 2, 600, 1024
+    if case == "many_pages":
+        B, T, cap = 1, 150, 4200     # a page table too long for the kernel's shared-memory copy, and 16 slices of which 13 are empty
     cfg = synth.base_config(**kw)
     assert cfg.attn_head_dim == 64
     tens = list(synth.iter_tensors(cfg, seed=21, weights_dtype="bf16", perturb_ones=0.05))
